@@ -1,0 +1,198 @@
+/*
+ * moondream_b200 — C ABI of the B200 (sm_100a) replacement for moondream-zig's
+ * FP16 matmul + attention hot path (src/core/{hgemm,hgemm_trans,attention,rope}.zig
+ * and the glue ops of src/core/ops.zig that sit between the GEMMs).
+ *
+ * Conventions
+ *  - f16 tensors are IEEE binary16 passed as `const uint16_t*` / `uint16_t*`,
+ *    row-major, with explicit sizes (`size_t`, the reference's `usize`).  The
+ *    reference's `Tensor(T)` struct is never passed: the Zig shim hands over
+ *    `tensor.data.ptr` and the dims.
+ *  - Every data pointer may be a HOST pointer or a DEVICE pointer of the
+ *    context's GPU (decided per pointer with cudaPointerGetAttributes):
+ *      host   -> "drop-in" mode: the call stages the buffer through device memory
+ *                owned by the context and returns when the result is back in the
+ *                caller's buffer (the reference's calls are synchronous).
+ *      device -> "resident" mode: the kernel is enqueued on the context's stream
+ *                and the call returns immediately; md_sync() waits.
+ *    A call whose OUTPUT is a host buffer always returns completed.
+ *  - Weights live for the whole process in the reference (preslice_text.zig:53-79);
+ *    upload them once with md_upload() and pass the returned device pointer to
+ *    the GEMM entry points.  Nothing is cached by host address (the reference's
+ *    slab allocator recycles addresses, slab_reusing_allocator.zig:141-156).
+ *  - Every function returns an md_status; md_last_error() describes the last failure.
+ *  - One context per GPU, used from one thread at a time.  No entry point ever
+ *    falls back to the CPU: without a usable sm_100a device md_init fails.
+ */
+#ifndef MOONDREAM_B200_H
+#define MOONDREAM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum md_status {
+    MD_OK = 0,
+    MD_ERR_INVALID_ARG = 1,      /* null pointer, zero size */
+    MD_ERR_INVALID_DIMENSION = 2,/* error.InvalidTensorDimension / InvalidInputDimensions */
+    MD_ERR_SHAPE = 3,            /* error.IncompatibleTensorShapes */
+    MD_ERR_SEQUENCE_TOO_LONG = 4,/* error.SequenceTooLong (attention.zig:769, text_model.zig:478) */
+    MD_ERR_INVALID_ROT_DIM = 5,  /* error.InvalidRotationDimension (rope.zig:141-143) */
+    MD_ERR_UNSUPPORTED = 6,
+    MD_ERR_OOM = 7,              /* error.OutOfMemory */
+    MD_ERR_CUDA = 8,
+    MD_ERR_TIMEOUT = 9,          /* a bounded device-side wait gave up; results are invalid */
+    MD_ERR_NO_DEVICE = 10
+} md_status;
+
+typedef struct md_ctx md_ctx;
+
+/* ---- context, memory, streams ------------------------------------------------ */
+
+/* Create a context on CUDA device `device`.  Fails with MD_ERR_NO_DEVICE when the
+ * device is absent or is not compute capability 10.x. */
+int md_init(md_ctx** out, int device);
+int md_destroy(md_ctx* ctx);
+/* Human-readable description of the last error on this context ("" if none).
+ * ctx may be NULL: then the last md_init failure is described. */
+const char* md_last_error(const md_ctx* ctx);
+/* Wait for everything enqueued on the context's stream; reports MD_ERR_TIMEOUT if
+ * any kernel since the last md_sync gave up on a bounded wait. */
+int md_sync(md_ctx* ctx);
+/* Use an existing cudaStream_t (e.g. the harness's stream) instead of the
+ * context's own.  NULL restores the context's own stream. */
+int md_set_stream(md_ctx* ctx, void* cuda_stream);
+/* Device memory owned by the caller until md_free. */
+int md_alloc(md_ctx* ctx, size_t bytes, void** dev_out);
+int md_free(md_ctx* ctx, void* dev);
+/* md_alloc + host->device copy: the "register a weight once" call. */
+int md_upload(md_ctx* ctx, const void* host, size_t bytes, void** dev_out);
+int md_memcpy_h2d(md_ctx* ctx, void* dev, const void* host, size_t bytes);
+int md_memcpy_d2h(md_ctx* ctx, void* host, const void* dev, size_t bytes);
+/* Number of kernels of this library launched on the context since md_init. */
+int md_launch_count(const md_ctx* ctx, uint64_t* count_out);
+/* Select the GEMM kernel: 0 = automatic (tcgen05 when the operands meet the TMA
+ * alignment rules, SIMT otherwise), 1 = force the SIMT kernel, 2 = force tcgen05
+ * (MD_ERR_UNSUPPORTED when the shape cannot take it).  For tests and profiling. */
+int md_set_gemm_mode(md_ctx* ctx, int mode);
+
+/* ---- matmul -------------------------------------------------------------------- */
+
+/* Replaces hgemm.matmul(a, b, allocator) — src/core/hgemm.zig:362-426.
+ * C[M,N] = A[M,K] . B[K,N]; f16 in/out, f32 accumulate, one rounding to f16. */
+int md_hgemm_nn(md_ctx* ctx, const uint16_t* a, const uint16_t* b, uint16_t* c, size_t M, size_t N, size_t K);
+
+/* Replaces hgemm_trans.matmul(a, b_transposed, allocator) — src/core/hgemm_trans.zig:400-488.
+ * C[M,N] = A[M,K] . B_t[N,K]^T.  M <= 8 takes the weight-streaming GEMV kernel
+ * (the reference has a dedicated path for M == 1 only, hgemm_trans.zig:430-455). */
+int md_hgemm_nt(md_ctx* ctx, const uint16_t* a, const uint16_t* b_t, uint16_t* c, size_t M, size_t N, size_t K);
+
+/* Shape checks of hgemm.zig:369-381 / hgemm_trans.zig:408-420 for callers that hold
+ * full shapes: rank != 2 -> MD_ERR_INVALID_DIMENSION, inner dims differ -> MD_ERR_SHAPE. */
+int md_check_matmul_shapes(const size_t* a_shape, size_t a_rank, const size_t* b_shape, size_t b_rank,
+                           int b_transposed);
+
+/* The GEMMs above with the glue the reference applies right after them fused into the
+ * epilogue, keeping the reference's rounding points: c = f16(acc); if bias: c = f16(c + bias[n])
+ * (ops.broadcast_add_simd, ops.zig:1780-1953); if gelu: c = gelu(c) (ops.gelu, ops.zig:1635-1774);
+ * if residual: c = f16(c + residual[m,n]) (ops.add, ops.zig:312-323).  bias/residual may be NULL.
+ * b_layout: 0 = B is [K,N] (hgemm), 1 = B is [N,K] (hgemm_trans).  All pointers device-resident. */
+int md_hgemm_fused(md_ctx* ctx, const uint16_t* a, const uint16_t* b, uint16_t* c, size_t M, size_t N, size_t K,
+                   int b_layout, const uint16_t* bias, int gelu, const uint16_t* residual);
+
+/* ---- attention ----------------------------------------------------------------- */
+
+/* Replaces attention.multiMasklessSDPA(n_heads, head_dim, q, k, v, allocator) —
+ * src/core/attention.zig:125-234.  q,out [n_heads,q_len,d]; k,v [n_heads,kv_len,d]. */
+int md_sdpa_maskless(md_ctx* ctx, const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* out,
+                     size_t n_heads, size_t q_len, size_t kv_len, size_t head_dim);
+
+/* Replaces attention.createAttentionMask(allocator, pos, seq_len) — attention.zig:256-281.
+ * mask is one byte per entry, [seq_len, pos+seq_len]. */
+int md_create_attention_mask(md_ctx* ctx, uint8_t* mask, size_t pos, size_t seq_len);
+
+/* Replaces attention.multiMaskedSDPA(q,k,v,mask,n_heads,head_dim,allocator) — attention.zig:416-541.
+ * mask [q_len, kv_len] bytes, 0 = masked out. */
+int md_sdpa_masked(md_ctx* ctx, const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint8_t* mask,
+                   uint16_t* out, size_t n_heads, size_t q_len, size_t kv_len, size_t head_dim);
+
+/* Replaces attention.singleMaskedSDPA(q,k,v,mask,allocator) — attention.zig:759-811.
+ * 32 heads x 64 dims fixed; q,out [32,1,64]; k,v [32,kv_len,64] contiguous; mask [kv_len];
+ * kv_len > 2048 -> MD_ERR_SEQUENCE_TOO_LONG. */
+int md_sdpa_single(md_ctx* ctx, const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint8_t* mask,
+                   uint16_t* out, size_t kv_len);
+
+/* The decode-step attention the GPU path uses instead of the sequence
+ * rope.applyRotEmb x2 -> LayerCache.updateCache -> getActiveCache -> createAttentionMask ->
+ * singleMaskedSDPA (text_model.zig:228-290): reads q,k,v of the new token from one row of the
+ * fused qkv projection ([3*n_heads*d]: q | k | v), rotates q and k at position `pos` in-kernel
+ * (partial rotary on the first rot_dim dims), appends k,v to the cache in place
+ * (layout [n_heads][max_seq][d], text_model.zig:392,485) and attends over positions 0..pos.
+ * out [n_heads*d].  Device pointers only.  pos >= max_seq -> MD_ERR_SEQUENCE_TOO_LONG. */
+int md_sdpa_decode_fused(md_ctx* ctx, const uint16_t* qkv_row, uint16_t* key_cache, uint16_t* value_cache,
+                         uint16_t* out, size_t n_heads, size_t head_dim, size_t max_seq, size_t pos,
+                         size_t rot_dim, float theta);
+
+/* The prefill attention the GPU path uses instead of the same sequence with multiMaskedSDPA
+ * (text_model.zig:228-290): qkv [S, 3*n_heads*d]; rotates q and k at positions pos..pos+S-1,
+ * appends k,v to the cache, causal attention over 0..pos+i for row i; out [S, n_heads*d]
+ * (already in the "transposed back" layout of text_model.zig:293-294).  Device pointers only. */
+int md_sdpa_prefill_fused(md_ctx* ctx, const uint16_t* qkv, uint16_t* key_cache, uint16_t* value_cache,
+                          uint16_t* out, size_t S, size_t n_heads, size_t head_dim, size_t max_seq, size_t pos,
+                          size_t rot_dim, float theta);
+
+/* ViT attention straight from the fused qkv projection (replaces the split / reshape / transposeAxes /
+ * multiMasklessSDPA / transposeAxes chain of vision_model.zig:285-330): qkv [crops*tokens, 3*n_heads*d],
+ * attention per crop over `tokens` keys, out [crops*tokens, n_heads*d].  Device pointers only. */
+int md_sdpa_vit_fused(md_ctx* ctx, const uint16_t* qkv, uint16_t* out, size_t crops, size_t tokens,
+                      size_t n_heads, size_t head_dim);
+
+/* ---- rope ---------------------------------------------------------------------- */
+
+/* Replaces rope.precomputeFreqsCis(f32, allocator, dim, end, theta) — src/core/rope.zig:32-128.
+ * table f32 [end, dim/2, 2] = (cos, sin). */
+int md_rope_table(md_ctx* ctx, float* table, size_t dim, size_t end, float theta);
+
+/* Replaces rope.applyRotEmb(allocator, x, n_heads, head_dim, freqs_cis, position_ids, rot_dim) —
+ * rope.zig:130-272.  x,out f16 [n_heads,seq_len,head_dim]; freqs_cis f32 [*, freqs_half, 2];
+ * position_ids u64 [seq_len] (the reference's usize).  rot_dim != 2*freqs_half -> MD_ERR_INVALID_ROT_DIM. */
+int md_rope_apply(md_ctx* ctx, const uint16_t* x, uint16_t* out, size_t n_heads, size_t seq_len, size_t head_dim,
+                  const float* freqs_cis, size_t freqs_half, const uint64_t* position_ids, size_t rot_dim);
+
+/* ---- KV cache (text_model.zig:383-516) ------------------------------------------- */
+
+/* LayerCache.updateCache — text_model.zig:476-515. k_new,v_new [n_heads,seq_len,d]. */
+int md_kv_update(md_ctx* ctx, uint16_t* key_cache, uint16_t* value_cache, const uint16_t* k_new,
+                 const uint16_t* v_new, size_t n_heads, size_t max_seq, size_t head_dim, size_t cur_len,
+                 size_t seq_len);
+/* LayerCache.getActiveCache — text_model.zig:436-474. */
+int md_kv_active(md_ctx* ctx, const uint16_t* key_cache, const uint16_t* value_cache, uint16_t* k_out,
+                 uint16_t* v_out, size_t n_heads, size_t max_seq, size_t head_dim, size_t cur_len);
+
+/* ---- glue ops between the GEMMs (src/core/ops.zig) ------------------------------- */
+
+/* ops.layerNorm(f16, x, w, b, eps) — ops.zig:1063-1070,1152-1419. eps is given as the f16 bits. */
+int md_layernorm(md_ctx* ctx, const uint16_t* x, const uint16_t* w, const uint16_t* b, uint16_t* y, size_t rows,
+                 size_t cols, uint16_t eps_f16);
+/* ops.gelu(f16, &x) in place — ops.zig:1635-1774. */
+int md_gelu(md_ctx* ctx, uint16_t* x, size_t n);
+/* ops.broadcast_add_simd(&a, b) in place — ops.zig:1780-1953; a [rows,cols] += b [cols]. */
+int md_bias_add(md_ctx* ctx, uint16_t* a, const uint16_t* b, size_t rows, size_t cols);
+/* ops.add(f16, &a, b) in place — ops.zig:312-323. */
+int md_add(md_ctx* ctx, uint16_t* a, const uint16_t* b, size_t n);
+/* sampling.argmax — src/utils/sampling.zig:257-273; first strict maximum. idx_out: host or device u64. */
+int md_argmax(md_ctx* ctx, const uint16_t* x, size_t n, uint64_t* idx_out);
+/* createPatches tail + convertBHWCtoBCHW + /255 + normalizePatch + rearrangeBCHWtoBTC
+ * (vision_model.zig:137-183, reshape_handler.zig:5-129): uint8 [crops,H,W,3] ->
+ * f16 [crops*(H/p)*(W/p), out_stride] with the first 3*p*p columns filled in (c,ph,pw) order and
+ * columns 3*p*p..out_stride-1 zeroed (out_stride >= 3*p*p lets the caller pad K for TMA). */
+int md_preprocess_patchify(md_ctx* ctx, const uint8_t* img, uint16_t* out, size_t crops, size_t height,
+                           size_t width, size_t patch, size_t out_stride);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOONDREAM_B200_H */

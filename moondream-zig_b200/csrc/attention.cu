@@ -1,0 +1,607 @@
+// Fused scaled-dot-product attention kernels.
+//
+//   sdpa_mma_kernel     multi-query attention (ViT 729 x 729 with d = 72, decoder prefill with
+//                       d = 64): replaces attention.multiMasklessSDPA (attention.zig:125-234)
+//                       and attention.multiMaskedSDPA (attention.zig:416-541).  The reference
+//                       materialises the full f32 score matrix per head and runs two f32 GEMMs
+//                       around a row softmax; here scores never leave the SM: 64-query x 64-key
+//                       tiles, S = Q K^T and O += P V on tensor cores (mma.sync m16n8k16, f32
+//                       accumulate), online softmax in f32 registers.  Strided addressing lets it
+//                       read q, k, v straight out of a fused qkv projection or the KV cache.
+//   sdpa_generic_kernel any head_dim <= 256, one warp per query row (odd shapes only).
+//   sdpa_decode_kernel  one query token against the cache (attention.singleMaskedSDPA,
+//                       attention.zig:564-642,759-811): split over the keys, 128-bit loads,
+//                       partial (max, sum, out) per split merged by the last CTA of each head.
+//                       The fused form also applies the partial rotary embedding to q and the
+//                       new k (rope.zig:130-272) and appends k, v to the cache in place
+//                       (text_model.zig:476-515), so no copy of the active cache is ever made
+//                       (text_model.zig:436-474 copies it on every call).
+//
+// Numerics: q, k, v are f16, scores / probabilities / accumulators f32, one rounding to f16
+// at the output (attention.zig:199-202,505-508,635-640).  The tensor-core kernel rounds the
+// probabilities to f16 for the P V product (relative error <= 2^-11 per weight).  A query row
+// whose keys are all masked yields zeros (the reference leaves -inf scores in place, which
+// cannot happen with the masks createAttentionMask builds).
+#include "md_internal.cuh"
+
+#include <cfloat>
+
+namespace {
+
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+struct SdpaParams {
+    const __half *q, *k, *v;
+    __half* out;
+    const uint8_t* mask;  // [q_len, kv_len] or null
+    int q_len, kv_len;
+    long long q_row, q_head, q_batch, kv_row, kv_head, kv_batch, o_row, o_head, o_batch;
+    int causal_pos;  // < 0: none; else key j is visible to query i iff j <= causal_pos + i
+    float scale_log2;  // (1/sqrt(d)) * log2(e)
+};
+
+constexpr int BQ = 64, BKV = 64;
+
+template <int D, int D_PAD>
+__global__ void __launch_bounds__(128)
+sdpa_mma_kernel(SdpaParams p) {
+    constexpr int PITCH = D_PAD + 8;  // halves; 144 B or 176 B rows keep ldmatrix conflict-free
+    constexpr int CHUNKS = D_PAD / 8, REAL_CHUNKS = D / 8;
+    __shared__ __align__(16) __half Qs[BQ][PITCH];
+    __shared__ __align__(16) __half Ks[BKV][PITCH];
+    __shared__ __align__(16) __half Vs[BKV][PITCH];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int q0 = blockIdx.x * BQ, head = blockIdx.y, batch = blockIdx.z;
+    const __half* qb = p.q + batch * p.q_batch + head * p.q_head;
+    const __half* kb = p.k + batch * p.kv_batch + head * p.kv_head;
+    const __half* vb = p.v + batch * p.kv_batch + head * p.kv_head;
+
+    for (int idx = tid; idx < BQ * CHUNKS; idx += 128) {
+        const int r = idx / CHUNKS, c = idx % CHUNKS;
+        if (q0 + r < p.q_len && c < REAL_CHUNKS)
+            cp_async16(smem_u32(&Qs[r][c * 8]), qb + (long long)(q0 + r) * p.q_row + c * 8);
+        else
+            *reinterpret_cast<uint4*>(&Qs[r][c * 8]) = make_uint4(0, 0, 0, 0);
+    }
+    cp_async_wait_all();
+    __syncthreads();
+
+    uint32_t qf[D_PAD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < D_PAD / 16; ++ks) {
+        const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = ks * 16 + (lane >> 4) * 8;
+        ldsm_x4(smem_u32(&Qs[r][c]), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+    }
+
+    float o[D_PAD / 8][4];
+#pragma unroll
+    for (int i = 0; i < D_PAD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const int qi[2] = {q0 + warp * 16 + g, q0 + warp * 16 + g + 8};
+
+    int kv_end = p.kv_len;
+    if (p.causal_pos >= 0) kv_end = min(kv_end, p.causal_pos + min(q0 + BQ, p.q_len));
+
+    for (int k0 = 0; k0 < kv_end; k0 += BKV) {
+        for (int idx = tid; idx < BKV * CHUNKS; idx += 128) {
+            const int r = idx / CHUNKS, c = idx % CHUNKS;
+            if (k0 + r < p.kv_len && c < REAL_CHUNKS) {
+                cp_async16(smem_u32(&Ks[r][c * 8]), kb + (long long)(k0 + r) * p.kv_row + c * 8);
+                cp_async16(smem_u32(&Vs[r][c * 8]), vb + (long long)(k0 + r) * p.kv_row + c * 8);
+            } else {
+                *reinterpret_cast<uint4*>(&Ks[r][c * 8]) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(&Vs[r][c * 8]) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        cp_async_wait_all();
+        __syncthreads();
+
+        float s[BKV / 8][4];
+#pragma unroll
+        for (int i = 0; i < BKV / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < D_PAD / 16; ++ks) {
+#pragma unroll
+            for (int np = 0; np < BKV / 16; ++np) {
+                uint32_t b0, b1, b2, b3;
+                const int r = np * 16 + (lane & 7) + (lane >> 4) * 8, c = ks * 16 + ((lane >> 3) & 1) * 8;
+                ldsm_x4(smem_u32(&Ks[r][c]), b0, b1, b2, b3);
+                mma_16816(s[2 * np], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
+                mma_16816(s[2 * np + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+            }
+        }
+
+        // scale (folded with log2 e), mask, row maxima
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < BKV / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int rr = e >> 1;
+                const int key = k0 + nt * 8 + 2 * t + (e & 1);
+                bool vis = key < p.kv_len && qi[rr] < p.q_len;
+                if (p.causal_pos >= 0) vis = vis && key <= p.causal_pos + qi[rr];
+                if (vis && p.mask) vis = p.mask[(long long)qi[rr] * p.kv_len + key] != 0;
+                const float v = vis ? s[nt][e] * p.scale_log2 : -INFINITY;
+                s[nt][e] = v;
+                mx[rr] = fmaxf(mx[rr], v);
+            }
+        }
+        float corr[2], m_use[2];
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+            mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+            const float m_new = fmaxf(m_run[rr], mx[rr]);
+            m_use[rr] = (m_new == -INFINITY) ? 0.f : m_new;
+            corr[rr] = (m_run[rr] == -INFINITY) ? 0.f : exp2f(m_run[rr] - m_use[rr]);
+            m_run[rr] = m_new;
+        }
+        float rs[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < BKV / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pv = exp2f(s[nt][e] - m_use[e >> 1]);
+                s[nt][e] = pv;
+                rs[e >> 1] += pv;
+            }
+        }
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            rs[rr] += __shfl_xor_sync(0xffffffffu, rs[rr], 1);
+            rs[rr] += __shfl_xor_sync(0xffffffffu, rs[rr], 2);
+            l_run[rr] = l_run[rr] * corr[rr] + rs[rr];
+        }
+#pragma unroll
+        for (int i = 0; i < D_PAD / 8; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk) {
+            const uint32_t a0 = pack_h2(s[2 * kk][0], s[2 * kk][1]), a1 = pack_h2(s[2 * kk][2], s[2 * kk][3]);
+            const uint32_t a2 = pack_h2(s[2 * kk + 1][0], s[2 * kk + 1][1]),
+                           a3 = pack_h2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int dp = 0; dp < D_PAD / 16; ++dp) {
+                uint32_t b0, b1, b2, b3;
+                const int r = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = dp * 16 + (lane >> 4) * 8;
+                ldsm_x4_t(smem_u32(&Vs[r][c]), b0, b1, b2, b3);
+                mma_16816(o[2 * dp], a0, a1, a2, a3, b0, b1);
+                mma_16816(o[2 * dp + 1], a0, a1, a2, a3, b2, b3);
+            }
+        }
+        __syncthreads();
+    }
+
+    __half* ob = p.out + batch * p.o_batch + head * p.o_head;
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        if (qi[rr] >= p.q_len) continue;
+        const float inv = l_run[rr] > 0.f ? 1.0f / l_run[rr] : 0.f;
+        __half* orow = ob + (long long)qi[rr] * p.o_row;
+#pragma unroll
+        for (int nt = 0; nt < D / 8; ++nt) {
+            const __half2 h = __floats2half2_rn(o[nt][2 * rr] * inv, o[nt][2 * rr + 1] * inv);
+            *reinterpret_cast<__half2*>(orow + nt * 8 + 2 * t) = h;
+        }
+    }
+}
+
+// One warp per (query row, head): any head_dim <= 256.  Slow path for odd shapes.
+__global__ void __launch_bounds__(128)
+sdpa_generic_kernel(SdpaParams p, int d, int n_heads, float scale) {
+    const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    const int total = p.q_len * n_heads;
+    const int batch = blockIdx.y;
+    if (warp_global >= total) return;
+    const int head = warp_global / p.q_len, qi = warp_global % p.q_len;
+    const __half* q = p.q + batch * p.q_batch + head * p.q_head + (long long)qi * p.q_row;
+    const __half* kb = p.k + batch * p.kv_batch + head * p.kv_head;
+    const __half* vb = p.v + batch * p.kv_batch + head * p.kv_head;
+    float qv[8], acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = lane + 32 * i;
+        qv[i] = c < d ? __half2float(q[c]) : 0.f;
+        acc[i] = 0.f;
+    }
+    float m = -INFINITY, l = 0.f;
+    for (int j = 0; j < p.kv_len; ++j) {
+        bool vis = true;
+        if (p.causal_pos >= 0) vis = j <= p.causal_pos + qi;
+        if (vis && p.mask) vis = p.mask[(long long)qi * p.kv_len + j] != 0;
+        if (!vis) continue;
+        const __half* kr = kb + (long long)j * p.kv_row;
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = lane + 32 * i;
+            if (c < d) dot += qv[i] * __half2float(kr[c]);
+        }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+        const float sc = dot * scale;
+        const float m_new = fmaxf(m, sc);
+        const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+        const float pw = expf(sc - m_new);
+        l = l * corr + pw;
+        const __half* vr = vb + (long long)j * p.kv_row;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = lane + 32 * i;
+            if (c < d) acc[i] = acc[i] * corr + pw * __half2float(vr[c]);
+        }
+        m = m_new;
+    }
+    __half* o = p.out + batch * p.o_batch + head * p.o_head + (long long)qi * p.o_row;
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = lane + 32 * i;
+        if (c < d) o[c] = __float2half_rn(acc[i] * inv);
+    }
+}
+
+// ------------------------------------------------------------------------------ decode
+constexpr int DEC_D = 64;          // head_dim (attention.zig:248-249)
+constexpr int DEC_KEYS = 128;      // keys per CTA (split)
+constexpr int DEC_WARPS = 4;
+
+struct DecodeParams {
+    const __half* q;        // plain: [n_heads][64]; fused: qkv row [3*n_heads*64]
+    const __half* k;        // [n_heads][k_head_stride / 64][64]
+    const __half* v;
+    __half* k_w;            // fused: cache to append to (same memory as k), else null
+    __half* v_w;
+    const uint8_t* mask;    // [kv_len] or null
+    __half* out;            // [n_heads][64]
+    float* partial;         // [n_heads][splits][66]: max, sum, out[64]
+    unsigned int* counters; // [n_heads], zero before launch, left zero after
+    long long k_head_stride;
+    int n_heads, kv_cache_len;  // keys to read from memory
+    int fused, pos, rot_dim;
+    float theta;
+    int splits;
+};
+
+__device__ __forceinline__ uint4 ldg_nc16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 x = __half22float2(h[i]);
+        f[2 * i] = x.x;
+        f[2 * i + 1] = x.y;
+    }
+}
+
+// rope.zig:50-65,223-230 for one head vector held in shared memory (f32 in, f16-rounded out).
+__device__ __forceinline__ float rope_elem(const float* x, int dd, int pos, int rot_dim, float theta) {
+    if (dd >= rot_dim) return x[dd];
+    const int half = rot_dim / 2, j = dd < half ? dd : dd - half;
+    const float freq = 1.0f / powf(theta, (float)(2 * j) / (float)rot_dim);
+    const float ang = (float)pos * freq;
+    const float c = cosf(ang), sn = sinf(ang);
+    const float xr = x[j], xi = x[j + half];
+    return dd < half ? xr * c - xi * sn : xr * sn + xi * c;
+}
+
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+sdpa_decode_kernel(DecodeParams p) {
+    __shared__ float q_s[DEC_D], knew_s[DEC_D], vnew_s[DEC_D], raw_s[DEC_D];
+    __shared__ float red_m[DEC_WARPS], red_l[DEC_WARPS], red_o[DEC_WARPS][DEC_D];
+    __shared__ int is_last;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int head = blockIdx.y, split = blockIdx.x;
+    const bool last_split = split == p.splits - 1;
+    const float scale = 0.125f;  // 1/sqrt(64)
+
+    // ---- stage q (and, fused, the new k and v) in shared memory
+    if (p.fused) {
+        const int hd = p.n_heads * DEC_D;
+        if (tid < DEC_D) raw_s[tid] = __half2float(p.q[head * DEC_D + tid]);
+        __syncthreads();
+        if (tid < DEC_D) q_s[tid] = md_round_f16(rope_elem(raw_s, tid, p.pos, p.rot_dim, p.theta));
+        __syncthreads();
+        if (last_split) {
+            if (tid < DEC_D) raw_s[tid] = __half2float(p.q[hd + head * DEC_D + tid]);
+            __syncthreads();
+            if (tid < DEC_D) {
+                const __half kr = __float2half_rn(rope_elem(raw_s, tid, p.pos, p.rot_dim, p.theta));
+                const __half vn = p.q[2 * hd + head * DEC_D + tid];
+                knew_s[tid] = __half2float(kr);
+                vnew_s[tid] = __half2float(vn);
+                p.k_w[head * p.k_head_stride + (long long)p.pos * DEC_D + tid] = kr;
+                p.v_w[head * p.k_head_stride + (long long)p.pos * DEC_D + tid] = vn;
+            }
+        }
+    } else {
+        if (tid < DEC_D) q_s[tid] = __half2float(p.q[head * DEC_D + tid]);
+    }
+    __syncthreads();
+
+    const int sub = lane & 7, grp = lane >> 3;  // 8 lanes x 16 B cover one 128-byte key row
+    float qv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) qv[i] = q_s[sub * 8 + i];
+
+    const __half* kh = p.k + head * p.k_head_stride;
+    const __half* vh = p.v + head * p.k_head_stride;
+    const int key_lo = split * DEC_KEYS + warp * (DEC_KEYS / DEC_WARPS);
+    constexpr int ITER = DEC_KEYS / DEC_WARPS / 4;  // 8 keys per lane group
+
+    uint4 kreg[ITER], vreg[ITER];
+    bool valid[ITER];
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+        const int key = key_lo + it * 4 + grp;
+        valid[it] = key < p.kv_cache_len;
+        kreg[it] = valid[it] ? ldg_nc16(kh + (long long)key * DEC_D + sub * 8) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+        const int key = key_lo + it * 4 + grp;
+        vreg[it] = valid[it] ? ldg_nc16(vh + (long long)key * DEC_D + sub * 8) : make_uint4(0, 0, 0, 0);
+    }
+    float sc[ITER];
+    float m = -INFINITY;
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+        float kf[8];
+        unpack8(kreg[it], kf);
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dot = fmaf(qv[i], kf[i], dot);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+        const int key = key_lo + it * 4 + grp;
+        bool vis = valid[it];
+        if (vis && p.mask) vis = p.mask[key] != 0;
+        sc[it] = vis ? dot * scale : -INFINITY;
+        m = fmaxf(m, sc[it]);
+    }
+    // the appended token: handled by lane group 0 of warp 0 of the last split
+    float s_new = -INFINITY;
+    const bool do_new = p.fused && last_split && warp == 0 && grp == 0;
+    if (do_new) {
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dot = fmaf(qv[i], knew_s[sub * 8 + i], dot);
+        dot += __shfl_xor_sync(0x000000ffu, dot, 1);
+        dot += __shfl_xor_sync(0x000000ffu, dot, 2);
+        dot += __shfl_xor_sync(0x000000ffu, dot, 4);
+        s_new = dot * scale;
+        m = fmaxf(m, s_new);
+    }
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+    const float m_use = (m == -INFINITY) ? 0.f : m;
+    float l = 0.f, acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+        const float pw = expf(sc[it] - m_use);  // exp(-inf) = 0 for masked / absent keys
+        l += pw;
+        float vf[8];
+        unpack8(vreg[it], vf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = fmaf(pw, vf[i], acc[i]);
+    }
+    if (do_new) {
+        const float pw = expf(s_new - m_use);
+        l += pw;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = fmaf(pw, vnew_s[sub * 8 + i], acc[i]);
+    }
+    // combine the four lane groups (each lane keeps its 8 dims)
+    l += __shfl_xor_sync(0xffffffffu, l, 8);
+    l += __shfl_xor_sync(0xffffffffu, l, 16);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 8);
+        acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 16);
+    }
+    if (lane < 8) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) red_o[warp][lane * 8 + i] = acc[i];
+    }
+    if (lane == 0) { red_m[warp] = m; red_l[warp] = l; }
+    __syncthreads();
+
+    // combine the warps: thread d < 64 owns output dim d
+    float M = -INFINITY, L = 0.f, O = 0.f;
+    if (tid < DEC_D) {
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, red_m[w]);
+        const float Mu = (M == -INFINITY) ? 0.f : M;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float f = (red_m[w] == -INFINITY) ? 0.f : expf(red_m[w] - Mu);
+            L += red_l[w] * f;
+            O += red_o[w][tid] * f;
+        }
+    }
+    if (p.splits == 1) {
+        if (tid < DEC_D) p.out[head * DEC_D + tid] = __float2half_rn(L > 0.f ? O / L : 0.f);
+        return;
+    }
+    float* mine = p.partial + ((long long)head * p.splits + split) * (DEC_D + 2);
+    if (tid < DEC_D) mine[2 + tid] = O;
+    if (tid == 0) { mine[0] = M; mine[1] = L; }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned int ticket = atomicAdd(&p.counters[head], 1u);
+        is_last = (ticket == (unsigned)p.splits - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (tid < DEC_D) {
+        const float* base = p.partial + (long long)head * p.splits * (DEC_D + 2);
+        float Mg = -INFINITY;
+        for (int s2 = 0; s2 < p.splits; ++s2) Mg = fmaxf(Mg, __ldcg(base + s2 * (DEC_D + 2)));
+        const float Mu = (Mg == -INFINITY) ? 0.f : Mg;
+        float Lg = 0.f, Og = 0.f;
+        for (int s2 = 0; s2 < p.splits; ++s2) {
+            const float ms = __ldcg(base + s2 * (DEC_D + 2));
+            const float f = (ms == -INFINITY) ? 0.f : expf(ms - Mu);
+            Lg += __ldcg(base + s2 * (DEC_D + 2) + 1) * f;
+            Og += __ldcg(base + s2 * (DEC_D + 2) + 2 + tid) * f;
+        }
+        p.out[head * DEC_D + tid] = __float2half_rn(Lg > 0.f ? Og / Lg : 0.f);
+    }
+    if (tid == 0) p.counters[head] = 0;  // ready for the next launch
+}
+
+// qkv [S, 3*H*d] -> rotated q [S, H*d], rotated k and raw v appended to the cache at pos..pos+S-1.
+__global__ void __launch_bounds__(128)
+rope_cache_write_kernel(const __half* __restrict__ qkv, __half* __restrict__ q_rot, __half* __restrict__ kc,
+                        __half* __restrict__ vc, int S, int H, int d, int max_seq, int pos, int rot_dim,
+                        float theta) {
+    const int s = blockIdx.x, hd = H * d;
+    const __half* row = qkv + (long long)s * 3 * hd;
+    const int half = rot_dim / 2;
+    for (int idx = threadIdx.x; idx < hd; idx += blockDim.x) {
+        const int h = idx / d, dd = idx % d;
+        float qo, ko;
+        if (dd < rot_dim) {
+            const int j = dd < half ? dd : dd - half;
+            const float freq = 1.0f / powf(theta, (float)(2 * j) / (float)rot_dim);
+            const float ang = (float)(pos + s) * freq;
+            const float c = cosf(ang), sn = sinf(ang);
+            const float qr = __half2float(row[h * d + j]), qi = __half2float(row[h * d + j + half]);
+            const float kr = __half2float(row[hd + h * d + j]), ki = __half2float(row[hd + h * d + j + half]);
+            qo = dd < half ? qr * c - qi * sn : qr * sn + qi * c;
+            ko = dd < half ? kr * c - ki * sn : kr * sn + ki * c;
+        } else {
+            qo = __half2float(row[idx]);
+            ko = __half2float(row[hd + idx]);
+        }
+        q_rot[(long long)s * hd + idx] = __float2half_rn(qo);
+        const long long cidx = ((long long)h * max_seq + pos + s) * d + dd;
+        kc[cidx] = __float2half_rn(ko);
+        vc[cidx] = row[2 * hd + idx];
+    }
+}
+
+}  // namespace
+
+int md_launch_sdpa(md_ctx* ctx, const __half* q, const __half* k, const __half* v, const uint8_t* mask, __half* out,
+                   size_t n_heads, size_t q_len, size_t kv_len, size_t d, size_t q_row, size_t q_head, size_t kv_row,
+                   size_t kv_head, size_t o_row, size_t o_head, size_t batch, size_t q_batch, size_t kv_batch,
+                   size_t o_batch, int causal_pos) {
+    if (d == 0 || d > 256) return md_fail(ctx, MD_ERR_UNSUPPORTED, "head_dim %zu not supported (1..256)", d);
+    SdpaParams p;
+    p.q = q; p.k = k; p.v = v; p.out = out; p.mask = mask;
+    p.q_len = (int)q_len; p.kv_len = (int)kv_len;
+    p.q_row = (long long)q_row; p.q_head = (long long)q_head; p.q_batch = (long long)q_batch;
+    p.kv_row = (long long)kv_row; p.kv_head = (long long)kv_head; p.kv_batch = (long long)kv_batch;
+    p.o_row = (long long)o_row; p.o_head = (long long)o_head; p.o_batch = (long long)o_batch;
+    p.causal_pos = causal_pos;
+    const float scale = 1.0f / sqrtf((float)d);
+    p.scale_log2 = scale * LOG2E;
+    auto aligned = [](const void* ptr, size_t a, size_t b, size_t c) {
+        return (reinterpret_cast<uintptr_t>(ptr) % 16 == 0) && (a % 8 == 0) && (b % 8 == 0) && (c % 8 == 0);
+    };
+    const bool vec_ok = aligned(q, q_row, q_head, q_batch) && aligned(k, kv_row, kv_head, kv_batch) &&
+                        aligned(v, kv_row, kv_head, kv_batch) && (reinterpret_cast<uintptr_t>(out) % 4 == 0) &&
+                        (o_row % 2 == 0) && (o_head % 2 == 0) && (o_batch % 2 == 0);
+    if ((d == 64 || d == 72) && vec_ok) {
+        dim3 grid((unsigned)((q_len + BQ - 1) / BQ), (unsigned)n_heads, (unsigned)batch);
+        if (d == 64) sdpa_mma_kernel<64, 64><<<grid, 128, 0, ctx->stream>>>(p);
+        else sdpa_mma_kernel<72, 80><<<grid, 128, 0, ctx->stream>>>(p);
+        MD_LAUNCH_CHECK(ctx, "sdpa_mma_kernel");
+        return MD_OK;
+    }
+    const size_t warps = q_len * n_heads;
+    dim3 grid((unsigned)((warps + 3) / 4), (unsigned)batch);
+    sdpa_generic_kernel<<<grid, 128, 0, ctx->stream>>>(p, (int)d, (int)n_heads, scale);
+    MD_LAUNCH_CHECK(ctx, "sdpa_generic_kernel");
+    return MD_OK;
+}
+
+static int decode_launch(md_ctx* ctx, DecodeParams& p) {
+    p.splits = (p.kv_cache_len + DEC_KEYS - 1) / DEC_KEYS;
+    if (p.splits < 1) p.splits = 1;
+    const size_t partial_bytes = (size_t)p.n_heads * p.splits * (DEC_D + 2) * sizeof(float);
+    void* scratch = nullptr;
+    MD_TRY(md_scratch(ctx, partial_bytes, &scratch));
+    p.counters = ctx->counters;
+    p.partial = reinterpret_cast<float*>(scratch);
+    dim3 grid((unsigned)p.splits, (unsigned)p.n_heads);
+    sdpa_decode_kernel<<<grid, DEC_WARPS * 32, 0, ctx->stream>>>(p);
+    MD_LAUNCH_CHECK(ctx, "sdpa_decode_kernel");
+    return MD_OK;
+}
+
+int md_launch_sdpa_single(md_ctx* ctx, const __half* q, const __half* k, const __half* v, const uint8_t* mask,
+                          __half* out, size_t kv_len) {
+    DecodeParams p{};
+    p.q = q; p.k = k; p.v = v; p.k_w = nullptr; p.v_w = nullptr; p.mask = mask; p.out = out;
+    p.k_head_stride = (long long)kv_len * DEC_D;
+    p.n_heads = 32; p.kv_cache_len = (int)kv_len; p.fused = 0; p.pos = 0; p.rot_dim = 0; p.theta = 0.f;
+    return decode_launch(ctx, p);
+}
+
+int md_launch_sdpa_decode_fused(md_ctx* ctx, const __half* qkv_row, __half* kc, __half* vc, __half* out,
+                                size_t n_heads, size_t d, size_t max_seq, size_t pos, size_t rot_dim, float theta) {
+    if (d != DEC_D || n_heads > 256)
+        return md_fail(ctx, MD_ERR_UNSUPPORTED, "decode attention supports head_dim 64 and <= 256 heads");
+    DecodeParams p{};
+    p.q = qkv_row; p.k = kc; p.v = vc; p.k_w = kc; p.v_w = vc; p.mask = nullptr; p.out = out;
+    p.k_head_stride = (long long)max_seq * DEC_D;
+    p.n_heads = (int)n_heads; p.kv_cache_len = (int)pos; p.fused = 1; p.pos = (int)pos; p.rot_dim = (int)rot_dim;
+    p.theta = theta;
+    return decode_launch(ctx, p);
+}
+
+int md_launch_rope_cache_write(md_ctx* ctx, const __half* qkv, __half* q_rot, __half* kc, __half* vc, size_t S,
+                               size_t n_heads, size_t d, size_t max_seq, size_t pos, size_t rot_dim, float theta) {
+    if (S == 0) return MD_OK;
+    rope_cache_write_kernel<<<(unsigned)S, 128, 0, ctx->stream>>>(qkv, q_rot, kc, vc, (int)S, (int)n_heads, (int)d,
+                                                                  (int)max_seq, (int)pos, (int)rot_dim, theta);
+    MD_LAUNCH_CHECK(ctx, "rope_cache_write_kernel");
+    return MD_OK;
+}

@@ -1,0 +1,430 @@
+// Tensor-core GEMM for sm_100a: C[M,N] = A[M,K] . B, f16 operands, f32 accumulation in
+// tensor memory, one rounding to f16, optional fused glue.  B is [N,K] ("NT",
+// hgemm_trans.zig:400-488) or [K,N] ("NN", hgemm.zig:362-426).
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of the A tile (128 x 64) and the
+//               B tile (BLOCK_N x 64) into a ring of shared-memory stages, 128-byte swizzle.
+//   warp 1      MMA issuer: one lane issues tcgen05.mma (128 x BLOCK_N x 16, kind::f16) with
+//               shared-memory descriptors; accumulators live in TMEM, two buffers of
+//               BLOCK_N columns so the epilogue of tile i overlaps the main loop of tile i+1.
+//               tcgen05.commit releases smem stages and publishes finished accumulators.
+//   warps 2..5  epilogue: tcgen05.ld (32 lanes x 32 columns) -> fused glue -> f16 ->
+//               swizzled smem -> TMA store (clips the M and N tails).
+// Tails: TMA zero-fills out-of-bounds loads and clips out-of-bounds stores, so any M, N, K
+// with 16-byte-aligned row strides is accepted.
+//
+// Every mbarrier wait is bounded (about a second); a wait that gives up records an error
+// in the context's device flag word, raises a CTA-wide abort flag that makes all later
+// waits return at once, and the kernel still runs to its end, frees its TMEM and exits.
+#include "md_internal.cuh"
+
+namespace {
+
+constexpr int BLOCK_M = 128, BLOCK_K = 64, UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BLOCK_M * BLOCK_K * 2;     // 16 KiB
+constexpr int EPI_WARPS = 4, EPI_BUF_BYTES = 32 * 128;   // 32 rows x 64 f16 per buffer
+constexpr int EPI_BYTES = EPI_WARPS * 2 * EPI_BUF_BYTES; // 32 KiB
+constexpr int SMEM_LIMIT = 232448;                       // 227 KiB opt-in maximum
+constexpr int BAR_BYTES = 1024;
+
+__host__ __device__ constexpr int stage_bytes(int block_n) { return A_STAGE_BYTES + block_n * BLOCK_K * 2; }
+__host__ __device__ constexpr int num_stages(int block_n) {
+    int s = (SMEM_LIMIT - 1024 /*alignment slack*/ - EPI_BYTES - BAR_BYTES) / stage_bytes(block_n);
+    return s > 10 ? 10 : s;
+}
+__host__ __device__ constexpr int smem_bytes(int block_n) {
+    return 1024 + num_stages(block_n) * stage_bytes(block_n) + EPI_BYTES + BAR_BYTES;
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+constexpr unsigned long long WAIT_BUDGET_NS = 1000000000ull;  // 1 s
+
+// Bounded wait.  Returns false (and records the failure) instead of spinning forever.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                            md_devflags* flags, unsigned site) {
+    const unsigned long long t0 = global_ns();
+    for (unsigned spin = 0;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if ((spin & 63u) == 63u && global_ns() - t0 > WAIT_BUDGET_NS) {
+            *abort_flag = 1;
+            if (atomicOr(&flags->error, 1u) == 0u) flags->where = site;
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          md_devflags* flags, unsigned site) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, flags, site);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src),
+                 "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
+//   K-major operand (rows of 64 halves = 128 B, 8-row groups 1024 B apart):
+//       leading offset unused (1), stride offset 1024 B.
+//   MN-major operand (64-element chunks of the MN dimension contiguous, k rows 128 B apart,
+//   8-k-row groups 1024 B apart, successive 64-element chunks `lbo_bytes` apart).
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;  // version
+    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+    return d;
+}
+
+template <int BLOCK_N, bool B_MN_MAJOR>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+               const __grid_constant__ CUtensorMap tm_c, int M, int N, int K, int tiles_m, int num_tiles,
+               md_epilogue ep, md_devflags* flags) {
+    constexpr int STAGES = num_stages(BLOCK_N);
+    constexpr int B_STAGE_BYTES = BLOCK_N * BLOCK_K * 2;
+    constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // 128, 256 or 512: a power of two >= 32
+    static_assert(BLOCK_N == 64 || BLOCK_N == 128 || BLOCK_N == 256, "BLOCK_N");
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw);
+    const uint32_t smem_a = base;
+    const uint32_t smem_b = base + STAGES * A_STAGE_BYTES;
+    const uint32_t smem_epi = base + STAGES * STAGE_BYTES;
+    uint8_t* epi_ptr = base_ptr + STAGES * STAGE_BYTES;
+    const uint32_t bars = smem_epi + EPI_BYTES;
+    uint8_t* bars_ptr = epi_ptr + EPI_BYTES;
+    // barrier block: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then tmem address, abort flag
+    const uint32_t bar_full = bars, bar_empty = bars + 8 * STAGES;
+    const uint32_t bar_tfull = bars + 16 * STAGES, bar_tempty = bar_tfull + 16;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_ptr + 16 * STAGES + 32);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 16 * STAGES + 36);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_tfull + 8 * b, 1);
+            mbar_init(bar_tempty + 8 * b, EPI_WARPS);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(const_cast<uint32_t*>(tmem_slot))),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * BLOCK_M, n0 = (tile / tiles_m) * BLOCK_N;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, flags, 1);
+                    const uint32_t full = bar_full + 8 * stage;
+                    mbar_expect_tx(full, STAGE_BYTES);
+                    tma_load_2d(smem_a + stage * A_STAGE_BYTES, &tm_a, full, kb * BLOCK_K, m0);
+                    if (B_MN_MAJOR) {
+#pragma unroll
+                        for (int j = 0; j < BLOCK_N / 64; ++j)
+                            tma_load_2d(smem_b + stage * B_STAGE_BYTES + j * (64 * BLOCK_K * 2), &tm_b, full,
+                                        n0 + j * 64, kb * BLOCK_K);
+                    } else {
+                        tma_load_2d(smem_b + stage * B_STAGE_BYTES, &tm_b, full, kb * BLOCK_K, n0);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+            // After an abort loads may still be in flight towards this CTA's shared memory:
+            // give them time to land before the CTA exits (they complete within microseconds).
+            if (*abort_flag) {
+                const unsigned long long t0 = global_ns();
+                while (global_ns() - t0 < 500000ull) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | ((B_MN_MAJOR ? 1u : 0u) << 16) | ((uint32_t)(BLOCK_N >> 3) << 17) |
+                                   ((uint32_t)(BLOCK_M >> 4) << 24);
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+                mbar_wait(bar_tempty + 8 * buf, acc_phase ^ 1u, abort_flag, flags, 2);
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BLOCK_N);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    mbar_wait(bar_full + 8 * stage, phase, abort_flag, flags, 3);
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_a + stage * A_STAGE_BYTES;
+                    const uint32_t b_addr = smem_b + stage * B_STAGE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        const uint64_t da = make_desc(a_addr + k * (UMMA_K * 2), 16, 1024);
+                        const uint64_t db = B_MN_MAJOR
+                                                ? make_desc(b_addr + k * (UMMA_K * 128), 64 * BLOCK_K * 2, 1024)
+                                                : make_desc(b_addr + k * (UMMA_K * 2), 16, 1024);
+                        tc_mma_f16(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tc_commit(bar_empty + 8 * stage);  // frees the smem stage once these MMAs retire
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                tc_commit(bar_tfull + 8 * buf);  // accumulator complete
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+        const uint32_t my_epi = smem_epi + (uint32_t)(warp - 2) * 2 * EPI_BUF_BYTES;
+        uint8_t* my_epi_ptr = epi_ptr + (warp - 2) * 2 * EPI_BUF_BYTES;
+        const bool hb = ep.bias != nullptr, hr = ep.residual != nullptr, gelu = ep.gelu != 0;
+        int local = 0, bufsel = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+            const int m0 = (tile % tiles_m) * BLOCK_M, n0 = (tile / tiles_m) * BLOCK_N;
+            const int buf = local & 1;
+            const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+            mbar_wait(bar_tfull + 8 * buf, acc_phase, abort_flag, flags, 4);
+            tc_fence_after();
+            const int row = m0 + quad * 32 + lane;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BLOCK_N);
+#pragma unroll 1
+            for (int c = 0; c < BLOCK_N / 64; ++c) {
+                // the buffer about to be overwritten must have been read by its earlier TMA store
+                if (lane == 0) tma_store_wait_read<1>();
+                __syncwarp();
+                uint8_t* out_row = my_epi_ptr + bufsel * EPI_BUF_BYTES + lane * 128;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t r[32];
+                    tc_ld_32x32(t_row + (uint32_t)(c * 64 + h * 32), r);
+                    tc_wait_ld();
+                    const int col0 = n0 + c * 64 + h * 32;
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        float v0 = __uint_as_float(r[2 * j]), v1 = __uint_as_float(r[2 * j + 1]);
+                        if (hb || hr || gelu) {
+                            const int c0 = col0 + 2 * j, c1 = c0 + 1;
+                            const float b0 = (hb && c0 < N) ? __half2float(ep.bias[c0]) : 0.f;
+                            const float b1 = (hb && c1 < N) ? __half2float(ep.bias[c1]) : 0.f;
+                            float r0 = 0.f, r1 = 0.f;
+                            if (hr && row < M) {
+                                if (c0 < N) r0 = __half2float(ep.residual[(size_t)row * N + c0]);
+                                if (c1 < N) r1 = __half2float(ep.residual[(size_t)row * N + c1]);
+                            }
+                            v0 = md_apply_epilogue(v0, b0, hb, gelu, r0, hr);
+                            v1 = md_apply_epilogue(v1, b1, hb, gelu, r1, hr);
+                        }
+                        __half2 p = __floats2half2_rn(v0, v1);
+                        packed[j] = *reinterpret_cast<uint32_t*>(&p);
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int chunk = (h * 4 + q) ^ (lane & 7);  // 128-byte swizzle, matches the store map
+                        *reinterpret_cast<uint4*>(out_row + chunk * 16) =
+                            make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                    }
+                }
+                if (c == BLOCK_N / 64 - 1) {
+                    // all of this warp's TMEM reads of the tile are done: hand the buffer back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(&tm_c, my_epi + bufsel * EPI_BUF_BYTES, n0 + c * 64, m0 + quad * 32);
+                    tma_store_commit();
+                }
+                bufsel ^= 1;
+            }
+        }
+        if (lane == 0) tma_store_wait_all();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                     : "memory");
+    }
+}
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int make_map_2d(md_ctx* ctx, CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,
+                uint32_t box_outer) {
+    if (!ctx->encode_tiled) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
+            return md_fail(ctx, MD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        ctx->encode_tiled = fn;
+    }
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {inner * 2};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult r = reinterpret_cast<encode_tiled_fn>(ctx->encode_tiled)(
+        map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return md_fail(ctx, MD_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return MD_OK;
+}
+
+template <int BLOCK_N, bool B_MN_MAJOR>
+int launch(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
+           const md_epilogue& ep) {
+    CUtensorMap tm_a, tm_b, tm_c;
+    MD_TRY(make_map_2d(ctx, &tm_a, a, K, M, BLOCK_K, BLOCK_M));
+    if (B_MN_MAJOR) MD_TRY(make_map_2d(ctx, &tm_b, b, N, K, 64, BLOCK_K));
+    else MD_TRY(make_map_2d(ctx, &tm_b, b, K, N, BLOCK_K, BLOCK_N));
+    MD_TRY(make_map_2d(ctx, &tm_c, c, N, M, 64, 32));
+    const int tiles_m = (int)((M + BLOCK_M - 1) / BLOCK_M), tiles_n = (int)((N + BLOCK_N - 1) / BLOCK_N);
+    const int num_tiles = tiles_m * tiles_n;
+    const int grid = num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count;
+    auto kern = gemm_tc_kernel<BLOCK_N, B_MN_MAJOR>;
+    constexpr int smem = smem_bytes(BLOCK_N);
+    const uint32_t cfg_bit = 1u << ((BLOCK_N == 256 ? 0 : BLOCK_N == 128 ? 1 : 2) + (B_MN_MAJOR ? 3 : 0));
+    if (!(ctx->tc_configured & cfg_bit)) {
+        MD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        ctx->tc_configured |= cfg_bit;
+    }
+    kern<<<grid, 192, smem, ctx->stream>>>(tm_a, tm_b, tm_c, (int)M, (int)N, (int)K, tiles_m, num_tiles, ep,
+                                           ctx->flags);
+    MD_LAUNCH_CHECK(ctx, "gemm_tc_kernel");
+    return MD_OK;
+}
+
+}  // namespace
+
+bool md_gemm_tc_supported(const void* a, const void* b, const void* c, size_t M, size_t N, size_t K, int b_layout) {
+    (void)b_layout;
+    if (M == 0 || N == 0 || K == 0) return false;
+    if ((K % 8) != 0 || (N % 8) != 0) return false;  // row strides must be multiples of 16 bytes
+    if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15)
+        return false;
+    if (M > (1u << 30) || N > (1u << 30) || K > (1u << 30)) return false;
+    return true;
+}
+
+int md_launch_gemm_tc(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
+                      int b_layout, const md_epilogue& ep) {
+    if (!md_gemm_tc_supported(a, b, c, M, N, K, b_layout))
+        return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 GEMM needs K %% 8 == 0, N %% 8 == 0 and 16-byte aligned operands");
+    // Tile width: the widest tile that still gives every SM work; narrow tiles for skinny
+    // problems, which are bandwidth-bound and want many CTAs streaming B.
+    const size_t tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
+    auto tiles = [&](size_t bn) { return tiles_m * ((N + bn - 1) / bn); };
+    int bn = 256;
+    if (tiles(256) < (size_t)ctx->sm_count) bn = 128;
+    if (bn == 128 && tiles(128) < (size_t)ctx->sm_count) bn = 64;
+    const bool mn = (b_layout == 0);
+    if (mn) {
+        if (bn == 256) return launch<256, true>(ctx, a, b, c, M, N, K, ep);
+        if (bn == 128) return launch<128, true>(ctx, a, b, c, M, N, K, ep);
+        return launch<64, true>(ctx, a, b, c, M, N, K, ep);
+    }
+    if (bn == 256) return launch<256, false>(ctx, a, b, c, M, N, K, ep);
+    if (bn == 128) return launch<128, false>(ctx, a, b, c, M, N, K, ep);
+    return launch<64, false>(ctx, a, b, c, M, N, K, ep);
+}

@@ -1,0 +1,144 @@
+// Weight-streaming GEMV for the decode path: C[M,N] = A[M,K] . Bt[N,K]^T with M <= 8.
+//
+// Replaces the M == 1 vector path of hgemm_trans.zig:55-134,430-455 and, for
+// M in 2..8, the scalar remainder-row loop the reference falls into
+// (hgemm_trans.zig:348-356).  HBM-bound: every weight byte is read exactly once
+// (N*K*2 bytes); the M activation rows (M*K*2 bytes) stay in L1/L2.
+//
+// Mapping.  A CTA owns 16 consecutive weight rows; its WARPS warps split K.
+// Each lane streams 16-byte pieces (8 halves) of two weight rows with
+// ld.global.nc, so the 4 lanes of a quad cover 64 contiguous bytes of a row and
+// a warp instruction covers 16 rows x 64 B.  The multiply-accumulate runs on the
+// tensor cores as mma.sync.m16n8k16 with the 16 weight rows as the "M" side and
+// the (up to) 8 activation rows as the "N" side: the order of the k index inside
+// a dot product is free, so the 8 halves a lane loaded feed two MMAs directly
+// (halves 0..3 -> k slots {2t,2t+1,2t+8,2t+9} of the first, 4..7 of the second)
+// as long as the activation fragment is loaded with the same permutation, which
+// it is by reading the same 16-byte piece of row g of A.  This removes the
+// f16->f32 convert and FMA issue pressure of a SIMT GEMV for every M up to 8,
+// accumulates in f32, and needs no shuffle reduction: the warps' partial 16x8
+// tiles are summed through shared memory.
+#include "md_internal.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int ROWS_PER_CTA = 16;
+
+// UNROLL = number of 32-wide k chunks whose loads are issued before any is consumed.
+template <int WARPS, int UNROLL>
+__global__ void __launch_bounds__(WARPS * 32)
+gemv_nt_mma_kernel(const __half* __restrict__ A, const __half* __restrict__ Bt, __half* __restrict__ C, int M, int N,
+                   int K, md_epilogue ep) {
+    __shared__ float partial[WARPS][ROWS_PER_CTA][8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int row0 = blockIdx.x * ROWS_PER_CTA;
+    // Rows past N are clamped for the loads and dropped at the store.
+    const int r_lo = min(row0 + g, N - 1), r_hi = min(row0 + g + 8, N - 1);
+    const __half* w_lo = Bt + (size_t)r_lo * K + t * 8;
+    const __half* w_hi = Bt + (size_t)r_hi * K + t * 8;
+    const bool has_x = g < M;
+    const __half* x = A + (size_t)(has_x ? g : 0) * K + t * 8;
+
+    // K is split into 32-wide chunks dealt round-robin to the warps, so that at any
+    // moment the CTA reads one contiguous span of each of its 16 rows.
+    const int chunks = K / 32;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    int ch = warp;
+    for (; ch + (UNROLL - 1) * WARPS < chunks; ch += UNROLL * WARPS) {
+        uint4 lo[UNROLL], hi[UNROLL], xv[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = (ch + u * WARPS) * 32;
+            lo[u] = ldg_stream(w_lo + k);
+            hi[u] = ldg_stream(w_hi + k);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = (ch + u * WARPS) * 32;
+            xv[u] = has_x ? __ldg(reinterpret_cast<const uint4*>(x + k)) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            mma_16816(acc, lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv[u].x, xv[u].y);
+            mma_16816(acc, lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv[u].z, xv[u].w);
+        }
+    }
+    for (; ch < chunks; ch += WARPS) {
+        const int k = ch * 32;
+        const uint4 lo = ldg_stream(w_lo + k), hi = ldg_stream(w_hi + k);
+        const uint4 xv = has_x ? __ldg(reinterpret_cast<const uint4*>(x + k)) : make_uint4(0, 0, 0, 0);
+        mma_16816(acc, lo.x, hi.x, lo.y, hi.y, xv.x, xv.y);
+        mma_16816(acc, lo.z, hi.z, lo.w, hi.w, xv.z, xv.w);
+    }
+    // K tail (K % 32 != 0, still a multiple of 8): 8-half pieces handled by warp 0 with
+    // the lanes whose piece exists; missing pieces contribute zeros.
+    const int tail0 = chunks * 32;
+    if (warp == 0 && tail0 < K) {
+        const int k = tail0 + t * 8;
+        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo, xv = lo;
+        if (k < K) {
+            lo = ldg_stream(Bt + (size_t)r_lo * K + k);
+            hi = ldg_stream(Bt + (size_t)r_hi * K + k);
+            if (has_x) xv = __ldg(reinterpret_cast<const uint4*>(A + (size_t)g * K + k));
+        }
+        mma_16816(acc, lo.x, hi.x, lo.y, hi.y, xv.x, xv.y);
+        mma_16816(acc, lo.z, hi.z, lo.w, hi.w, xv.z, xv.w);
+    }
+
+    // c0,c1 = (weight row g, activation rows 2t,2t+1); c2,c3 = (weight row g+8, same).
+    partial[warp][g][2 * t] = acc[0];
+    partial[warp][g][2 * t + 1] = acc[1];
+    partial[warp][g + 8][2 * t] = acc[2];
+    partial[warp][g + 8][2 * t + 1] = acc[3];
+    __syncthreads();
+    if (threadIdx.x < ROWS_PER_CTA * 8) {
+        const int m = threadIdx.x >> 4, r = threadIdx.x & 15;  // consecutive threads -> consecutive n
+        const int n = row0 + r;
+        if (m < M && n < N) {
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) s += partial[w][r][m];
+            const bool hb = ep.bias != nullptr, hr = ep.residual != nullptr;
+            const float bias = hb ? __half2float(ep.bias[n]) : 0.f;
+            const float res = hr ? __half2float(ep.residual[(size_t)m * N + n]) : 0.f;
+            C[(size_t)m * N + n] = __float2half_rn(md_apply_epilogue(s, bias, hb, ep.gelu != 0, res, hr));
+        }
+    }
+}
+
+}  // namespace
+
+int md_launch_gemv_nt(md_ctx* ctx, const __half* a, const __half* bt, __half* c, size_t M, size_t N, size_t K,
+                      const md_epilogue& ep) {
+    if (M == 0 || M > 8 || (K % 8) != 0 || K == 0 || N == 0)
+        return md_fail(ctx, MD_ERR_UNSUPPORTED, "gemv_nt needs 1 <= M <= 8 and K %% 8 == 0 (M=%zu K=%zu)", M, K);
+    if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(bt)) & 15)
+        return md_fail(ctx, MD_ERR_UNSUPPORTED, "gemv_nt needs 16-byte aligned operands");
+    const unsigned grid = (unsigned)((N + ROWS_PER_CTA - 1) / ROWS_PER_CTA);
+    // Few weight rows (N <= 4096): more warps per CTA so enough bytes are in flight;
+    // many rows: fewer warps, deeper unroll.
+    if (K >= 4096) {
+        gemv_nt_mma_kernel<8, 4><<<grid, 8 * 32, 0, ctx->stream>>>(a, bt, c, (int)M, (int)N, (int)K, ep);
+    } else {
+        gemv_nt_mma_kernel<4, 8><<<grid, 4 * 32, 0, ctx->stream>>>(a, bt, c, (int)M, (int)N, (int)K, ep);
+    }
+    MD_LAUNCH_CHECK(ctx, "gemv_nt_mma_kernel");
+    return MD_OK;
+}

@@ -1,0 +1,160 @@
+// Internal declarations shared by the translation units of libmoondream_b200.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/moondream_b200.h"
+
+// Device-side error word: bit 0 = a bounded wait gave up.  One word per context,
+// zeroed at md_init and re-zeroed by md_sync after it has been reported.
+struct md_devflags {
+    unsigned int error;
+    unsigned int where;  // site id of the first wait that gave up
+};
+
+struct md_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    md_devflags* flags = nullptr;       // device
+    md_devflags* flags_host = nullptr;  // pinned host mirror
+    std::string last_error;
+    uint64_t launches = 0;
+    int gemm_mode = 0;
+    // staging buffers for host-pointer ("drop-in") calls, grown on demand
+    struct Stage { void* ptr = nullptr; size_t cap = 0; };
+    std::vector<Stage> stage;
+    // scratch for kernels that need global memory beyond inputs and outputs
+    void* scratch = nullptr;
+    size_t scratch_cap = 0;
+    // per-head arrival counters of the split-KV decode attention: zero between launches
+    unsigned int* counters = nullptr;
+    // cuTensorMapEncodeTiled resolved through the runtime (no link against libcuda)
+    void* encode_tiled = nullptr;
+    uint32_t tc_configured = 0;  // kernels whose dynamic shared memory limit has been raised
+};
+
+int md_fail(md_ctx* ctx, int status, const char* fmt, ...);
+#define MD_CUDA(ctx, expr)                                                                      \
+    do {                                                                                        \
+        cudaError_t _e = (expr);                                                                \
+        if (_e != cudaSuccess)                                                                  \
+            return md_fail((ctx), _e == cudaErrorMemoryAllocation ? MD_ERR_OOM : MD_ERR_CUDA,   \
+                           "%s failed: %s", #expr, cudaGetErrorString(_e));                     \
+    } while (0)
+#define MD_TRY(expr)                    \
+    do {                                \
+        int _s = (expr);                \
+        if (_s != MD_OK) return _s;     \
+    } while (0)
+
+// Ensure ctx->scratch holds at least `bytes`.
+int md_scratch(md_ctx* ctx, size_t bytes, void** out);
+
+// Host-or-device argument resolution for drop-in calls.
+bool md_is_device_ptr(const void* p);
+struct md_arg {
+    const void* user = nullptr;
+    void* dev = nullptr;
+    size_t bytes = 0;
+    bool staged = false;
+};
+// Bring an input to the device (no-op for device pointers). slot selects the staging buffer.
+int md_stage_in(md_ctx* ctx, int slot, const void* user, size_t bytes, md_arg* out);
+// Reserve device space for an output (no-op for device pointers).
+int md_stage_out(md_ctx* ctx, int slot, void* user, size_t bytes, md_arg* out);
+// Copy a staged output back and wait; for device outputs nothing happens.
+int md_finish_out(md_ctx* ctx, md_arg* out);
+// After a drop-in call whose output was a host buffer: check the device error word.
+int md_check_flags(md_ctx* ctx);
+
+// ---- kernel launchers (device pointers only) ------------------------------------
+struct md_epilogue {
+    const __half* bias = nullptr;      // [N] or null
+    const __half* residual = nullptr;  // [M,N] or null
+    int gelu = 0;
+};
+
+// gemv.cu: C[M,N] = A[M,K] . Bt[N,K]^T for M <= 8, K % 8 == 0.
+int md_launch_gemv_nt(md_ctx* ctx, const __half* a, const __half* bt, __half* c, size_t M, size_t N, size_t K,
+                      const md_epilogue& ep);
+// gemm_simt.cu: any shape; b_layout 0 = [K,N], 1 = [N,K].
+int md_launch_gemm_simt(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
+                        int b_layout, const md_epilogue& ep);
+// gemm_tc.cu: tcgen05 + TMA; returns MD_ERR_UNSUPPORTED when alignment rules are not met.
+bool md_gemm_tc_supported(const void* a, const void* b, const void* c, size_t M, size_t N, size_t K, int b_layout);
+int md_launch_gemm_tc(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
+                      int b_layout, const md_epilogue& ep);
+
+// attention.cu
+int md_launch_sdpa(md_ctx* ctx, const __half* q, const __half* k, const __half* v, const uint8_t* mask, __half* out,
+                   size_t n_heads, size_t q_len, size_t kv_len, size_t d,
+                   // strides in elements: q/out row stride and head stride, k/v row stride and head stride
+                   size_t q_row, size_t q_head, size_t kv_row, size_t kv_head, size_t o_row, size_t o_head,
+                   size_t batch, size_t q_batch, size_t kv_batch, size_t o_batch, int causal_pos);
+int md_launch_sdpa_single(md_ctx* ctx, const __half* q, const __half* k, const __half* v, const uint8_t* mask,
+                          __half* out, size_t kv_len);
+int md_launch_sdpa_decode_fused(md_ctx* ctx, const __half* qkv_row, __half* kc, __half* vc, __half* out,
+                                size_t n_heads, size_t d, size_t max_seq, size_t pos, size_t rot_dim, float theta);
+int md_launch_rope_cache_write(md_ctx* ctx, const __half* qkv, __half* q_rot, __half* kc, __half* vc, size_t S,
+                               size_t n_heads, size_t d, size_t max_seq, size_t pos, size_t rot_dim, float theta);
+
+// glue.cu
+int md_launch_layernorm(md_ctx* ctx, const __half* x, const __half* w, const __half* b, __half* y, size_t rows,
+                        size_t cols, float eps);
+int md_launch_gelu(md_ctx* ctx, __half* x, size_t n);
+int md_launch_bias_add(md_ctx* ctx, __half* a, const __half* b, size_t rows, size_t cols);
+int md_launch_add(md_ctx* ctx, __half* a, const __half* b, size_t n);
+int md_launch_argmax(md_ctx* ctx, const __half* x, size_t n, unsigned long long* idx_dev);
+int md_launch_patchify(md_ctx* ctx, const uint8_t* img, __half* out, size_t crops, size_t h, size_t w, size_t patch,
+                       size_t out_stride);
+int md_launch_rope_table(md_ctx* ctx, float* table, size_t dim, size_t end, float theta);
+int md_launch_rope_apply(md_ctx* ctx, const __half* x, __half* out, size_t n_heads, size_t seq_len, size_t d,
+                         const float* freqs, const unsigned long long* pos, size_t rot_dim);
+int md_launch_mask(md_ctx* ctx, uint8_t* mask, size_t pos, size_t seq_len);
+int md_launch_kv_update(md_ctx* ctx, __half* kc, __half* vc, const __half* k, const __half* v, size_t n_heads,
+                        size_t max_seq, size_t d, size_t cur_len, size_t seq_len);
+int md_launch_kv_active(md_ctx* ctx, const __half* kc, const __half* vc, __half* k, __half* v, size_t n_heads,
+                        size_t max_seq, size_t d, size_t cur_len);
+
+#define MD_LAUNCH_CHECK(ctx, name)                                                             \
+    do {                                                                                       \
+        cudaError_t _e = cudaGetLastError();                                                   \
+        if (_e != cudaSuccess)                                                                 \
+            return md_fail((ctx), MD_ERR_CUDA, "launch of %s failed: %s", name,                \
+                           cudaGetErrorString(_e));                                            \
+        (ctx)->launches++;                                                                     \
+    } while (0)
+
+// ---- device helpers ----------------------------------------------------------------
+#ifdef __CUDACC__
+// The reference's rounding points for the glue fused into GEMM epilogues.
+__device__ __forceinline__ float md_round_f16(float v) { return __half2float(__float2half_rn(v)); }
+
+__device__ __forceinline__ float md_gelu_f32(float v) {
+    // ops.zig:1641-1642: sqrt(2/pi) and 0.044715 are f16 constants in the reference.
+    const float c = 0.7978515625f, a = 0.044708251953125f;
+    const float inner = c * (v + a * (v * v * v));
+    return 0.5f * v * (1.0f + tanhf(inner));
+}
+
+// acc (f32 accumulator) -> f16 value after the fused glue, as f32 holding an f16-representable value.
+__device__ __forceinline__ float md_apply_epilogue(float acc, float bias, bool has_bias, bool gelu, float resid,
+                                                   bool has_resid) {
+    float v = md_round_f16(acc);
+    if (has_bias) v = md_round_f16(v + bias);
+    if (gelu) v = md_round_f16(md_gelu_f32(v));
+    if (has_resid) v = md_round_f16(v + resid);
+    return v;
+}
+#endif

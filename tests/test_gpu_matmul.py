@@ -1,0 +1,190 @@
+"""GPU parity of the matmul entry points against the oracle, through the C ABI.
+
+Covers the reference's own hgemm test cases (src/core/matmul_test.zig:154-367, same fill
+patterns and comparison rule), the BASELINE shapes (config 1, the decode GEMV sweep, vision
+and prefill GEMMs) with the north-star tolerance max|gpu - ref| <= 1e-2 * max|ref|, edge
+shapes around the tile sizes, and size-independent properties at full size."""
+import numpy as np
+import pytest
+
+from conftest import assert_close_ref, compare_results_f16, f16_normal
+
+pytestmark = pytest.mark.gpu
+
+
+def random_pm1(rng, shape, scale=0.01):
+    return ((rng.random(shape, np.float32) * 2 - 1).astype(np.float16).astype(np.float32) * scale).astype(np.float16)
+
+
+# ---- the reference's hgemm tests, run against the GPU library (host pointers = drop-in mode)
+
+def test_ref_basic_sequential(ctx, oracle):
+    a = (np.arange(12, dtype=np.float32) * 0.01).astype(np.float16).reshape(4, 3)
+    b = (np.arange(12, dtype=np.float32) * 0.01).astype(np.float16).reshape(3, 4)
+    compare_results_f16(oracle.naive_matmul_f16(a, b), ctx.hgemm_nn(a, b, 4, 4, 3), 0.005)
+
+
+def test_ref_large(ctx, oracle):
+    rng = np.random.default_rng(42)
+    a, b = random_pm1(rng, (2000, 180)), random_pm1(rng, (180, 1600))
+    compare_results_f16(oracle.naive_matmul_f16(a, b), ctx.hgemm_nn(a, b, 2000, 1600, 180), 0.05)
+
+
+@pytest.mark.parametrize("m,k,n", [(50, 30, 70), (25, 80, 35), (100, 20, 100)])
+def test_ref_non_square(ctx, oracle, m, k, n):
+    rng = np.random.default_rng(m)
+    a, b = random_pm1(rng, (m, k)), random_pm1(rng, (k, n))
+    compare_results_f16(oracle.naive_matmul_f16(a, b), ctx.hgemm_nn(a, b, m, n, k), 0.05)
+
+
+def test_ref_identity(ctx):
+    a = random_pm1(np.random.default_rng(1), (32, 32))
+    compare_results_f16(a, ctx.hgemm_nn(a, np.eye(32, dtype=np.float16), 32, 32, 32), 0.005)
+
+
+def test_ref_error_case(ctx, pkg):
+    with pytest.raises(pkg.MdError) as e:
+        ctx.check_matmul_shapes((3, 4), (5, 6), False)
+    assert e.value.zig_error == "error.IncompatibleTensorShapes"
+
+
+@pytest.mark.parametrize("size", [158, 159, 160, 161, 162])
+def test_ref_tile_boundaries(ctx, oracle, size):
+    rng = np.random.default_rng(size)
+    a, b = random_pm1(rng, (size, size)), random_pm1(rng, (size, size))
+    compare_results_f16(oracle.naive_matmul_f16(a, b), ctx.hgemm_nn(a, b, size, size, size), 0.05)
+
+
+@pytest.mark.parametrize("val", [1e-2, 1.0])
+def test_ref_constant_matrices(ctx, oracle, val):
+    a = np.full((32, 32), val, np.float16)
+    compare_results_f16(oracle.naive_matmul_f16(a, a), ctx.hgemm_nn(a, a, 32, 32, 32), 0.01)
+
+
+# ---- oracle parity, every kernel selected explicitly (mode 1 = SIMT, 2 = tcgen05, 0 = auto)
+
+EDGE = [(1, 8, 8), (7, 16, 24), (8, 64, 8), (9, 72, 40), (127, 128, 136), (128, 64, 128), (129, 200, 264),
+        (167, 168, 168), (300, 1152, 520), (64, 592, 1152)]
+
+
+@pytest.mark.parametrize("layout", ["nn", "nt"])
+@pytest.mark.parametrize("m,k,n", EDGE)
+@pytest.mark.parametrize("mode", [1, 2])
+def test_edge_shapes(ctx, oracle, mode, m, k, n, layout):
+    rng = np.random.default_rng(m * 7 + k * 3 + n)
+    a = f16_normal(rng, (m, k))
+    w_kn = f16_normal(rng, (k, n), 0.05)
+    ctx.set_gemm_mode(mode)
+    try:
+        if layout == "nn":
+            got, ref = ctx.hgemm_nn(a, w_kn, m, n, k), oracle.hgemm_nn(a, w_kn)
+        else:
+            w_nk = np.ascontiguousarray(w_kn.T)
+            got, ref = ctx.hgemm_nt(a, w_nk, m, n, k), oracle.hgemm_nt(a, w_nk)
+    finally:
+        ctx.set_gemm_mode(0)
+    assert_close_ref(got, ref, f"mode{mode} {layout} {m}x{n}x{k}")
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 3, 5), (5, 30, 7), (33, 588, 1152), (3, 7, 9)])
+def test_unaligned_shapes_take_the_simt_kernel(ctx, oracle, m, k, n):
+    rng = np.random.default_rng(k)
+    a, w = f16_normal(rng, (m, k)), f16_normal(rng, (k, n), 0.05)
+    assert_close_ref(ctx.hgemm_nn(a, w, m, n, k), oracle.hgemm_nn(a, w), "nn")
+    wt = np.ascontiguousarray(w.T)
+    assert_close_ref(ctx.hgemm_nt(a, wt, m, n, k), oracle.hgemm_nt(a, wt), "nt")
+
+
+def test_empty_dims(ctx):
+    a = np.zeros((4, 0), np.float16)
+    b = np.zeros((0, 8), np.float16)
+    out = ctx.hgemm_nn(a, b, 4, 8, 0)
+    assert (out == 0).all()
+
+
+def test_config1_prefill_fc1(ctx, oracle):
+    """BASELINE config 1: A[64,2048] ~N(0,1), W[2048,8192] ~N(0,0.02), both layouts."""
+    rng = np.random.default_rng(1000)
+    a, w = f16_normal(rng, (64, 2048)), f16_normal(rng, (2048, 8192), 0.02)
+    ref = oracle.hgemm_nn(a, w)
+    assert_close_ref(ctx.hgemm_nn(a, w, 64, 8192, 2048), ref, "config1 nn")
+    wt = np.ascontiguousarray(w.T)
+    assert_close_ref(ctx.hgemm_nt(a, wt, 64, 8192, 2048), oracle.hgemm_nt(a, wt), "config1 nt")
+
+
+GEMV_SHAPES = [(2048, 6144), (2048, 2048), (2048, 8192), (8192, 2048), (2048, 51200)]
+
+
+@pytest.mark.parametrize("k,n", GEMV_SHAPES)
+@pytest.mark.parametrize("m", [1, 2, 4, 8])
+def test_config2_decode_gemv(ctx, oracle, m, k, n):
+    """BASELINE config 2: M in {1,2,4,8} over the Phi-1.5 layer shapes, weights resident."""
+    rng = np.random.default_rng(2000 + m)
+    w = f16_normal(rng, (n, k), 0.02)
+    a = f16_normal(rng, (m, k))
+    wd = ctx.upload(w)
+    got = ctx.hgemm_nt(a, wd, m, n, k, out=np.empty((m, n), np.float16))
+    wd.free()
+    assert_close_ref(got, oracle.hgemm_nt(a, w), f"gemv M={m} {k}->{n}")
+
+
+@pytest.mark.parametrize("m,k,n", [(3, 2048, 100), (8, 40, 17), (1, 8, 1), (5, 8200, 33)])
+def test_gemv_edges(ctx, oracle, m, k, n):
+    rng = np.random.default_rng(n)
+    a, w = f16_normal(rng, (m, k)), f16_normal(rng, (n, k), 0.05)
+    assert_close_ref(ctx.hgemm_nt(a, w, m, n, k), oracle.hgemm_nt(a, w), "gemv edge")
+
+
+@pytest.mark.parametrize("m,k,n,layout", [(729, 1152, 3456, "nn"), (729, 4304, 1152, "nn"), (729, 1152, 4304, "nn"),
+                                          (729, 2304, 8192, "nn"), (761, 2048, 6144, "nt"), (761, 8192, 2048, "nt")])
+def test_model_gemm_shapes(ctx, oracle, m, k, n, layout):
+    rng = np.random.default_rng(3000 + n)
+    a = f16_normal(rng, (m, k))
+    if layout == "nn":
+        w = f16_normal(rng, (k, n), 0.02)
+        got, ref = ctx.hgemm_nn(a, w, m, n, k), oracle.hgemm_nn(a, w)
+    else:
+        w = f16_normal(rng, (n, k), 0.02)
+        got, ref = ctx.hgemm_nt(a, w, m, n, k), oracle.hgemm_nt(a, w)
+    assert_close_ref(got, ref, f"{layout} {m}x{n}x{k}")
+
+
+@pytest.mark.parametrize("layout", [0, 1])
+@pytest.mark.parametrize("m,k,n", [(4, 2048, 8192), (200, 1152, 4304), (64, 30, 70)])
+def test_fused_epilogue_keeps_reference_rounding(ctx, oracle, m, k, n, layout):
+    """bias -> GELU -> residual fused into the GEMM equals the reference's op sequence
+    (hgemm, broadcast_add_simd, gelu, add) within the parity bar."""
+    rng = np.random.default_rng(m + n)
+    a = f16_normal(rng, (m, k))
+    w_kn = f16_normal(rng, (k, n), 0.05)
+    bias, res = f16_normal(rng, (n,), 0.5), f16_normal(rng, (m, n))
+    w = w_kn if layout == 0 else np.ascontiguousarray(w_kn.T)
+    ref = oracle.hgemm_nn(a, w_kn) if layout == 0 else oracle.hgemm_nt(a, w)
+    ref = oracle.add(oracle.gelu(oracle.bias_add(ref, bias)), res)
+    da, dw, db, dr = ctx.upload(a), ctx.upload(w), ctx.upload(bias), ctx.upload(res)
+    out = ctx.alloc((m, n))
+    ctx.hgemm_fused(da, dw, out, m, n, k, layout, bias=db, gelu=True, residual=dr)
+    ctx.sync()
+    assert_close_ref(out.numpy(), ref, "fused epilogue")
+    for b in (da, dw, db, dr, out):
+        b.free()
+
+
+def test_linearity_at_full_size(ctx):
+    """Size-independent property at the lm_head size: (a1 + a2) W == a1 W + a2 W up to rounding,
+    and a one-hot activation selects a weight column exactly."""
+    rng = np.random.default_rng(5)
+    k, n = 2048, 51200
+    w = f16_normal(rng, (n, k), 0.02)
+    wd = ctx.upload(w)
+    onehot = np.zeros((1, k), np.float16)
+    onehot[0, 77] = 1.0
+    got = ctx.hgemm_nt(onehot, wd, 1, n, k, out=np.empty((1, n), np.float16))
+    np.testing.assert_array_equal(got[0], w[:, 77])
+    a1, a2 = f16_normal(rng, (1, k), 0.5), f16_normal(rng, (1, k), 0.5)
+    s = (a1.astype(np.float32) + a2.astype(np.float32)).astype(np.float16)
+    y1 = ctx.hgemm_nt(a1, wd, 1, n, k, out=np.empty((1, n), np.float16)).astype(np.float32)
+    y2 = ctx.hgemm_nt(a2, wd, 1, n, k, out=np.empty((1, n), np.float16)).astype(np.float32)
+    ys = ctx.hgemm_nt(s, wd, 1, n, k, out=np.empty((1, n), np.float16)).astype(np.float32)
+    assert np.abs(ys - (y1 + y2)).max() <= 1e-2 * np.abs(ys).max() + 2e-3
+    wd.free()
