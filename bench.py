@@ -1,0 +1,391 @@
+#!/usr/bin/env python
+"""Benchmark of the decode GEMV hot path (BASELINE config 2) on N B200 GPUs of one node.
+
+Workload ("step"): one pass over the decode GEMV sweep — M in {1,2,4,8} activation rows
+times the five Phi-1.5 layer shapes (K->N: 2048->6144, 2048->2048, 2048->8192, 8192->2048,
+2048->51200), f16 weights ~N(0,0.02) resident in HBM, activations ~N(0,1): 20 launches of
+the GEMV kernel, replayed as one CUDA graph.  The metric is achieved HBM GB/s counted with
+the reference's own byte formula 2*(M*K + K*N + M*N) (hgemm_trans.zig:580-593).  The sweep
+touches 1.24 GB per pass, ten times the L2, so no flush is needed between iterations.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+N > 1 is launched by torch.distributed.run; every rank runs the sweep on its own GPU
+(independent requests are partitioned across GPUs, no collective on the data path), the
+timed region is bracketed by barriers, the time is the max over ranks.
+
+--impl reference times the CPU oracle (the C++ restatement of the reference's AVX2 path;
+the Zig reference itself cannot be built on this box) on the host cores for the same sweep.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES = [(2048, 6144), (2048, 2048), (2048, 8192), (8192, 2048), (2048, 51200)]  # (K, N)
+MS = [1, 2, 4, 8]
+METRIC = "decode_gemv_hbm_gbs"
+UNIT = "GB/s"
+
+
+def algo_bytes(m, k, n):
+    return 2 * (m * k + k * n + m * n)
+
+
+STEP_BYTES = sum(algo_bytes(m, k, n) for m in MS for k, n in SHAPES)
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_inputs(seed=2000):
+    """Seeded synthetic inputs of config 2 (weights ~N(0,0.02), activations ~N(0,1))."""
+    rng = np.random.default_rng(seed)
+    ws = [(rng.standard_normal((n, k), dtype=np.float32) * 0.02).astype(np.float16) for k, n in SHAPES]
+    xs = {(m, i): rng.standard_normal((m, k), dtype=np.float32).astype(np.float16)
+          for m in MS for i, (k, n) in enumerate(SHAPES)}
+    return ws, xs
+
+
+def cpu_sweep(oracle, ws, xs):
+    for m in MS:
+        for i in range(len(SHAPES)):
+            oracle.hgemm_nt(xs[(m, i)], ws[i])
+
+
+def run_reference(args, rank):
+    """The reference arm: the CPU oracle on the host cores, all threads, same sweep."""
+    if rank != 0:
+        return
+    from oracle import oracle
+    oracle.build()
+    ws, xs = make_inputs()
+    for _ in range(max(args.warmup, 1)):
+        cpu_sweep(oracle, ws, xs)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_sweep(oracle, ws, xs)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = STEP_BYTES / dt / 1e9
+    cores = oracle.get_threads()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "decode GEMV sweep: M in {1,2,4,8} x Phi-1.5 layer shapes (BASELINE config 2)",
+                   "bytes_per_step": STEP_BYTES},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": "the full 20-GEMV sweep per step (C++ restatement of hgemm_trans.zig; the Zig "
+                                   "reference cannot be built here)"},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the per-shape and GEMM side measurements")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    pkg = entry.load_package()
+    ctx = pkg.Context(local_rank)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    ctx.set_stream(stream.cuda_stream)
+
+    ws_h, xs_h = make_inputs()
+    ws = [torch.from_numpy(w).cuda() for w in ws_h]
+    xs = {key: torch.from_numpy(x).cuda() for key, x in xs_h.items()}
+    ys = {(m, i): torch.empty((m, n), dtype=torch.float16, device="cuda") for m in MS for i, (k, n) in enumerate(SHAPES)}
+
+    def sweep():
+        for m in MS:
+            for i, (k, n) in enumerate(SHAPES):
+                ctx.hgemm_nt(xs[(m, i)].data_ptr(), ws[i].data_ptr(), m, n, k, out=ys[(m, i)].data_ptr())
+
+    # one eager pass (sets up everything), a parity spot check against torch f32, then capture
+    sweep()
+    ctx.sync()
+    for key in [(1, 0), (8, 4)]:
+        ref = xs[key].float() @ ws[key[1]].float().T
+        err = (ys[key].float() - ref).abs().max().item()
+        assert err <= 1e-2 * ref.abs().max().item(), f"parity check failed for {key}: {err}"
+    n0 = ctx.launch_count()
+    ctx.graph_begin()
+    sweep()
+    graph = ctx.graph_end()
+    launches_per_step = ctx.launch_count() - n0
+
+    for _ in range(max(args.warmup, 3)):
+        ctx.graph_launch(graph)
+    ctx.sync()
+
+    sampler = ClockSampler(local_rank)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    barrier()
+    sampler.start()
+    # keep the sampler fed: very short runs finish before nvidia-smi prints its first line
+    ev0.record(stream)
+    for _ in range(args.steps):
+        ctx.graph_launch(graph)
+    ev1.record(stream)
+    torch.cuda.synchronize()
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    if ms_total < 400:  # give nvidia-smi a few samples under the same load (not timed)
+        t_end = time.time() + 0.6
+        while time.time() < t_end:
+            ctx.graph_launch(graph)
+            ctx.sync()
+    clocks = sampler.stop()
+    t = torch.tensor([ms_total], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = t.item() / args.steps
+    value = world * STEP_BYTES / (ms_step * 1e-3) / 1e9
+
+    # ---- end to end through the C ABI with HOST buffers: H2D of the activations and D2H of the
+    # result inside every call (weights registered once), as the Zig host would call it
+    pin_x = {key: torch.from_numpy(x).pin_memory() for key, x in xs_h.items()}
+    pin_y = {key: torch.empty(tuple(ys[key].shape), dtype=torch.float16).pin_memory() for key in ys}
+
+    def e2e_sweep():
+        for m in MS:
+            for i, (k, n) in enumerate(SHAPES):
+                st = ctx.lib.md_hgemm_nt(ctx.h, pin_x[(m, i)].data_ptr(), ws[i].data_ptr(), pin_y[(m, i)].data_ptr(),
+                                         m, n, k)
+                if st != 0:
+                    raise RuntimeError(ctx.lib.md_last_error(ctx.h).decode())
+
+    import ctypes as C
+    ctx.lib.md_hgemm_nt.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t]
+    for _ in range(3):
+        e2e_sweep()
+    e2e_steps = max(5, min(args.steps, 20))
+    torch.cuda.synchronize()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_sweep()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    barrier()
+    t = torch.tensor([dt], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_val = world * STEP_BYTES / (t.item() / e2e_steps) / 1e9
+    h2d = sum(m * k * 2 for m in MS for k, n in SHAPES)
+    d2h = sum(m * n * 2 for m in MS for k, n in SHAPES)
+    err = (pin_y[(8, 4)].float() - (xs[(8, 4)].float() @ ws[4].float().T).cpu()).abs().max().item()
+    assert err < 0.2, f"e2e parity check failed: {err}"
+
+    if rank != 0:
+        ctx.sync()
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    hbm_peak, tensor_peak, peak_kind = measured_peaks()
+    achieved = (STEP_BYTES / launches_per_step) / (ms_step * 1e-3 / launches_per_step) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic",
+        "config": {"workload": "decode GEMV sweep: M in {1,2,4,8} x Phi-1.5 layer shapes (BASELINE config 2)",
+                   "bytes_per_step": STEP_BYTES, "launches_per_step": launches_per_step,
+                   "l2": "inputs larger than L2 (1.24 GB per step, every weight reused only after 310 MB of other traffic)",
+                   "replay": "one CUDA graph per step", "parallelism": f"replicas x{world}"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                     "traffic": TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": peak_kind, "kernel": "gemv_nt_mma_kernel",
+                     "frac_of_nominal_8tbs": achieved / 8000.0},
+        "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "note": "md_hgemm_nt with pinned HOST activations/outputs per call, weights registered once"},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks,
+    }
+
+    if not args.no_extras and world == 1:
+        line["extras"] = extras(ctx, torch, stream, tensor_peak, hbm_peak)
+
+    # ---- CPU baseline: the oracle on this box's host cores, bounded sample
+    from oracle import oracle
+    oracle.build()
+    cpu_sweep(oracle, ws_h, xs_h)
+    best = None
+    t_begin = time.perf_counter()
+    for _ in range(5):
+        t0 = time.perf_counter()
+        cpu_sweep(oracle, ws_h, xs_h)
+        d = time.perf_counter() - t0
+        best = d if best is None else min(best, d)
+        if time.perf_counter() - t_begin > 20:
+            break
+    line["cpu_baseline"] = {"value": STEP_BYTES / best / 1e9, "unit": UNIT, "cores": oracle.get_threads(), "kind": "port",
+                            "sample": "best of up to 5 full sweeps (1.24 GB each) of the C++ restatement of "
+                                      "hgemm_trans.zig on the host cores"}
+    print(json.dumps(line), flush=True)
+    ctx.graph_destroy(graph)
+    ctx.sync()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from an ncu
+# capture (profiles/); None until a capture exists.
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def extras(ctx, torch, stream, tensor_peak, hbm_peak):
+    """Side measurements quoted in DESIGN.md: per-shape GEMV GB/s (rotating weight copies so every
+    launch streams from HBM), config 1 (64x2048 . 2048x8192) and large GEMMs on the tcgen05 kernel."""
+    out = {"gemv": [], "gemm": []}
+
+    def time_graph(fn, reps):
+        fn()
+        ctx.sync()
+        ctx.graph_begin()
+        fn()
+        g = ctx.graph_end()
+        for _ in range(3):
+            ctx.graph_launch(g)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            ctx.graph_launch(g)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ctx.graph_destroy(g)
+        return e0.elapsed_time(e1) / reps
+
+    for m in (1, 8):
+        for k, n in SHAPES:
+            copies = max(3, (300 << 20) // (n * k * 2) + 1)
+            w = (torch.randn(copies, n, k, device="cuda") * 0.02).half()
+            x = torch.randn(m, k, device="cuda").half()
+            y = torch.empty(m, n, device="cuda", dtype=torch.float16)
+
+            def fn():
+                for c in range(copies):
+                    ctx.hgemm_nt(x.data_ptr(), w[c].data_ptr(), m, n, k, out=y.data_ptr())
+            us = time_graph(fn, 5) / copies * 1e3
+            gbs = algo_bytes(m, k, n) / us / 1e3
+            out["gemv"].append({"M": m, "K": k, "N": n, "us": round(us, 2), "GB/s": round(gbs, 1),
+                                "frac_of_measured_hbm": round(gbs / hbm_peak, 3)})
+            del w
+    for (m, k, n, layout, copies) in [(64, 2048, 8192, "nn", 10), (64, 2048, 8192, "nt", 10),
+                                      (761, 2048, 8192, "nt", 10), (9477, 1152, 4304, "nn", 4),
+                                      (729, 1152, 3456, "nn", 16), (8192, 8192, 8192, "nt", 1)]:
+        shape = (copies, n, k) if layout == "nt" else (copies, k, n)
+        w = (torch.randn(*shape, device="cuda") * 0.02).half()
+        x = torch.randn(m, k, device="cuda").half()
+        y = torch.empty(m, n, device="cuda", dtype=torch.float16)
+        call = ctx.hgemm_nt if layout == "nt" else ctx.hgemm_nn
+
+        def fn():
+            for c in range(copies):
+                call(x.data_ptr(), w[c].data_ptr(), m, n, k, out=y.data_ptr())
+        us = time_graph(fn, 5) / copies * 1e3
+        tf = 2.0 * m * n * k / us / 1e6
+        out["gemm"].append({"M": m, "K": k, "N": n, "layout": layout, "us": round(us, 2), "TFLOP/s": round(tf, 1),
+                            "GB/s": round(algo_bytes(m, k, n) / us / 1e3, 1),
+                            "frac_of_measured_tensor": round(tf / tensor_peak, 3)})
+        del w
+    return out
+
+
+if __name__ == "__main__":
+    main()

@@ -79,6 +79,23 @@ int md_launch_count(const md_ctx* ctx, uint64_t* count_out);
  * (MD_ERR_UNSUPPORTED when the shape cannot take it).  For tests and profiling. */
 int md_set_gemm_mode(md_ctx* ctx, int mode);
 
+/* Tuning knobs for tests and profiling; unknown keys return MD_ERR_INVALID_ARG.
+ *   "gemv_variant"  0 = automatic, 1..6 = a fixed (warps, unroll) configuration of the GEMV kernel
+ *   "tc_block_n"    0 = automatic, 64 / 128 / 256 = fixed tile width of the tcgen05 GEMM */
+int md_set_option(md_ctx* ctx, const char* key, long value);
+
+/* ---- CUDA graphs -------------------------------------------------------------------
+ * A decode step is ~170 small kernels; replaying them as one graph removes the launch
+ * overhead.  Between md_graph_begin and md_graph_end every entry point called with DEVICE
+ * pointers only is recorded instead of executed (host-pointer calls are rejected with
+ * MD_ERR_UNSUPPORTED, they would need a synchronous copy).  Run the same calls once before
+ * capturing so that scratch memory and kernel attributes are already set up. */
+typedef struct md_graph md_graph;
+int md_graph_begin(md_ctx* ctx);
+int md_graph_end(md_ctx* ctx, md_graph** out);
+int md_graph_launch(md_ctx* ctx, md_graph* graph);
+int md_graph_destroy(md_ctx* ctx, md_graph* graph);
+
 /* ---- matmul -------------------------------------------------------------------- */
 
 /* Replaces hgemm.matmul(a, b, allocator) — src/core/hgemm.zig:362-426.

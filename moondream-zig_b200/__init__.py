@@ -135,6 +135,23 @@ class Context:
     def set_gemm_mode(self, mode: int):
         self._check(self.lib.md_set_gemm_mode(self.h, C.c_int(mode)))
 
+    def set_option(self, key: str, value: int):
+        self._check(self.lib.md_set_option(self.h, C.c_char_p(key.encode()), C.c_long(int(value))))
+
+    def graph_begin(self):
+        self._check(self.lib.md_graph_begin(self.h))
+
+    def graph_end(self):
+        g = C.c_void_p()
+        self._check(self.lib.md_graph_end(self.h, C.byref(g)))
+        return g
+
+    def graph_launch(self, g):
+        self._check(self.lib.md_graph_launch(self.h, g))
+
+    def graph_destroy(self, g):
+        self._check(self.lib.md_graph_destroy(self.h, g))
+
     def launch_count(self) -> int:
         n = C.c_uint64()
         self._check(self.lib.md_launch_count(self.h, C.byref(n)))

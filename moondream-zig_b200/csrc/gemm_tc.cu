@@ -418,6 +418,7 @@ int md_launch_gemm_tc(md_ctx* ctx, const __half* a, const __half* b, __half* c, 
     int bn = 256;
     if (tiles(256) < (size_t)ctx->sm_count) bn = 128;
     if (bn == 128 && tiles(128) < (size_t)ctx->sm_count) bn = 64;
+    if (ctx->tc_block_n) bn = ctx->tc_block_n;
     const bool mn = (b_layout == 0);
     if (mn) {
         if (bn == 256) return launch<256, true>(ctx, a, b, c, M, N, K, ep);

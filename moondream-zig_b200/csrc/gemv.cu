@@ -132,13 +132,31 @@ int md_launch_gemv_nt(md_ctx* ctx, const __half* a, const __half* bt, __half* c,
     if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(bt)) & 15)
         return md_fail(ctx, MD_ERR_UNSUPPORTED, "gemv_nt needs 16-byte aligned operands");
     const unsigned grid = (unsigned)((N + ROWS_PER_CTA - 1) / ROWS_PER_CTA);
-    // Few weight rows (N <= 4096): more warps per CTA so enough bytes are in flight;
-    // many rows: fewer warps, deeper unroll.
-    if (K >= 4096) {
-        gemv_nt_mma_kernel<8, 4><<<grid, 8 * 32, 0, ctx->stream>>>(a, bt, c, (int)M, (int)N, (int)K, ep);
-    } else {
-        gemv_nt_mma_kernel<4, 8><<<grid, 4 * 32, 0, ctx->stream>>>(a, bt, c, (int)M, (int)N, (int)K, ep);
+    // (warps, unroll) variants; 0 = automatic choice by K.
+    int variant = ctx->gemv_variant;
+    if (variant == 0) {
+        // Measured on B200 with weights streamed from HBM: many CTAs (vocabulary-sized N) want
+        // small CTAs; few CTAs (N <= 2048) or long rows (K >= 4096) want many warps per CTA so
+        // that the whole matrix is in flight at once.
+        if (N >= 16384) variant = 4;
+        else if (K >= 4096 || N <= 2048) variant = 6;
+        else variant = 2;
     }
+#define MD_GEMV_CASE(id, W, U)                                                                          \
+    case id:                                                                                            \
+        gemv_nt_mma_kernel<W, U><<<grid, W * 32, 0, ctx->stream>>>(a, bt, c, (int)M, (int)N, (int)K, ep); \
+        break;
+    switch (variant) {
+        MD_GEMV_CASE(1, 4, 8)
+        MD_GEMV_CASE(2, 8, 4)
+        MD_GEMV_CASE(3, 8, 8)
+        MD_GEMV_CASE(4, 4, 4)
+        MD_GEMV_CASE(5, 2, 8)
+        MD_GEMV_CASE(6, 16, 2)
+        default:
+            return md_fail(ctx, MD_ERR_INVALID_ARG, "unknown gemv variant %d", variant);
+    }
+#undef MD_GEMV_CASE
     MD_LAUNCH_CHECK(ctx, "gemv_nt_mma_kernel");
     return MD_OK;
 }

@@ -55,6 +55,8 @@ int md_stage_in(md_ctx* ctx, int slot, const void* user, size_t bytes, md_arg* o
         out->staged = false;
         return MD_OK;
     }
+    if (ctx->capturing)
+        return md_fail(ctx, MD_ERR_UNSUPPORTED, "host pointers cannot be used while a graph is being captured");
     MD_TRY(stage_reserve(ctx, slot, bytes ? bytes : 1, &out->dev));
     out->staged = true;
     if (bytes) MD_CUDA(ctx, cudaMemcpyAsync(out->dev, user, bytes, cudaMemcpyHostToDevice, ctx->stream));
@@ -69,6 +71,8 @@ int md_stage_out(md_ctx* ctx, int slot, void* user, size_t bytes, md_arg* out) {
         out->staged = false;
         return MD_OK;
     }
+    if (ctx->capturing)
+        return md_fail(ctx, MD_ERR_UNSUPPORTED, "host pointers cannot be used while a graph is being captured");
     MD_TRY(stage_reserve(ctx, slot, bytes ? bytes : 1, &out->dev));
     out->staged = true;
     return MD_OK;
@@ -97,6 +101,9 @@ int md_finish_out(md_ctx* ctx, md_arg* out) {
 
 int md_scratch(md_ctx* ctx, size_t bytes, void** out) {
     if (ctx->scratch_cap < bytes) {
+        if (ctx->capturing)
+            return md_fail(ctx, MD_ERR_UNSUPPORTED,
+                           "scratch memory would have to grow during graph capture; run the call once before capturing");
         if (ctx->scratch) {
             MD_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
             MD_CUDA(ctx, cudaFree(ctx->scratch));
@@ -153,6 +160,8 @@ int md_init(md_ctx** out, int device) {
     if (cudaMallocHost(&ctx->flags_host, sizeof(md_devflags)) != cudaSuccess) return bail("cudaMallocHost");
     if (cudaMalloc(&ctx->counters, 1024) != cudaSuccess) return bail("cudaMalloc counters");
     if (cudaMemset(ctx->counters, 0, 1024) != cudaSuccess) return bail("cudaMemset counters");
+    ctx->scratch_cap = (size_t)16 << 20;
+    if (cudaMalloc(&ctx->scratch, ctx->scratch_cap) != cudaSuccess) return bail("cudaMalloc scratch");
     *out = ctx;
     return MD_OK;
 }
@@ -226,6 +235,60 @@ int md_memcpy_d2h(md_ctx* ctx, void* host, const void* dev, size_t bytes) {
 int md_launch_count(const md_ctx* ctx, uint64_t* count_out) {
     if (!ctx || !count_out) return MD_ERR_INVALID_ARG;
     *count_out = ctx->launches;
+    return MD_OK;
+}
+
+int md_set_option(md_ctx* ctx, const char* key, long value) {
+    MD_NEED_CTX(ctx);
+    MD_NEED(ctx, key, "md_set_option: null key");
+    if (!strcmp(key, "gemv_variant")) { ctx->gemv_variant = (int)value; return MD_OK; }
+    if (!strcmp(key, "tc_block_n")) {
+        MD_NEED(ctx, value == 0 || value == 64 || value == 128 || value == 256, "tc_block_n must be 0, 64, 128 or 256");
+        ctx->tc_block_n = (int)value;
+        return MD_OK;
+    }
+    return md_fail(ctx, MD_ERR_INVALID_ARG, "md_set_option: unknown key '%s'", key);
+}
+
+int md_graph_begin(md_ctx* ctx) {
+    MD_NEED_CTX(ctx);
+    MD_NEED(ctx, !ctx->capturing, "md_graph_begin: a capture is already in progress");
+    MD_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
+    ctx->capturing = true;
+    return MD_OK;
+}
+
+int md_graph_end(md_ctx* ctx, md_graph** out) {
+    MD_NEED_CTX(ctx);
+    MD_NEED(ctx, out, "md_graph_end: null output");
+    MD_NEED(ctx, ctx->capturing, "md_graph_end: no capture in progress");
+    ctx->capturing = false;
+    md_graph* g = new md_graph();
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &g->graph);
+    if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
+    if (e != cudaSuccess) {
+        if (g->graph) cudaGraphDestroy(g->graph);
+        delete g;
+        return md_fail(ctx, MD_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+    }
+    *out = g;
+    return MD_OK;
+}
+
+int md_graph_launch(md_ctx* ctx, md_graph* graph) {
+    MD_NEED_CTX(ctx);
+    MD_NEED(ctx, graph && graph->exec, "md_graph_launch: null graph");
+    MD_CUDA(ctx, cudaGraphLaunch(graph->exec, ctx->stream));
+    return MD_OK;
+}
+
+int md_graph_destroy(md_ctx* ctx, md_graph* graph) {
+    MD_NEED_CTX(ctx);
+    if (graph) {
+        if (graph->exec) cudaGraphExecDestroy(graph->exec);
+        if (graph->graph) cudaGraphDestroy(graph->graph);
+        delete graph;
+    }
     return MD_OK;
 }
 

@@ -21,6 +21,11 @@ struct md_devflags {
     unsigned int where;  // site id of the first wait that gave up
 };
 
+struct md_graph {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+};
+
 struct md_ctx {
     int device = 0;
     int sm_count = 0;
@@ -41,7 +46,10 @@ struct md_ctx {
     unsigned int* counters = nullptr;
     // cuTensorMapEncodeTiled resolved through the runtime (no link against libcuda)
     void* encode_tiled = nullptr;
-    uint32_t tc_configured = 0;  // kernels whose dynamic shared memory limit has been raised
+    uint32_t tc_configured = 0;
+    bool capturing = false;  // between md_graph_begin and md_graph_end
+    int gemv_variant = 0;    // md_set_option("gemv_variant")
+    int tc_block_n = 0;      // md_set_option("tc_block_n")  // kernels whose dynamic shared memory limit has been raised
 };
 
 int md_fail(md_ctx* ctx, int status, const char* fmt, ...);
