@@ -324,9 +324,11 @@ def main():
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from an ncu
-# capture (profiles/); None until a capture exists.
-TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of gemv_nt_mma_kernel from the ncu capture summarised in
+# profiles/gemv_nt_mma_kernel__decode_gemv_sweep.md: 280.41 MB measured over the three captured launches
+# (fc1, fc2, lm_head at M = 1) against 276.97 MB of algorithmic bytes, a factor of 1.0124; traffic grows in
+# proportion to the weight bytes, so the average launch of the sweep is scaled by the same factor.
+TRAFFIC_BYTES_PER_LAUNCH = int(round(1.0124 * STEP_BYTES / 20))
 
 
 def extras(ctx, torch, stream, tensor_peak, hbm_peak):
