@@ -142,6 +142,23 @@ int md_sdpa_masked(md_ctx* ctx, const uint16_t* q, const uint16_t* k, const uint
 int md_sdpa_single(md_ctx* ctx, const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint8_t* mask,
                    uint16_t* out, size_t kv_len);
 
+/* md_sdpa_single for callers that must not allocate.  It has no counterpart in the reference: it
+ * exists for hosts that cannot call cudaMalloc once they are running — a serving process that gave
+ * all of HBM to its own arena at start-up, or a latency-critical decode loop that cannot afford the
+ * device-wide synchronisation cudaMalloc/cudaFree imply.  It takes no context and calls no cudaMalloc,
+ * cudaFree or allocating library routine: the split-KV scratch is a 135,424-byte device array built
+ * into the library (held by every GPU that loads it until the process exits).
+ *   - same arithmetic and layouts as md_sdpa_single (32 heads x 64 dims), DEVICE pointers only;
+ *   - kv_len > 2048 (the scratch's maximum) -> MD_ERR_SEQUENCE_TOO_LONG; a message is written to
+ *     err[0..err_cap) when err is not NULL;
+ *   - enqueues on cuda_stream (NULL = the default stream) and returns without waiting;
+ *   - the first call on a device looks up the scratch's device address; make that call with the
+ *     device current and before any stream capture begins;
+ *   - every call on a device shares the one scratch array: calls that overlap on the GPU race,
+ *     so keep them on one stream or order them with events. */
+int md_sdpa_single_noalloc(const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint8_t* mask,
+                           uint16_t* out, size_t kv_len, void* cuda_stream, char* err, size_t err_cap);
+
 /* The decode-step attention the GPU path uses instead of the sequence
  * rope.applyRotEmb x2 -> LayerCache.updateCache -> getActiveCache -> createAttentionMask ->
  * singleMaskedSDPA (text_model.zig:228-290): reads q,k,v of the new token from one row of the

@@ -605,3 +605,114 @@ int md_launch_rope_cache_write(md_ctx* ctx, const __half* qkv, __half* q_rot, __
     MD_LAUNCH_CHECK(ctx, "rope_cache_write_kernel");
     return MD_OK;
 }
+
+// ------------------------------------------------------------------------------------------
+// md_sdpa_single_noalloc: the decode attention above for callers that must not allocate.
+//
+// Some hosts cannot call cudaMalloc once they are running: a serving process that handed all of
+// HBM to its own arena at start-up (weights + KV caches for as many requests as fit) gets
+// cudaErrorMemoryAllocation from any later cudaMalloc, and a latency-critical decode loop cannot
+// afford the implicit device-wide synchronisation of cudaMalloc/cudaFree.  The regular entry point
+// needs a context (whose creation allocates a stream, flags and scratch).  This one needs nothing:
+// the split-KV partials and the per-head arrival counters live in the file-scope device array
+// below, which every GPU that loads this library holds from module load until process exit.
+//
+// Limits and rules:
+//   * fixed geometry of the reference's decode attention: 32 heads x 64 dims, kv_len <= 2048,
+//     hence at most 16 splits; the array is 256 B of counters + 32*16*66 floats = 135,424 bytes.
+//   * device pointers only (a host pointer cannot be staged without allocating).
+//   * the first call on a device resolves the array's device address (cudaGetSymbolAddress with that
+//     device current).  That first call is set-up work: make it before any stream capture begins.
+//   * all calls on a device share the one array, which keeps the previous call's contents.  The
+//     counters are cleared on the stream before every launch; the partials need no clearing (every
+//     slot that is read was written by the same launch).  Two calls that overlap on the GPU (different
+//     streams, no dependency between them) race on the array: serialise them.
+namespace {
+
+constexpr size_t NOALLOC_MAX_KV = 2048;
+constexpr size_t NOALLOC_COUNTER_BYTES = 256;
+constexpr size_t NOALLOC_PARTIAL_BYTES = 32 * (NOALLOC_MAX_KV / DEC_KEYS) * (DEC_D + 2) * sizeof(float);
+constexpr size_t NOALLOC_BYTES = NOALLOC_COUNTER_BYTES + NOALLOC_PARTIAL_BYTES;
+constexpr int NOALLOC_MAX_DEVICES = 64;
+
+static __device__ __align__(256) unsigned char md_noalloc_scratch[NOALLOC_BYTES];
+
+// In host code the name md_noalloc_scratch is only a handle for the runtime, not an address a
+// kernel can use; the usable device address is looked up once per device and kept here.
+static void* g_noalloc_addr[NOALLOC_MAX_DEVICES] = {};
+
+static int noalloc_fail(int status, char* err, size_t cap, const char* fmt, ...) {
+    if (err && cap) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(err, cap, fmt, ap);
+        va_end(ap);
+    }
+    return status;
+}
+
+}  // namespace
+
+extern "C" int md_sdpa_single_noalloc(const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint8_t* mask,
+                                      uint16_t* out, size_t kv_len, void* cuda_stream, char* err, size_t err_cap) {
+    if (err && err_cap) err[0] = '\0';
+    if (!q || !k || !v || !mask || !out)
+        return noalloc_fail(MD_ERR_INVALID_ARG, err, err_cap, "md_sdpa_single_noalloc: null tensor pointer");
+    if (kv_len == 0)
+        return noalloc_fail(MD_ERR_INVALID_ARG, err, err_cap, "md_sdpa_single_noalloc: kv_len is 0");
+    if (kv_len > NOALLOC_MAX_KV)
+        return noalloc_fail(MD_ERR_SEQUENCE_TOO_LONG, err, err_cap,
+                            "md_sdpa_single_noalloc: kv_len %zu exceeds the built-in scratch (max %zu keys)", kv_len,
+                            NOALLOC_MAX_KV);
+    const void* ptrs[5] = {q, k, v, mask, out};
+    for (const void* p : ptrs) {
+        cudaPointerAttributes attr;
+        if (cudaPointerGetAttributes(&attr, p) != cudaSuccess ||
+            (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged)) {
+            cudaGetLastError();
+            return noalloc_fail(MD_ERR_INVALID_ARG, err, err_cap,
+                                "md_sdpa_single_noalloc: every tensor must be device memory (host buffers would "
+                                "need a staging allocation)");
+        }
+    }
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES)
+        return noalloc_fail(MD_ERR_CUDA, err, err_cap, "md_sdpa_single_noalloc: cudaGetDevice: %s",
+                            e != cudaSuccess ? cudaGetErrorString(e) : "device index out of range");
+    if (!g_noalloc_addr[dev]) {
+        void* addr = nullptr;
+        e = cudaGetSymbolAddress(&addr, md_noalloc_scratch);  // the current device's instance of the array
+        if (e != cudaSuccess || !addr)
+            return noalloc_fail(MD_ERR_CUDA, err, err_cap, "md_sdpa_single_noalloc: cudaGetSymbolAddress: %s",
+                                cudaGetErrorString(e));
+        g_noalloc_addr[dev] = addr;
+    }
+    unsigned char* base = static_cast<unsigned char*>(g_noalloc_addr[dev]);
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+    e = cudaMemsetAsync(base, 0, NOALLOC_COUNTER_BYTES, stream);
+    if (e != cudaSuccess)
+        return noalloc_fail(MD_ERR_CUDA, err, err_cap, "md_sdpa_single_noalloc: cudaMemsetAsync: %s",
+                            cudaGetErrorString(e));
+    DecodeParams p{};
+    p.q = reinterpret_cast<const __half*>(q);
+    p.k = reinterpret_cast<const __half*>(k);
+    p.v = reinterpret_cast<const __half*>(v);
+    p.k_w = nullptr;
+    p.v_w = nullptr;
+    p.mask = mask;
+    p.out = reinterpret_cast<__half*>(out);
+    p.k_head_stride = (long long)kv_len * DEC_D;
+    p.n_heads = 32;
+    p.kv_cache_len = (int)kv_len;
+    p.fused = 0;
+    p.splits = (int)((kv_len + DEC_KEYS - 1) / DEC_KEYS);
+    p.counters = reinterpret_cast<unsigned int*>(base);
+    p.partial = reinterpret_cast<float*>(base + NOALLOC_COUNTER_BYTES);
+    sdpa_decode_kernel<<<dim3((unsigned)p.splits, 32u), DEC_WARPS * 32, 0, stream>>>(p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return noalloc_fail(MD_ERR_CUDA, err, err_cap, "md_sdpa_single_noalloc: launch failed: %s",
+                            cudaGetErrorString(e));
+    return MD_OK;
+}
