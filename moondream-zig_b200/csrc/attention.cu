@@ -295,6 +295,7 @@ struct DecodeParams {
     int fused, pos, rot_dim;
     float theta;
     int splits;
+    const int* pos_ptr;     // fused + graph replay: position read from device memory, else null
 };
 
 __device__ __forceinline__ uint4 ldg_nc16(const void* p) {
@@ -332,6 +333,14 @@ sdpa_decode_kernel(DecodeParams p) {
     __shared__ int is_last;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int head = blockIdx.y, split = blockIdx.x;
+    if (p.pos_ptr) {
+        // Position held in device memory (graph replay): the grid is sized for the longest
+        // context, CTAs beyond the splits this position needs leave at once.
+        p.pos = *p.pos_ptr;
+        p.kv_cache_len = p.pos;
+        p.splits = max(1, (p.pos + DEC_KEYS - 1) / DEC_KEYS);
+        if (split >= p.splits) return;
+    }
     const bool last_split = split == p.splits - 1;
     const float scale = 0.125f;  // 1/sqrt(64)
 
@@ -595,6 +604,28 @@ int md_launch_sdpa_decode_fused(md_ctx* ctx, const __half* qkv_row, __half* kc, 
     p.n_heads = (int)n_heads; p.kv_cache_len = (int)pos; p.fused = 1; p.pos = (int)pos; p.rot_dim = (int)rot_dim;
     p.theta = theta;
     return decode_launch(ctx, p);
+}
+
+int md_launch_sdpa_decode_fused_devpos(md_ctx* ctx, const __half* qkv_row, __half* kc, __half* vc, __half* out,
+                                       size_t n_heads, size_t d, size_t max_seq, const int* pos_dev, size_t rot_dim,
+                                       float theta) {
+    if (d != DEC_D || n_heads > 256)
+        return md_fail(ctx, MD_ERR_UNSUPPORTED, "decode attention supports head_dim 64 and <= 256 heads");
+    DecodeParams p{};
+    p.q = qkv_row; p.k = kc; p.v = vc; p.k_w = kc; p.v_w = vc; p.mask = nullptr; p.out = out;
+    p.k_head_stride = (long long)max_seq * DEC_D;
+    p.n_heads = (int)n_heads; p.fused = 1; p.rot_dim = (int)rot_dim; p.theta = theta;
+    p.pos_ptr = pos_dev;
+    const int max_splits = (int)((max_seq + DEC_KEYS - 1) / DEC_KEYS);
+    void* scratch = nullptr;
+    MD_TRY(md_scratch(ctx, (size_t)p.n_heads * max_splits * (DEC_D + 2) * sizeof(float), &scratch));
+    p.counters = ctx->counters;
+    p.partial = reinterpret_cast<float*>(scratch);
+    p.splits = max_splits;  // stride of the partial array; the kernel recomputes the live count
+    dim3 grid((unsigned)max_splits, (unsigned)p.n_heads);
+    sdpa_decode_kernel<<<grid, DEC_WARPS * 32, 0, ctx->stream>>>(p);
+    MD_LAUNCH_CHECK(ctx, "sdpa_decode_kernel");
+    return MD_OK;
 }
 
 int md_launch_rope_cache_write(md_ctx* ctx, const __half* qkv, __half* q_rot, __half* kc, __half* vc, size_t S,

@@ -66,7 +66,6 @@ gemm_simt_kernel(const __half* __restrict__ A, const __half* __restrict__ B, __h
         }
         __syncthreads();
     }
-    const bool hb = ep.bias != nullptr, hr = ep.residual != nullptr;
 #pragma unroll
     for (int i = 0; i < TM; ++i) {
         const int gm = m0 + ty * TM + i;
@@ -75,9 +74,7 @@ gemm_simt_kernel(const __half* __restrict__ A, const __half* __restrict__ B, __h
         for (int j = 0; j < TN; ++j) {
             const int gn = n0 + tx + 16 * j;
             if (gn >= N) continue;
-            const float bias = hb ? __half2float(ep.bias[gn]) : 0.f;
-            const float res = hr ? __half2float(ep.residual[(size_t)gm * N + gn]) : 0.f;
-            C[(size_t)gm * N + gn] = __float2half_rn(md_apply_epilogue(acc[i][j], bias, hb, ep.gelu != 0, res, hr));
+            C[(size_t)gm * N + gn] = __float2half_rn(md_epilogue_value(ep, acc[i][j], gm, gn, N));
         }
     }
 }

@@ -270,7 +270,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const int quad = warp & 3;  // TMEM lane quadrant this warp may read
         const uint32_t my_epi = smem_epi + (uint32_t)(warp - 2) * 2 * EPI_BUF_BYTES;
         uint8_t* my_epi_ptr = epi_ptr + (warp - 2) * 2 * EPI_BUF_BYTES;
-        const bool hb = ep.bias != nullptr, hr = ep.residual != nullptr, gelu = ep.gelu != 0;
+        const bool any_glue = ep.bias || ep.residual || ep.residual2 || ep.gelu;
         int local = 0, bufsel = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
             const int m0 = (tile % tiles_m) * BLOCK_M, n0 = (tile / tiles_m) * BLOCK_N;
@@ -296,17 +296,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         float v0 = __uint_as_float(r[2 * j]), v1 = __uint_as_float(r[2 * j + 1]);
-                        if (hb || hr || gelu) {
+                        if (any_glue && row < M) {
                             const int c0 = col0 + 2 * j, c1 = c0 + 1;
-                            const float b0 = (hb && c0 < N) ? __half2float(ep.bias[c0]) : 0.f;
-                            const float b1 = (hb && c1 < N) ? __half2float(ep.bias[c1]) : 0.f;
-                            float r0 = 0.f, r1 = 0.f;
-                            if (hr && row < M) {
-                                if (c0 < N) r0 = __half2float(ep.residual[(size_t)row * N + c0]);
-                                if (c1 < N) r1 = __half2float(ep.residual[(size_t)row * N + c1]);
-                            }
-                            v0 = md_apply_epilogue(v0, b0, hb, gelu, r0, hr);
-                            v1 = md_apply_epilogue(v1, b1, hb, gelu, r1, hr);
+                            if (c0 < N) v0 = md_epilogue_value(ep, v0, row, c0, N);
+                            if (c1 < N) v1 = md_epilogue_value(ep, v1, row, c1, N);
                         }
                         __half2 p = __floats2half2_rn(v0, v1);
                         packed[j] = *reinterpret_cast<uint32_t*>(&p);

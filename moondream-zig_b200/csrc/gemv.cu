@@ -115,10 +115,7 @@ gemv_nt_mma_kernel(const __half* __restrict__ A, const __half* __restrict__ Bt, 
             float s = 0.f;
 #pragma unroll
             for (int w = 0; w < WARPS; ++w) s += partial[w][r][m];
-            const bool hb = ep.bias != nullptr, hr = ep.residual != nullptr;
-            const float bias = hb ? __half2float(ep.bias[n]) : 0.f;
-            const float res = hr ? __half2float(ep.residual[(size_t)m * N + n]) : 0.f;
-            C[(size_t)m * N + n] = __float2half_rn(md_apply_epilogue(s, bias, hb, ep.gelu != 0, res, hr));
+            C[(size_t)m * N + n] = __float2half_rn(md_epilogue_value(ep, s, m, n, N));
         }
     }
 }

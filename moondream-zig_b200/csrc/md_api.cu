@@ -309,7 +309,7 @@ int md_check_matmul_shapes(const size_t* a_shape, size_t a_rank, const size_t* b
 }
 
 // device-pointer GEMM dispatch shared by every matmul entry point
-static int gemm_dispatch(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
+int md_gemm_dispatch(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
                          int b_layout, const md_epilogue& ep) {
     if (M == 0 || N == 0) return MD_OK;
     if (K == 0) {
@@ -317,7 +317,8 @@ static int gemm_dispatch(md_ctx* ctx, const __half* a, const __half* b, __half* 
         MD_CUDA(ctx, cudaMemsetAsync(c, 0, M * N * sizeof(__half), ctx->stream));
         if (ep.bias) MD_TRY(md_launch_bias_add(ctx, c, ep.bias, M, N));
         if (ep.gelu) MD_TRY(md_launch_gelu(ctx, c, M * N));
-        if (ep.residual) MD_TRY(md_launch_add(ctx, c, ep.residual, M * N));
+        if (ep.residual && ep.residual_rows == 0) MD_TRY(md_launch_add(ctx, c, ep.residual, M * N));
+        if (ep.residual2) MD_TRY(md_launch_add(ctx, c, ep.residual2, M * N));
         return MD_OK;
     }
     const bool aligned16 = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0;
@@ -340,7 +341,7 @@ static int hgemm_entry(md_ctx* ctx, const uint16_t* a, const uint16_t* b, uint16
     MD_TRY(md_stage_in(ctx, 1, b, N * K * 2, &B));
     MD_TRY(md_stage_out(ctx, 2, c, M * N * 2, &Cc));
     md_epilogue ep;
-    MD_TRY(gemm_dispatch(ctx, (const __half*)A.dev, (const __half*)B.dev, (__half*)Cc.dev, M, N, K, b_layout, ep));
+    MD_TRY(md_gemm_dispatch(ctx, (const __half*)A.dev, (const __half*)B.dev, (__half*)Cc.dev, M, N, K, b_layout, ep));
     return md_finish_out(ctx, &Cc);
 }
 
@@ -361,7 +362,7 @@ int md_hgemm_fused(md_ctx* ctx, const uint16_t* a, const uint16_t* b, uint16_t* 
     ep.bias = (const __half*)bias;
     ep.residual = (const __half*)residual;
     ep.gelu = gelu;
-    return gemm_dispatch(ctx, (const __half*)a, (const __half*)b, (__half*)c, M, N, K, b_layout, ep);
+    return md_gemm_dispatch(ctx, (const __half*)a, (const __half*)b, (__half*)c, M, N, K, b_layout, ep);
 }
 
 int md_sdpa_maskless(md_ctx* ctx, const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* out,

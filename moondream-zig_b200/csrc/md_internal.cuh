@@ -88,9 +88,11 @@ int md_check_flags(md_ctx* ctx);
 
 // ---- kernel launchers (device pointers only) ------------------------------------
 struct md_epilogue {
-    const __half* bias = nullptr;      // [N] or null
-    const __half* residual = nullptr;  // [M,N] or null
+    const __half* bias = nullptr;       // [N] or null
+    const __half* residual = nullptr;   // [M,N] (or [residual_rows,N] repeated every residual_rows rows) or null
+    const __half* residual2 = nullptr;  // [M,N] or null, added after `residual`
     int gelu = 0;
+    int residual_rows = 0;              // > 0: row m reads residual row m % residual_rows (broadcast over batches)
 };
 
 // gemv.cu: C[M,N] = A[M,K] . Bt[N,K]^T for M <= 8, K % 8 == 0.
@@ -163,6 +165,20 @@ __device__ __forceinline__ float md_apply_epilogue(float acc, float bias, bool h
     if (has_bias) v = md_round_f16(v + bias);
     if (gelu) v = md_round_f16(md_gelu_f32(v));
     if (has_resid) v = md_round_f16(v + resid);
+    return v;
+}
+
+// The fused glue for output element (m, n): f16(acc) -> +bias -> gelu -> +residual -> +residual2, one
+// rounding to f16 after every step, exactly where the reference's separate ops round.
+__device__ __forceinline__ float md_epilogue_value(const md_epilogue& ep, float acc, int m, int n, int N) {
+    float v = md_round_f16(acc);
+    if (ep.bias) v = md_round_f16(v + __half2float(ep.bias[n]));
+    if (ep.gelu) v = md_round_f16(md_gelu_f32(v));
+    if (ep.residual) {
+        const int rm = ep.residual_rows > 0 ? m % ep.residual_rows : m;
+        v = md_round_f16(v + __half2float(ep.residual[(size_t)rm * N + n]));
+    }
+    if (ep.residual2) v = md_round_f16(v + __half2float(ep.residual2[(size_t)m * N + n]));
     return v;
 }
 #endif

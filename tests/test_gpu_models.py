@@ -1,0 +1,171 @@
+"""GPU parity of the device-resident model runners against the oracle's restatement of
+text_model.zig / vision_model.zig: hidden states and logits within 1e-2 * max|ref|, and identical
+greedy tokens (teacher forcing) wherever the oracle's top-2 logit gap exceeds 0.05."""
+import numpy as np
+import pytest
+
+import __graft_entry__ as entry
+from conftest import assert_close_ref
+from model_utils import text_weights, top2_gap, vision_weights
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def models_mod(pkg):
+    import importlib
+    return importlib.import_module(entry.PKG_NAME + ".models")
+
+
+def run_text_parity(ctx, oracle, models_mod, w, prompt_rows, n_steps, seed):
+    rng = np.random.default_rng(seed)
+    ref = oracle.TextModel(w)
+    gpu = models_mod.TextModel(ctx, w)
+    req = gpu.request()
+    ids = rng.integers(0, ref.vocab, prompt_rows)
+    np.testing.assert_array_equal(gpu.text_encoder(ids), ref.embed(ids))
+    embeds = ref.embed(ids)
+    # prefill
+    h_ref = ref.decoder(embeds)
+    l_ref = ref.lm_head(h_ref)
+    h_gpu, l_gpu, tok_gpu = gpu.forward(req, embeds)
+    assert_close_ref(h_gpu, h_ref, "prefill hidden")
+    assert_close_ref(l_gpu, l_ref, "prefill logits")
+    tok_ref = oracle.argmax(l_ref)
+    if top2_gap(l_ref) > 0.05:
+        assert tok_gpu == tok_ref
+    assert len(req) == prompt_rows
+    # decode: the oracle generates; the GPU is fed the oracle's tokens (teacher forcing)
+    ref_tokens, gaps, ref_logits = [], [], []
+    cur = tok_ref
+    for _ in range(n_steps):
+        h = ref.decoder(ref.embed([cur]))
+        l = ref.lm_head(h)
+        cur = oracle.argmax(l)
+        ref_tokens.append(cur); gaps.append(top2_gap(l)); ref_logits.append(l)
+    toks, logits = gpu.generate(req, tok_ref, n_steps, forced=np.array(ref_tokens, np.uint32), want_logits=True)
+    pinned = np.array(gaps) > 0.05
+    assert pinned.sum() >= 1
+    np.testing.assert_array_equal(toks[pinned], np.array(ref_tokens)[pinned])
+    for i in (0, n_steps // 2, n_steps - 1):
+        assert_close_ref(logits[i], ref_logits[i], f"decode logits step {i}")
+    assert len(req) == prompt_rows + n_steps
+    stats = {"pinned": int(pinned.sum()), "steps": n_steps, "match_all": int((toks == np.array(ref_tokens)).sum())}
+    # free-running from the same state reproduces the teacher-forced tokens while they agree
+    req.close(); gpu.close()
+    return stats
+
+
+def test_text_small_model(ctx, oracle, models_mod):
+    w = text_weights(4001, n_layers=2, hidden=1024, vocab=4096)
+    stats = run_text_parity(ctx, oracle, models_mod, w, prompt_rows=37, n_steps=12, seed=1)
+    assert stats["match_all"] >= stats["pinned"]
+
+
+def test_text_prefill_of_one_row_then_decode(ctx, oracle, models_mod):
+    w = text_weights(4002, n_layers=2, hidden=512, vocab=2048)
+    run_text_parity(ctx, oracle, models_mod, w, prompt_rows=1, n_steps=5, seed=2)
+
+
+def test_text_free_running_generation_and_graph_reuse(ctx, oracle, models_mod):
+    w = text_weights(4003, n_layers=2, hidden=512, vocab=2048)
+    gpu = models_mod.TextModel(ctx, w)
+    rng = np.random.default_rng(3)
+    embeds = w["wte"][rng.integers(0, 2048, 20)]
+    outs = []
+    for _ in range(2):                      # second pass replays the graph captured by the first
+        req = gpu.request() if not outs else req
+        req.reset()
+        _, _, tok = gpu.forward(req, embeds)
+        outs.append(gpu.generate(req, tok, 16))
+    np.testing.assert_array_equal(outs[0], outs[1])
+    # teacher forcing with its own output changes nothing
+    req.reset()
+    _, _, tok = gpu.forward(req, embeds)
+    np.testing.assert_array_equal(gpu.generate(req, tok, 16, forced=outs[0]), outs[0])
+    req.close(); gpu.close()
+
+
+def test_text_batched_decode_equals_single_requests(ctx, models_mod):
+    w = text_weights(4004, n_layers=2, hidden=512, vocab=2048)
+    gpu = models_mod.TextModel(ctx, w)
+    rng = np.random.default_rng(4)
+    prompts = [w["wte"][rng.integers(0, 2048, n)] for n in (5, 130, 33)]
+    singles, firsts = [], []
+    for p in prompts:
+        r = gpu.request()
+        _, _, tok = gpu.forward(r, p)
+        firsts.append(tok)
+        singles.append(gpu.generate(r, tok, 10))
+        r.close()
+    reqs = [gpu.request() for _ in prompts]
+    for r, p in zip(reqs, prompts):
+        gpu.forward(r, p)
+    batch = gpu.generate_batch(reqs, firsts, 10)
+    np.testing.assert_array_equal(batch, np.stack(singles))
+    for r in reqs:
+        r.close()
+    gpu.close()
+
+
+def test_text_cache_overflow_is_an_error(ctx, pkg, models_mod):
+    w = text_weights(4005, n_layers=1, hidden=256, vocab=512)
+    gpu = models_mod.TextModel(ctx, w, max_seq=64)
+    req = gpu.request()
+    with pytest.raises(pkg.MdError) as e:
+        gpu.forward(req, w["wte"][:65])
+    assert e.value.zig_error == "error.SequenceTooLong"
+    gpu.forward(req, w["wte"][:60])
+    with pytest.raises(pkg.MdError):
+        gpu.generate(req, 1, 5)
+    req.close(); gpu.close()
+
+
+def test_text_full_config4(ctx, oracle, models_mod):
+    """BASELINE config 4: 24 layers, prefill of 761 rows (729 image rows + 32 tokens), 200 greedy steps."""
+    w = text_weights(4000)
+    stats = run_text_parity(ctx, oracle, models_mod, w, prompt_rows=761, n_steps=200, seed=4)
+    print("config 4 parity:", stats)
+    assert stats["pinned"] >= 100
+
+
+def run_vision(ctx, oracle, models_mod, w, crops, seed):
+    rng = np.random.default_rng(seed)
+    img = rng.integers(0, 256, (crops, 378, 378, 3), dtype=np.uint8)
+    ref = oracle.VisionModel(w)
+    patches = oracle.preprocess_patchify(img)
+    f_ref = ref.encoder(patches, joint_attention=False)
+    b = min(1, crops - 1)
+    o_ref = ref.projection(f_ref[0], f_ref[b])
+    gpu = models_mod.VisionModel(ctx, w, max_crops=crops)
+    o_gpu, f_gpu = gpu.encode(img, want_features=True)
+    assert_close_ref(f_gpu.reshape(f_ref.shape), f_ref, "vision features")
+    assert_close_ref(o_gpu, o_ref, "projection output")
+    gpu.close()
+    return ref, img, o_gpu
+
+
+def test_vision_small_two_identical_crops_match_the_reference_joint_attention(ctx, oracle, models_mod):
+    """The reference feeds two identical crops and attends over both as one sequence
+    (vision_model.zig:137-155,308-316); per-crop attention gives the same features."""
+    w = vision_weights(3001, n_layers=2)
+    rng = np.random.default_rng(7)
+    one = rng.integers(0, 256, (1, 378, 378, 3), dtype=np.uint8)
+    img = np.concatenate([one, one])
+    ref = oracle.VisionModel(w)
+    f_joint = ref.encoder(oracle.preprocess_patchify(img), joint_attention=True)
+    gpu = models_mod.VisionModel(ctx, w, max_crops=2)
+    o_gpu, f_gpu = gpu.encode(img, want_features=True)
+    assert_close_ref(f_gpu.reshape(f_joint.shape), f_joint, "features vs joint attention")
+    assert_close_ref(o_gpu, ref.projection(f_joint[0], f_joint[1]), "projection")
+    gpu.close()
+
+
+@pytest.mark.parametrize("crops", [1, 5])
+def test_vision_small_crops(ctx, oracle, models_mod, crops):
+    run_vision(ctx, oracle, models_mod, vision_weights(3002, n_layers=2), crops, seed=crops)
+
+
+def test_vision_full_config3_one_crop(ctx, oracle, models_mod):
+    """BASELINE config 3 at full depth (27 layers), one crop."""
+    run_vision(ctx, oracle, models_mod, vision_weights(3000), 1, seed=11)
