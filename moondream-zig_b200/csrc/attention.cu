@@ -295,6 +295,7 @@ struct DecodeParams {
     int fused, pos, rot_dim;
     float theta;
     int splits;
+    const float* rope_tab;  // fused: (cos, sin) table [positions][rot_dim/2][2] (rope.zig:32-128)
     const int* pos_ptr;     // fused + graph replay: position read from device memory, else null
 };
 
@@ -316,14 +317,12 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
 }
 
 // rope.zig:50-65,223-230 for one head vector held in shared memory (f32 in, f16-rounded out).
-__device__ __forceinline__ float rope_elem(const float* x, int dd, int pos, int rot_dim, float theta) {
+__device__ __forceinline__ float rope_elem(const float* x, int dd, int pos, int rot_dim, const float* tab) {
     if (dd >= rot_dim) return x[dd];
     const int half = rot_dim / 2, j = dd < half ? dd : dd - half;
-    const float freq = 1.0f / powf(theta, (float)(2 * j) / (float)rot_dim);
-    const float ang = (float)pos * freq;
-    const float c = cosf(ang), sn = sinf(ang);
+    const float2 cs = *reinterpret_cast<const float2*>(tab + ((size_t)pos * half + j) * 2);  // (cos, sin)
     const float xr = x[j], xi = x[j + half];
-    return dd < half ? xr * c - xi * sn : xr * sn + xi * c;
+    return dd < half ? xr * cs.x - xi * cs.y : xr * cs.y + xi * cs.x;
 }
 
 __global__ void __launch_bounds__(DEC_WARPS * 32)
@@ -349,13 +348,13 @@ sdpa_decode_kernel(DecodeParams p) {
         const int hd = p.n_heads * DEC_D;
         if (tid < DEC_D) raw_s[tid] = __half2float(p.q[head * DEC_D + tid]);
         __syncthreads();
-        if (tid < DEC_D) q_s[tid] = md_round_f16(rope_elem(raw_s, tid, p.pos, p.rot_dim, p.theta));
+        if (tid < DEC_D) q_s[tid] = md_round_f16(rope_elem(raw_s, tid, p.pos, p.rot_dim, p.rope_tab));
         __syncthreads();
         if (last_split) {
             if (tid < DEC_D) raw_s[tid] = __half2float(p.q[hd + head * DEC_D + tid]);
             __syncthreads();
             if (tid < DEC_D) {
-                const __half kr = __float2half_rn(rope_elem(raw_s, tid, p.pos, p.rot_dim, p.theta));
+                const __half kr = __float2half_rn(rope_elem(raw_s, tid, p.pos, p.rot_dim, p.rope_tab));
                 const __half vn = p.q[2 * hd + head * DEC_D + tid];
                 knew_s[tid] = __half2float(kr);
                 vnew_s[tid] = __half2float(vn);
@@ -508,7 +507,7 @@ sdpa_decode_kernel(DecodeParams p) {
 __global__ void __launch_bounds__(128)
 rope_cache_write_kernel(const __half* __restrict__ qkv, __half* __restrict__ q_rot, __half* __restrict__ kc,
                         __half* __restrict__ vc, int S, int H, int d, int max_seq, int pos, int rot_dim,
-                        float theta) {
+                        const float* __restrict__ tab) {
     const int s = blockIdx.x, hd = H * d;
     const __half* row = qkv + (long long)s * 3 * hd;
     const int half = rot_dim / 2;
@@ -517,9 +516,8 @@ rope_cache_write_kernel(const __half* __restrict__ qkv, __half* __restrict__ q_r
         float qo, ko;
         if (dd < rot_dim) {
             const int j = dd < half ? dd : dd - half;
-            const float freq = 1.0f / powf(theta, (float)(2 * j) / (float)rot_dim);
-            const float ang = (float)(pos + s) * freq;
-            const float c = cosf(ang), sn = sinf(ang);
+            const float2 cs = *reinterpret_cast<const float2*>(tab + ((size_t)(pos + s) * half + j) * 2);
+            const float c = cs.x, sn = cs.y;
             const float qr = __half2float(row[h * d + j]), qi = __half2float(row[h * d + j + half]);
             const float kr = __half2float(row[hd + h * d + j]), ki = __half2float(row[hd + h * d + j + half]);
             qo = dd < half ? qr * c - qi * sn : qr * sn + qi * c;
@@ -603,6 +601,7 @@ int md_launch_sdpa_decode_fused(md_ctx* ctx, const __half* qkv_row, __half* kc, 
     p.k_head_stride = (long long)max_seq * DEC_D;
     p.n_heads = (int)n_heads; p.kv_cache_len = (int)pos; p.fused = 1; p.pos = (int)pos; p.rot_dim = (int)rot_dim;
     p.theta = theta;
+    MD_TRY(md_rope_cached(ctx, rot_dim, theta, max_seq, &p.rope_tab));
     return decode_launch(ctx, p);
 }
 
@@ -615,6 +614,7 @@ int md_launch_sdpa_decode_fused_devpos(md_ctx* ctx, const __half* qkv_row, __hal
     p.q = qkv_row; p.k = kc; p.v = vc; p.k_w = kc; p.v_w = vc; p.mask = nullptr; p.out = out;
     p.k_head_stride = (long long)max_seq * DEC_D;
     p.n_heads = (int)n_heads; p.fused = 1; p.rot_dim = (int)rot_dim; p.theta = theta;
+    MD_TRY(md_rope_cached(ctx, rot_dim, theta, max_seq, &p.rope_tab));
     p.pos_ptr = pos_dev;
     const int max_splits = (int)((max_seq + DEC_KEYS - 1) / DEC_KEYS);
     void* scratch = nullptr;
@@ -631,8 +631,10 @@ int md_launch_sdpa_decode_fused_devpos(md_ctx* ctx, const __half* qkv_row, __hal
 int md_launch_rope_cache_write(md_ctx* ctx, const __half* qkv, __half* q_rot, __half* kc, __half* vc, size_t S,
                                size_t n_heads, size_t d, size_t max_seq, size_t pos, size_t rot_dim, float theta) {
     if (S == 0) return MD_OK;
+    const float* tab = nullptr;
+    MD_TRY(md_rope_cached(ctx, rot_dim, theta, max_seq, &tab));
     rope_cache_write_kernel<<<(unsigned)S, 128, 0, ctx->stream>>>(qkv, q_rot, kc, vc, (int)S, (int)n_heads, (int)d,
-                                                                  (int)max_seq, (int)pos, (int)rot_dim, theta);
+                                                                  (int)max_seq, (int)pos, (int)rot_dim, tab);
     MD_LAUNCH_CHECK(ctx, "rope_cache_write_kernel");
     return MD_OK;
 }

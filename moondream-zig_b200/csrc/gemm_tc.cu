@@ -2,14 +2,14 @@
 // tensor memory, one rounding to f16, optional fused glue.  B is [N,K] ("NT",
 // hgemm_trans.zig:400-488) or [K,N] ("NN", hgemm.zig:362-426).
 //
-// Structure (one persistent CTA per SM, 192 threads):
+// Structure (one persistent CTA per SM, 320 threads):
 //   warp 0      TMA producer: cp.async.bulk.tensor loads of the A tile (128 x 64) and the
 //               B tile (BLOCK_N x 64) into a ring of shared-memory stages, 128-byte swizzle.
 //   warp 1      MMA issuer: one lane issues tcgen05.mma (128 x BLOCK_N x 16, kind::f16) with
 //               shared-memory descriptors; accumulators live in TMEM, two buffers of
 //               BLOCK_N columns so the epilogue of tile i overlaps the main loop of tile i+1.
 //               tcgen05.commit releases smem stages and publishes finished accumulators.
-//   warps 2..5  epilogue: tcgen05.ld (32 lanes x 32 columns) -> fused glue -> f16 ->
+//   warps 2..9  epilogue: tcgen05.ld (32 lanes x 32 columns) -> fused glue -> f16 ->
 //               swizzled smem -> TMA store (clips the M and N tails).
 // Tails: TMA zero-fills out-of-bounds loads and clips out-of-bounds stores, so any M, N, K
 // with 16-byte-aligned row strides is accepted.
@@ -23,8 +23,9 @@ namespace {
 
 constexpr int BLOCK_M = 128, BLOCK_K = 64, UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BLOCK_M * BLOCK_K * 2;     // 16 KiB
-constexpr int EPI_WARPS = 4, EPI_BUF_BYTES = 32 * 128;   // 32 rows x 64 f16 per buffer
-constexpr int EPI_BYTES = EPI_WARPS * 2 * EPI_BUF_BYTES; // 32 KiB
+constexpr int EPI_WARPS = 8, EPI_BUF_BYTES = 32 * 128;   // 32 rows x 64 f16 per epilogue warp
+constexpr int EPI_BYTES = EPI_WARPS * EPI_BUF_BYTES;     // 32 KiB
+constexpr int NUM_THREADS = (2 + EPI_WARPS) * 32;
 constexpr int SMEM_LIMIT = 232448;                       // 227 KiB opt-in maximum
 constexpr int BAR_BYTES = 1024;
 
@@ -133,6 +134,18 @@ __device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// 8 consecutive halves (16-byte aligned) widened to f32.
+__device__ __forceinline__ void load8(const __half* p, float (&f)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 x = __half22float2(h[i]);
+        f[2 * i] = x.x;
+        f[2 * i + 1] = x.y;
+    }
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
 //   K-major operand (rows of 64 halves = 128 B, 8-row groups 1024 B apart):
 //       leading offset unused (1), stride offset 1024 B.
@@ -149,7 +162,7 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_b
 }
 
 template <int BLOCK_N, bool B_MN_MAJOR>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_c, int M, int N, int K, int tiles_m, int num_tiles,
                md_epilogue ep, md_devflags* flags) {
@@ -266,12 +279,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue (warps 2..5)
+        // ------------------------------------------------------------ epilogue (warps 2..9)
+        // Two warps per TMEM lane quadrant; they take alternate 64-column chunks of the tile.
         const int quad = warp & 3;  // TMEM lane quadrant this warp may read
-        const uint32_t my_epi = smem_epi + (uint32_t)(warp - 2) * 2 * EPI_BUF_BYTES;
-        uint8_t* my_epi_ptr = epi_ptr + (warp - 2) * 2 * EPI_BUF_BYTES;
+        const int half = (warp - 2) >> 2;
+        const uint32_t my_epi = smem_epi + (uint32_t)(warp - 2) * EPI_BUF_BYTES;
+        uint8_t* my_epi_ptr = epi_ptr + (warp - 2) * EPI_BUF_BYTES;
         const bool any_glue = ep.bias || ep.residual || ep.residual2 || ep.gelu;
-        int local = 0, bufsel = 0;
+        int local = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
             const int m0 = (tile % tiles_m) * BLOCK_M, n0 = (tile / tiles_m) * BLOCK_N;
             const int buf = local & 1;
@@ -281,37 +296,63 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const int row = m0 + quad * 32 + lane;
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BLOCK_N);
 #pragma unroll 1
-            for (int c = 0; c < BLOCK_N / 64; ++c) {
-                // the buffer about to be overwritten must have been read by its earlier TMA store
-                if (lane == 0) tma_store_wait_read<1>();
+            for (int c = half; c < BLOCK_N / 64; c += 2) {
+                // the staging buffer must have been read by this warp's previous TMA store
+                if (lane == 0) tma_store_wait_read<0>();
                 __syncwarp();
-                uint8_t* out_row = my_epi_ptr + bufsel * EPI_BUF_BYTES + lane * 128;
+                uint8_t* out_row = my_epi_ptr + lane * 128;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     uint32_t r[32];
                     tc_ld_32x32(t_row + (uint32_t)(c * 64 + h * 32), r);
                     tc_wait_ld();
                     const int col0 = n0 + c * 64 + h * 32;
-                    uint32_t packed[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        float v0 = __uint_as_float(r[2 * j]), v1 = __uint_as_float(r[2 * j + 1]);
-                        if (any_glue && row < M) {
-                            const int c0 = col0 + 2 * j, c1 = c0 + 1;
-                            if (c0 < N) v0 = md_epilogue_value(ep, v0, row, c0, N);
-                            if (c1 < N) v1 = md_epilogue_value(ep, v1, row, c1, N);
-                        }
-                        __half2 p = __floats2half2_rn(v0, v1);
-                        packed[j] = *reinterpret_cast<uint32_t*>(&p);
-                    }
+                    // Glue per group of 8 columns (N % 8 == 0, so a group is entirely inside or outside
+                    // the matrix): bias, residual and residual2 arrive as single 16-byte loads.
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
+                        const int cq = col0 + 8 * q;
+                        float v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[8 * q + j]);
+                        if (any_glue && row < M && cq < N) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) v[j] = md_round_f16(v[j]);
+                            if (ep.bias) {
+                                float b[8];
+                                load8(ep.bias + cq, b);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) v[j] = md_round_f16(v[j] + b[j]);
+                            }
+                            if (ep.gelu) {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) v[j] = md_round_f16(md_gelu_fast_f32(v[j]));
+                            }
+                            if (ep.residual) {
+                                const int rm = ep.residual_rows > 0 ? row % ep.residual_rows : row;
+                                float b[8];
+                                load8(ep.residual + (size_t)rm * N + cq, b);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) v[j] = md_round_f16(v[j] + b[j]);
+                            }
+                            if (ep.residual2) {
+                                float b[8];
+                                load8(ep.residual2 + (size_t)row * N + cq, b);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) v[j] = md_round_f16(v[j] + b[j]);
+                            }
+                        }
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            __half2 hh = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+                            pk[j] = *reinterpret_cast<uint32_t*>(&hh);
+                        }
                         const int chunk = (h * 4 + q) ^ (lane & 7);  // 128-byte swizzle, matches the store map
-                        *reinterpret_cast<uint4*>(out_row + chunk * 16) =
-                            make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                        *reinterpret_cast<uint4*>(out_row + chunk * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                     }
                 }
-                if (c == BLOCK_N / 64 - 1) {
+                if (c + 2 >= BLOCK_N / 64) {
                     // all of this warp's TMEM reads of the tile are done: hand the buffer back
                     tc_fence_before();
                     __syncwarp();
@@ -320,10 +361,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    tma_store_2d(&tm_c, my_epi + bufsel * EPI_BUF_BYTES, n0 + c * 64, m0 + quad * 32);
+                    tma_store_2d(&tm_c, my_epi, n0 + c * 64, m0 + quad * 32);
                     tma_store_commit();
                 }
-                bufsel ^= 1;
+            }
+            if (half >= BLOCK_N / 64) {
+                // a warp without a chunk (tile narrower than its share) still releases the accumulator
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
             }
         }
         if (lane == 0) tma_store_wait_all();
@@ -382,7 +428,7 @@ int launch(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, s
         MD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         ctx->tc_configured |= cfg_bit;
     }
-    kern<<<grid, 192, smem, ctx->stream>>>(tm_a, tm_b, tm_c, (int)M, (int)N, (int)K, tiles_m, num_tiles, ep,
+    kern<<<grid, NUM_THREADS, smem, ctx->stream>>>(tm_a, tm_b, tm_c, (int)M, (int)N, (int)K, tiles_m, num_tiles, ep,
                                            ctx->flags);
     MD_LAUNCH_CHECK(ctx, "gemm_tc_kernel");
     return MD_OK;
@@ -408,9 +454,21 @@ int md_launch_gemm_tc(md_ctx* ctx, const __half* a, const __half* b, __half* c, 
     // problems, which are bandwidth-bound and want many CTAs streaming B.
     const size_t tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
     auto tiles = [&](size_t bn) { return tiles_m * ((N + bn - 1) / bn); };
-    int bn = 256;
-    if (tiles(256) < (size_t)ctx->sm_count) bn = 128;
-    if (bn == 128 && tiles(128) < (size_t)ctx->sm_count) bn = 64;
+    // Cost model: (waves over the SMs) x (time of one tile); a tile's time grows with its width,
+    // narrower tiles run the tensor pipe less efficiently (smem bandwidth per MMA).  Skinny
+    // problems (M <= 64) are bandwidth-bound and take the narrowest tile to get many CTAs.
+    int bn = 64;
+    if (M > 64) {
+        const int cand[3] = {256, 128, 64};
+        const double eff[3] = {1.0, 0.9, 0.65};
+        double best = 0;
+        for (int i = 0; i < 3; ++i) {
+            const size_t t = tiles(cand[i]);
+            const size_t waves = (t + ctx->sm_count - 1) / ctx->sm_count;
+            const double cost = (double)waves * cand[i] / eff[i];
+            if (i == 0 || cost < best) { best = cost; bn = cand[i]; }
+        }
+    }
     if (ctx->tc_block_n) bn = ctx->tc_block_n;
     const bool mn = (b_layout == 0);
     if (mn) {

@@ -119,6 +119,26 @@ int md_scratch(md_ctx* ctx, size_t bytes, void** out) {
     return MD_OK;
 }
 
+int md_rope_cached(md_ctx* ctx, size_t rot_dim, float theta, size_t rows, const float** out) {
+    if (!ctx->rope_tab || ctx->rope_dim != rot_dim || ctx->rope_theta != theta || ctx->rope_rows < rows) {
+        if (ctx->capturing)
+            return md_fail(ctx, MD_ERR_UNSUPPORTED, "the rope table must exist before graph capture; run the call once first");
+        if (rot_dim == 0 || (rot_dim & 1)) return md_fail(ctx, MD_ERR_INVALID_ROT_DIM, "rope: rot_dim %zu", rot_dim);
+        if (ctx->rope_tab) {
+            MD_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            MD_CUDA(ctx, cudaFree(ctx->rope_tab));
+            ctx->rope_tab = nullptr;
+        }
+        MD_CUDA(ctx, cudaMalloc((void**)&ctx->rope_tab, rows * rot_dim * sizeof(float)));
+        ctx->rope_rows = rows;
+        ctx->rope_dim = rot_dim;
+        ctx->rope_theta = theta;
+        MD_TRY(md_launch_rope_table(ctx, ctx->rope_tab, rot_dim, rows, theta));
+    }
+    *out = ctx->rope_tab;
+    return MD_OK;
+}
+
 #define MD_NEED_CTX(ctx) \
     do { if (!(ctx)) return MD_ERR_INVALID_ARG; } while (0)
 #define MD_NEED(ctx, cond, what) \
@@ -174,6 +194,7 @@ int md_destroy(md_ctx* ctx) {
         if (s.ptr) cudaFree(s.ptr);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->counters) cudaFree(ctx->counters);
+    if (ctx->rope_tab) cudaFree(ctx->rope_tab);
     if (ctx->flags) cudaFree(ctx->flags);
     if (ctx->flags_host) cudaFreeHost(ctx->flags_host);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);

@@ -46,10 +46,14 @@ struct md_ctx {
     unsigned int* counters = nullptr;
     // cuTensorMapEncodeTiled resolved through the runtime (no link against libcuda)
     void* encode_tiled = nullptr;
-    uint32_t tc_configured = 0;
+    uint32_t tc_configured = 0;  // tcgen05 kernels whose dynamic shared memory limit has been raised
+    // (cos, sin) table shared by the fused attention calls: [rope_rows][rope_dim/2][2] f32
+    float* rope_tab = nullptr;
+    size_t rope_rows = 0, rope_dim = 0;
+    float rope_theta = 0.f;
     bool capturing = false;  // between md_graph_begin and md_graph_end
     int gemv_variant = 0;    // md_set_option("gemv_variant")
-    int tc_block_n = 0;      // md_set_option("tc_block_n")  // kernels whose dynamic shared memory limit has been raised
+    int tc_block_n = 0;      // md_set_option("tc_block_n")
 };
 
 int md_fail(md_ctx* ctx, int status, const char* fmt, ...);
@@ -66,6 +70,8 @@ int md_fail(md_ctx* ctx, int status, const char* fmt, ...);
         if (_s != MD_OK) return _s;     \
     } while (0)
 
+// The context's rope table for (rot_dim, theta), covering at least `rows` positions; built on first use.
+int md_rope_cached(md_ctx* ctx, size_t rot_dim, float theta, size_t rows, const float** out);
 // Ensure ctx->scratch holds at least `bytes`.
 int md_scratch(md_ctx* ctx, size_t bytes, void** out);
 
@@ -156,6 +162,17 @@ __device__ __forceinline__ float md_gelu_f32(float v) {
     const float c = 0.7978515625f, a = 0.044708251953125f;
     const float inner = c * (v + a * (v * v * v));
     return 0.5f * v * (1.0f + tanhf(inner));
+}
+
+// The same GELU with tanh(t) = 1 - 2 / (exp(2t) + 1) on the fast exp/divide units, for the GEMM
+// epilogues where tanhf would cost more than the tile's MMAs.  Absolute error < 1e-6, far below the
+// f16 rounding applied to the result.
+__device__ __forceinline__ float md_gelu_fast_f32(float v) {
+    const float c = 0.7978515625f, a = 0.044708251953125f;
+    const float inner = c * (v + a * (v * v * v));
+    const float e = __expf(2.0f * fminf(fmaxf(inner, -15.0f), 15.0f));  // tanh(+-15) = +-1 to 2e-13
+    const float th = 1.0f - __fdividef(2.0f, e + 1.0f);
+    return 0.5f * v * (1.0f + th);
 }
 
 // acc (f32 accumulator) -> f16 value after the fused glue, as f32 holding an f16-representable value.

@@ -102,6 +102,9 @@ struct md_text_request {
     md_graph* graph = nullptr;
     size_t graph_steps = 0;
     bool graph_forced = false, graph_logits = false;
+    // a prefill of the same shape at the same position seen twice is captured and replayed
+    md_graph* prefill_graph = nullptr;
+    size_t prefill_S = 0, prefill_pos = 0, seen_S = 0, seen_pos = ~(size_t)0;
 };
 
 namespace {
@@ -122,6 +125,10 @@ int ensure_rows(md_text_request* r, size_t rows) {
         // the buffers are about to move: a captured decode step that points at them is stale
         md_graph_destroy(ctx, r->graph);
         r->graph = nullptr;
+    }
+    if (r->prefill_graph && r->hidden.cap < rows * w.dim * 2) {
+        md_graph_destroy(ctx, r->prefill_graph);
+        r->prefill_graph = nullptr;
     }
     MD_TRY(r->hidden.ensure(ctx, rows * w.dim * 2));
     MD_TRY(r->ln.ensure(ctx, rows * w.dim * 2));
@@ -271,6 +278,7 @@ int md_text_request_destroy(md_text_request* req) {
     md_ctx* ctx = req->model->ctx;
     cudaStreamSynchronize(ctx->stream);
     if (req->graph) md_graph_destroy(ctx, req->graph);
+    if (req->prefill_graph) md_graph_destroy(ctx, req->prefill_graph);
     for (auto p : req->kc) cudaFree(p);
     for (auto p : req->vc) cudaFree(p);
     if (req->pos_dev) cudaFree(req->pos_dev);
@@ -333,11 +341,37 @@ int md_text_forward(md_text_model* model, md_text_request* req, const uint16_t* 
     MD_CUDA(ctx, cudaMemcpyAsync(req->hidden.p, embeds, S * w.dim * 2, kind, ctx->stream));
     const LayerIO io = io_of(req);
     md_text_request* reqs[1] = {req};
+    const size_t pos0 = req->pos;
     // S == 1 takes the decode kernels (text_model.zig:284-290 switches on seq_len == 1 as well)
-    for (size_t l = 0; l < w.n_layers; ++l) MD_TRY(text_layer(model, l, io, S, S == 1, reqs, req->pos));
-    req->pos += S;
-    set_int_kernel<<<1, 1, 0, ctx->stream>>>(req->pos_dev, (int)req->pos);
-    MD_LAUNCH_CHECK(ctx, "set_int_kernel");
+    auto body = [&]() -> int {
+        for (size_t l = 0; l < w.n_layers; ++l) MD_TRY(text_layer(model, l, io, S, S == 1, reqs, pos0));
+        set_int_kernel<<<1, 1, 0, ctx->stream>>>(req->pos_dev, (int)(pos0 + S));
+        MD_LAUNCH_CHECK(ctx, "set_int_kernel");
+        return MD_OK;
+    };
+    if (S > 1 && req->prefill_graph && req->prefill_S == S && req->prefill_pos == pos0) {
+        MD_TRY(md_graph_launch(ctx, req->prefill_graph));
+    } else {
+        MD_TRY(body());
+        if (S > 1 && !ctx->capturing && req->seen_S == S && req->seen_pos == pos0) {
+            // second prefill of this shape: record it (the ~170 launches are host-bound when issued one by one)
+            if (req->prefill_graph) { md_graph_destroy(ctx, req->prefill_graph); req->prefill_graph = nullptr; }
+            MD_TRY(md_graph_begin(ctx));
+            const int st = body();
+            md_graph* g = nullptr;
+            const int st2 = md_graph_end(ctx, &g);
+            if (st == MD_OK && st2 == MD_OK) {
+                req->prefill_graph = g;
+                req->prefill_S = S;
+                req->prefill_pos = pos0;
+            } else if (g) {
+                md_graph_destroy(ctx, g);
+            }
+        }
+        req->seen_S = S;
+        req->seen_pos = pos0;
+    }
+    req->pos = pos0 + S;
     MD_TRY(copy_out(ctx, hidden_out, req->hidden.p, S * w.dim * 2));
     if (logits_out || token_out) {
         MD_TRY(text_lm_head(model, req->hidden.as<__half>() + (S - 1) * w.dim, 1, req->ln_last.as<__half>(),
@@ -472,6 +506,8 @@ struct md_vision_model {
     std::vector<const uint16_t*> ln1_w, ln1_b, wqkv, bqkv, wout, bout, ln2_w, ln2_b, wfc1, bfc1, wfc2, bfc2;
     size_t max_crops = 0, patch_dim = 0, patch_dim_padded = 0;
     DevPtr patch_w_padded, img, patches, x, ln, qkv, att, fc1, cat, pfc1, out;
+    md_graph* graph = nullptr;  // the whole encode for (graph_crops, graph_a, graph_b), captured on its second use
+    size_t graph_crops = 0, graph_a = 0, graph_b = 0, seen_crops = 0, seen_a = 0, seen_b = 0;
 };
 
 extern "C" {
@@ -523,6 +559,7 @@ int md_vision_model_create(md_ctx* ctx, const md_vision_weights* w, size_t max_c
 
 int md_vision_model_destroy(md_vision_model* model) {
     if (model) cudaStreamSynchronize(model->ctx->stream);
+    if (model && model->graph) md_graph_destroy(model->ctx, model->graph);
     delete model;
     return MD_OK;
 }
@@ -538,12 +575,12 @@ int md_vision_encode(md_vision_model* m, const uint8_t* crops_u8, size_t crops, 
                        crop_b);
     const size_t T = w.tokens, D = w.dim, F = w.hidden, R = crops * T;
     const float eps = eps_of(w.eps_f16);
-    const uint8_t* img = crops_u8;
-    if (!md_is_device_ptr(crops_u8)) {
-        MD_CUDA(ctx, cudaMemcpyAsync(m->img.p, crops_u8, crops * w.img * w.img * 3, cudaMemcpyHostToDevice, ctx->stream));
-        img = m->img.as<uint8_t>();
-    }
-    __half *x = m->x.as<__half>(), *ln = m->ln.as<__half>(), *qkv = m->qkv.as<__half>(), *att = m->att.as<__half>(),
+    const cudaMemcpyKind in_kind = md_is_device_ptr(crops_u8) ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
+    MD_CUDA(ctx, cudaMemcpyAsync(m->img.p, crops_u8, crops * w.img * w.img * 3, in_kind, ctx->stream));
+    const uint8_t* img = m->img.as<uint8_t>();
+    __half* ln = m->ln.as<__half>();
+    auto body = [&]() -> int {
+    __half *x = m->x.as<__half>(), *qkv = m->qkv.as<__half>(), *att = m->att.as<__half>(),
            *fc1 = m->fc1.as<__half>();
     MD_TRY(md_launch_patchify(ctx, img, m->patches.as<__half>(), crops, w.img, w.img, w.patch, m->patch_dim_padded));
     // patch embedding + bias, then the position embedding broadcast over the crops (vision_model.zig:220-228)
@@ -575,23 +612,48 @@ int md_vision_encode(md_vision_model* m, const uint8_t* crops_u8, size_t crops, 
         MD_TRY(md_gemm_dispatch(ctx, fc1, H(m->wfc2[l]), x, R, D, F, 0, e_fc2));
     }
     MD_TRY(md_launch_layernorm(ctx, x, H(w.norm_w), H(w.norm_b), ln, R, D, eps));  // features, in ln
+        return MD_OK;
+    };
+    auto proj = [&]() -> int {
+        // concat(features[a], features[b]) on the feature dim (vision_model.zig:189-195)
+        __half* cat = m->cat.as<__half>();
+        MD_CUDA(ctx, cudaMemcpy2DAsync(cat, 2 * D * 2, ln + crop_a * T * D, D * 2, D * 2, T, cudaMemcpyDeviceToDevice,
+                                       ctx->stream));
+        MD_CUDA(ctx, cudaMemcpy2DAsync(cat + D, 2 * D * 2, ln + crop_b * T * D, D * 2, D * 2, T, cudaMemcpyDeviceToDevice,
+                                       ctx->stream));
+        md_epilogue e_p1;
+        e_p1.bias = H(w.proj_fc1_b);
+        e_p1.gelu = 1;
+        MD_TRY(md_gemm_dispatch(ctx, cat, H(w.proj_fc1_w), m->pfc1.as<__half>(), T, w.proj_hidden, 2 * D, 0, e_p1));
+        md_epilogue e_p2;
+        e_p2.bias = H(w.proj_fc2_b);
+        MD_TRY(md_gemm_dispatch(ctx, m->pfc1.as<__half>(), H(w.proj_fc2_w), m->out.as<__half>(), T, w.proj_out,
+                                w.proj_hidden, 0, e_p2));
+        return MD_OK;
+    };
+    if (m->graph && m->graph_crops == crops && m->graph_a == crop_a && m->graph_b == crop_b) {
+        MD_TRY(md_graph_launch(ctx, m->graph));
+    } else {
+        MD_TRY(body());
+        MD_TRY(proj());
+        if (!ctx->capturing && m->seen_crops == crops && m->seen_a == crop_a && m->seen_b == crop_b) {
+            if (m->graph) { md_graph_destroy(ctx, m->graph); m->graph = nullptr; }
+            MD_TRY(md_graph_begin(ctx));
+            int st = body();
+            if (st == MD_OK) st = proj();
+            md_graph* g = nullptr;
+            const int st2 = md_graph_end(ctx, &g);
+            if (st == MD_OK && st2 == MD_OK) {
+                m->graph = g;
+                m->graph_crops = crops; m->graph_a = crop_a; m->graph_b = crop_b;
+            } else if (g) {
+                md_graph_destroy(ctx, g);
+            }
+        }
+        m->seen_crops = crops; m->seen_a = crop_a; m->seen_b = crop_b;
+    }
     MD_TRY(copy_out(ctx, features_out, ln, R * D * 2));
-    // concat(features[a], features[b]) on the feature dim (vision_model.zig:189-195)
-    __half* cat = m->cat.as<__half>();
-    MD_CUDA(ctx, cudaMemcpy2DAsync(cat, 2 * D * 2, ln + crop_a * T * D, D * 2, D * 2, T, cudaMemcpyDeviceToDevice,
-                                   ctx->stream));
-    MD_CUDA(ctx, cudaMemcpy2DAsync(cat + D, 2 * D * 2, ln + crop_b * T * D, D * 2, D * 2, T, cudaMemcpyDeviceToDevice,
-                                   ctx->stream));
-    md_epilogue e_p1;
-    e_p1.bias = H(w.proj_fc1_b);
-    e_p1.gelu = 1;
-    MD_TRY(md_gemm_dispatch(ctx, cat, H(w.proj_fc1_w), m->pfc1.as<__half>(), T, w.proj_hidden, 2 * D, 0, e_p1));
-    md_epilogue e_p2;
-    e_p2.bias = H(w.proj_fc2_b);
-    const bool out_dev = md_is_device_ptr(out);
-    __half* dst = out_dev ? H(out) : m->out.as<__half>();
-    MD_TRY(md_gemm_dispatch(ctx, m->pfc1.as<__half>(), H(w.proj_fc2_w), dst, T, w.proj_out, w.proj_hidden, 0, e_p2));
-    if (!out_dev) MD_CUDA(ctx, cudaMemcpyAsync(out, dst, T * w.proj_out * 2, cudaMemcpyDeviceToHost, ctx->stream));
+    MD_TRY(copy_out(ctx, out, m->out.p, T * w.proj_out * 2));
     return md_check_flags(ctx);
 }
 
