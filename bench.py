@@ -273,6 +273,10 @@ def main():
     err = (pin_y[(8, 4)].float() - (xs[(8, 4)].float() @ ws[4].float().T).cpu()).abs().max().item()
     assert err < 0.2, f"e2e parity check failed: {err}"
 
+    colsplit = None
+    if world > 1 and not args.no_extras:
+        colsplit = colsplit_extras(ctx, torch, dist, stream, world, rank)
+
     if rank != 0:
         ctx.sync()
         if world > 1:
@@ -300,6 +304,8 @@ def main():
 
     if not args.no_extras and world == 1:
         line["extras"] = extras(ctx, torch, stream, tensor_peak, hbm_peak)
+    if colsplit is not None:
+        line["extras"] = {"colsplit_gemm_8192": colsplit}
 
     # ---- CPU baseline: the oracle on this box's host cores, bounded sample
     from oracle import oracle
@@ -329,6 +335,54 @@ def main():
 # (fc1, fc2, lm_head at M = 1) against 276.97 MB of algorithmic bytes, a factor of 1.0124; traffic grows in
 # proportion to the weight bytes, so the average launch of the sweep is scaled by the same factor.
 TRAFFIC_BYTES_PER_LAUNCH = int(round(1.0124 * STEP_BYTES / 20))
+
+
+def colsplit_extras(ctx, torch, dist, stream, world, rank):
+    """BASELINE config 5b: 8192^3 f16 GEMM with N split over the ranks; all-gather baseline (NCCL) against the
+    fused push epilogue.  Device time per call, max over ranks."""
+    import importlib
+    import __graft_entry__ as entry
+    par = importlib.import_module(entry.PKG_NAME + ".parallel")
+    M = N = K = 8192
+    a = torch.randn(M, K, device="cuda").half()
+    bs = (torch.randn(N // world, K, device="cuda") * 0.02).half()   # this rank's rows of B^T ([N,K] layout)
+    out = {"M": M, "N": N, "K": K, "world": world}
+    peaks = measured_peaks()
+    for mode in ("allgather", "fused"):
+        g = par.ColSplitGemm(ctx, M, N, K, 1, mode=mode)
+        for _ in range(3):
+            g(a, bs)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        e0.record(stream)
+        for _ in range(reps):
+            g(a, bs)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = t.item() * 1e3
+        out[mode] = {"us": round(us, 1), "TFLOP/s_total": round(2.0 * M * N * K / us / 1e6, 1)}
+        del g
+    # roofline of the fused kernel: the slower of the math and the bytes that must cross NVLink
+    t_math = 2.0 * M * (N / world) * K / (peaks[1] * 1e12)
+    t_link = M * (N / world) * 2 * (world - 1) / 770e9
+    out["fused"]["target_us"] = round(max(t_math, t_link) * 1e6, 1)
+    out["fused"]["frac_of_target"] = round(out["fused"]["target_us"] / out["fused"]["us"], 3)
+    # the GEMM alone, for reference
+    y = torch.empty(M, N // world, device="cuda", dtype=torch.float16)
+    for _ in range(2):
+        ctx.hgemm_nt(a.data_ptr(), bs.data_ptr(), M, N // world, K, out=y.data_ptr())
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(10):
+        ctx.hgemm_nt(a.data_ptr(), bs.data_ptr(), M, N // world, K, out=y.data_ptr())
+    e1.record(stream)
+    torch.cuda.synchronize()
+    out["local_gemm_us"] = round(e0.elapsed_time(e1) / 10 * 1e3, 1)
+    return out
 
 
 def extras(ctx, torch, stream, tensor_peak, hbm_peak):

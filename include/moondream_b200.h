@@ -120,6 +120,25 @@ int md_check_matmul_shapes(const size_t* a_shape, size_t a_rank, const size_t* b
 int md_hgemm_fused(md_ctx* ctx, const uint16_t* a, const uint16_t* b, uint16_t* c, size_t M, size_t N, size_t K,
                    int b_layout, const uint16_t* bias, int gelu, const uint16_t* residual);
 
+/* ---- column-split GEMM across the GPUs of one box (the one exchange step of the path) ----------
+ * C[M, N_total] = A[M,K] . B with N split over `world` GPUs: this rank computes the column block
+ * [col_offset, col_offset + N_local) from the full A and its slice of B (hgemm.zig / hgemm_trans.zig
+ * have no distributed counterpart; the arithmetic per block is md_hgemm_nn / md_hgemm_nt).
+ *
+ * md_hgemm_colsplit_push fuses the exchange into the GEMM: every finished chunk of the block is stored
+ * into this rank's full C (c_full, row stride N_total) and, with plain peer stores over NVLink, into the
+ * same place of the n_peers other ranks' full C buffers (peer_c_full: device pointers that are mapped
+ * into this process, e.g. from symmetric memory or CUDA IPC).  When every rank has run the call and a
+ * cross-rank barrier has passed, every C holds all column blocks; no separate all-gather runs.
+ * b is this rank's slice: [K, N_local] (b_layout 0) or [N_local, K] (b_layout 1).  n_peers <= 7. */
+int md_hgemm_colsplit_push(md_ctx* ctx, const uint16_t* a, const uint16_t* b_slice, uint16_t* c_full, size_t M,
+                           size_t N_local, size_t K, int b_layout, size_t N_total, size_t col_offset, size_t n_peers,
+                           uint16_t* const* peer_c_full);
+
+/* The re-layout step of the all-gather baseline: gathered [world][M][N_local] (what an all-gather of the
+ * ranks' contiguous blocks produces) -> c [M][world * N_local].  Device pointers. */
+int md_gather_colblocks(md_ctx* ctx, const uint16_t* gathered, uint16_t* c, size_t world, size_t M, size_t N_local);
+
 /* ---- attention ----------------------------------------------------------------- */
 
 /* Replaces attention.multiMasklessSDPA(n_heads, head_dim, q, k, v, allocator) —

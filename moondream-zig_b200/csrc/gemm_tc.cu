@@ -165,7 +165,7 @@ template <int BLOCK_N, bool B_MN_MAJOR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_c, int M, int N, int K, int tiles_m, int num_tiles,
-               md_epilogue ep, md_devflags* flags) {
+               md_epilogue ep, md_push push, md_devflags* flags) {
     constexpr int STAGES = num_stages(BLOCK_N);
     constexpr int B_STAGE_BYTES = BLOCK_N * BLOCK_K * 2;
     constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
@@ -364,6 +364,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     tma_store_2d(&tm_c, my_epi, n0 + c * 64, m0 + quad * 32);
                     tma_store_commit();
                 }
+                if (push.n > 0) {
+                    // Column-split GEMM: the same chunk goes to the other GPUs' copies of C with plain
+                    // peer stores, 128 contiguous bytes per row per instruction (8 lanes x 16 B).
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int r = it * 4 + (lane >> 3), ch = lane & 7;
+                        const uint4 val = *reinterpret_cast<const uint4*>(my_epi_ptr + r * 128 + ((ch ^ (r & 7)) * 16));
+                        const int gm = m0 + quad * 32 + r, gc = n0 + c * 64 + ch * 8;
+                        if (gm < M && gc < N) {
+                            for (int pi = 0; pi < push.n; ++pi)
+                                *reinterpret_cast<uint4*>(push.base[pi] + (long long)gm * push.ld + gc) = val;
+                        }
+                    }
+                }
             }
             if (half >= BLOCK_N / 64) {
                 // a warp without a chunk (tile narrower than its share) still releases the accumulator
@@ -373,6 +387,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             }
         }
         if (lane == 0) tma_store_wait_all();
+        if (push.n > 0) __threadfence_system();  // peer stores performed before the kernel ends
     }
 
     tc_fence_before();
@@ -389,7 +404,7 @@ typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_
                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 int make_map_2d(md_ctx* ctx, CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,
-                uint32_t box_outer) {
+                uint32_t box_outer, uint64_t ld = 0) {
     if (!ctx->encode_tiled) {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
@@ -399,7 +414,7 @@ int make_map_2d(md_ctx* ctx, CUtensorMap* map, const void* ptr, uint64_t inner, 
         ctx->encode_tiled = fn;
     }
     const cuuint64_t dims[2] = {inner, outer};
-    const cuuint64_t strides[1] = {inner * 2};
+    const cuuint64_t strides[1] = {(ld ? ld : inner) * 2};
     const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t elem[2] = {1, 1};
     CUresult r = reinterpret_cast<encode_tiled_fn>(ctx->encode_tiled)(
@@ -412,12 +427,12 @@ int make_map_2d(md_ctx* ctx, CUtensorMap* map, const void* ptr, uint64_t inner, 
 
 template <int BLOCK_N, bool B_MN_MAJOR>
 int launch(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
-           const md_epilogue& ep) {
+           const md_epilogue& ep, size_t ldc, const md_push& push) {
     CUtensorMap tm_a, tm_b, tm_c;
     MD_TRY(make_map_2d(ctx, &tm_a, a, K, M, BLOCK_K, BLOCK_M));
     if (B_MN_MAJOR) MD_TRY(make_map_2d(ctx, &tm_b, b, N, K, 64, BLOCK_K));
     else MD_TRY(make_map_2d(ctx, &tm_b, b, K, N, BLOCK_K, BLOCK_N));
-    MD_TRY(make_map_2d(ctx, &tm_c, c, N, M, 64, 32));
+    MD_TRY(make_map_2d(ctx, &tm_c, c, N, M, 64, 32, ldc));
     const int tiles_m = (int)((M + BLOCK_M - 1) / BLOCK_M), tiles_n = (int)((N + BLOCK_N - 1) / BLOCK_N);
     const int num_tiles = tiles_m * tiles_n;
     const int grid = num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count;
@@ -429,7 +444,7 @@ int launch(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, s
         ctx->tc_configured |= cfg_bit;
     }
     kern<<<grid, NUM_THREADS, smem, ctx->stream>>>(tm_a, tm_b, tm_c, (int)M, (int)N, (int)K, tiles_m, num_tiles, ep,
-                                           ctx->flags);
+                                                   push, ctx->flags);
     MD_LAUNCH_CHECK(ctx, "gemm_tc_kernel");
     return MD_OK;
 }
@@ -448,6 +463,16 @@ bool md_gemm_tc_supported(const void* a, const void* b, const void* c, size_t M,
 
 int md_launch_gemm_tc(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
                       int b_layout, const md_epilogue& ep) {
+    md_push none;
+    return md_launch_gemm_tc_ex(ctx, a, b, c, M, N, K, b_layout, ep, N, none);
+}
+
+int md_launch_gemm_tc_ex(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
+                         int b_layout, const md_epilogue& ep, size_t ldc, const md_push& push) {
+    if ((ldc % 8) != 0 || ldc < N)
+        return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 GEMM: the output row stride must be a multiple of 8 and >= N");
+    if (ldc != N && (ep.residual || ep.residual2))
+        return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 GEMM: residuals are not supported with a strided output");
     if (!md_gemm_tc_supported(a, b, c, M, N, K, b_layout))
         return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 GEMM needs K %% 8 == 0, N %% 8 == 0 and 16-byte aligned operands");
     // Tile width: the widest tile that still gives every SM work; narrow tiles for skinny
@@ -472,11 +497,11 @@ int md_launch_gemm_tc(md_ctx* ctx, const __half* a, const __half* b, __half* c, 
     if (ctx->tc_block_n) bn = ctx->tc_block_n;
     const bool mn = (b_layout == 0);
     if (mn) {
-        if (bn == 256) return launch<256, true>(ctx, a, b, c, M, N, K, ep);
-        if (bn == 128) return launch<128, true>(ctx, a, b, c, M, N, K, ep);
-        return launch<64, true>(ctx, a, b, c, M, N, K, ep);
+        if (bn == 256) return launch<256, true>(ctx, a, b, c, M, N, K, ep, ldc, push);
+        if (bn == 128) return launch<128, true>(ctx, a, b, c, M, N, K, ep, ldc, push);
+        return launch<64, true>(ctx, a, b, c, M, N, K, ep, ldc, push);
     }
-    if (bn == 256) return launch<256, false>(ctx, a, b, c, M, N, K, ep);
-    if (bn == 128) return launch<128, false>(ctx, a, b, c, M, N, K, ep);
-    return launch<64, false>(ctx, a, b, c, M, N, K, ep);
+    if (bn == 256) return launch<256, false>(ctx, a, b, c, M, N, K, ep, ldc, push);
+    if (bn == 128) return launch<128, false>(ctx, a, b, c, M, N, K, ep, ldc, push);
+    return launch<64, false>(ctx, a, b, c, M, N, K, ep, ldc, push);
 }

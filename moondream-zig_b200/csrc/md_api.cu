@@ -386,6 +386,39 @@ int md_hgemm_fused(md_ctx* ctx, const uint16_t* a, const uint16_t* b, uint16_t* 
     return md_gemm_dispatch(ctx, (const __half*)a, (const __half*)b, (__half*)c, M, N, K, b_layout, ep);
 }
 
+int md_hgemm_colsplit_push(md_ctx* ctx, const uint16_t* a, const uint16_t* b_slice, uint16_t* c_full, size_t M,
+                           size_t N_local, size_t K, int b_layout, size_t N_total, size_t col_offset, size_t n_peers,
+                           uint16_t* const* peer_c_full) {
+    MD_NEED_CTX(ctx);
+    MD_NEED(ctx, a && b_slice && c_full, "colsplit_push: null tensor pointer");
+    MD_NEED(ctx, b_layout == 0 || b_layout == 1, "colsplit_push: b_layout must be 0 or 1");
+    MD_NEED(ctx, n_peers <= 7 && (n_peers == 0 || peer_c_full), "colsplit_push: at most 7 peers");
+    if (col_offset + N_local > N_total) return md_fail(ctx, MD_ERR_SHAPE, "colsplit_push: column block outside C");
+    if ((col_offset % 8) != 0 || (N_total % 8) != 0)
+        return md_fail(ctx, MD_ERR_UNSUPPORTED, "colsplit_push: column offset and N_total must be multiples of 8");
+    md_push push;
+    push.n = (int)n_peers;
+    push.ld = (long long)N_total;
+    for (size_t i = 0; i < n_peers; ++i) {
+        MD_NEED(ctx, peer_c_full[i], "colsplit_push: null peer pointer");
+        push.base[i] = reinterpret_cast<__half*>(peer_c_full[i]) + col_offset;
+    }
+    md_epilogue ep;
+    return md_launch_gemm_tc_ex(ctx, (const __half*)a, (const __half*)b_slice, (__half*)c_full + col_offset, M, N_local, K,
+                                b_layout, ep, N_total, push);
+}
+
+int md_gather_colblocks(md_ctx* ctx, const uint16_t* gathered, uint16_t* c, size_t world, size_t M, size_t N_local) {
+    MD_NEED_CTX(ctx);
+    MD_NEED(ctx, gathered && c, "gather_colblocks: null pointer");
+    if (!world || !M || !N_local) return MD_OK;
+    // block g is a contiguous [M, N_local] matrix: one strided 2-D copy per block
+    for (size_t g = 0; g < world; ++g)
+        MD_CUDA(ctx, cudaMemcpy2DAsync(c + g * N_local, world * N_local * 2, gathered + g * M * N_local, N_local * 2,
+                                       N_local * 2, M, cudaMemcpyDeviceToDevice, ctx->stream));
+    return MD_OK;
+}
+
 int md_sdpa_maskless(md_ctx* ctx, const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* out,
                      size_t n_heads, size_t q_len, size_t kv_len, size_t d) {
     MD_NEED_CTX(ctx);

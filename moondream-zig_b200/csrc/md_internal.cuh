@@ -101,6 +101,13 @@ struct md_epilogue {
     int residual_rows = 0;              // > 0: row m reads residual row m % residual_rows (broadcast over batches)
 };
 
+// Column-split GEMM: finished C chunks are also stored into the other GPUs' buffers.
+struct md_push {
+    int n = 0;                 // number of peers (0 = none)
+    long long ld = 0;          // row stride of the peers' C in elements
+    __half* base[7] = {};      // peer pointers to element (0, 0) of this rank's column block
+};
+
 // gemv.cu: C[M,N] = A[M,K] . Bt[N,K]^T for M <= 8, K % 8 == 0.
 int md_launch_gemv_nt(md_ctx* ctx, const __half* a, const __half* bt, __half* c, size_t M, size_t N, size_t K,
                       const md_epilogue& ep);
@@ -111,6 +118,9 @@ int md_launch_gemm_simt(md_ctx* ctx, const __half* a, const __half* b, __half* c
 bool md_gemm_tc_supported(const void* a, const void* b, const void* c, size_t M, size_t N, size_t K, int b_layout);
 int md_launch_gemm_tc(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
                       int b_layout, const md_epilogue& ep);
+// as above with an output row stride ldc >= N (C is a column block of a wider matrix) and peer pushes
+int md_launch_gemm_tc_ex(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
+                         int b_layout, const md_epilogue& ep, size_t ldc, const md_push& push);
 
 // attention.cu
 int md_launch_sdpa(md_ctx* ctx, const __half* q, const __half* k, const __half* v, const uint8_t* mask, __half* out,
