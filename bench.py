@@ -185,6 +185,9 @@ def main():
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
     ctx.set_stream(stream.cuda_stream)
+    # the weights are registered once and never written on this stream, so consecutive GEMVs may be
+    # launched programmatically dependent (a kernel streams its first weights while its predecessor drains)
+    ctx.set_option("pdl", 1)
 
     ws_h, xs_h = make_inputs()
     ws = [torch.from_numpy(w).cuda() for w in ws_h]

@@ -30,6 +30,18 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     return v;
 }
 
+// Activations may be written by the predecessor kernel while this kernel already runs (programmatic
+// dependent launch), so they must not go through the non-coherent path: an L2-cached load that the
+// compiler may not move above the dependency wait.
+__device__ __forceinline__ uint4 ld_act(const __half* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -43,7 +55,7 @@ constexpr int ROWS_PER_CTA = 16;
 // UNROLL = number of 32-wide k chunks whose loads are issued before any is consumed.
 template <int WARPS, int UNROLL>
 __global__ void __launch_bounds__(WARPS * 32)
-gemv_nt_mma_kernel(const __half* __restrict__ A, const __half* __restrict__ Bt, __half* __restrict__ C, int M, int N,
+gemv_nt_mma_kernel(const __half* A, const __half* __restrict__ Bt, __half* C, int M, int N,
                    int K, md_epilogue ep) {
     __shared__ float partial[WARPS][ROWS_PER_CTA][8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -61,6 +73,11 @@ gemv_nt_mma_kernel(const __half* __restrict__ A, const __half* __restrict__ Bt, 
     const int chunks = K / 32;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     int ch = warp;
+    // Programmatic dependent launch: let the next kernel of the stream start its own prologue now, and
+    // stream this kernel's first weights (which no earlier kernel writes) before waiting for the kernel
+    // that produces the activations.  Without the launch attribute both instructions are no-ops.
+    asm volatile("griddepcontrol.launch_dependents;");
+    bool waited = false;
     for (; ch + (UNROLL - 1) * WARPS < chunks; ch += UNROLL * WARPS) {
         uint4 lo[UNROLL], hi[UNROLL], xv[UNROLL];
 #pragma unroll
@@ -69,10 +86,14 @@ gemv_nt_mma_kernel(const __half* __restrict__ A, const __half* __restrict__ Bt, 
             lo[u] = ldg_stream(w_lo + k);
             hi[u] = ldg_stream(w_hi + k);
         }
+        if (!waited) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            waited = true;
+        }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int k = (ch + u * WARPS) * 32;
-            xv[u] = has_x ? __ldg(reinterpret_cast<const uint4*>(x + k)) : make_uint4(0, 0, 0, 0);
+            xv[u] = has_x ? ld_act(x + k) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
@@ -80,10 +101,11 @@ gemv_nt_mma_kernel(const __half* __restrict__ A, const __half* __restrict__ Bt, 
             mma_16816(acc, lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv[u].z, xv[u].w);
         }
     }
+    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
     for (; ch < chunks; ch += WARPS) {
         const int k = ch * 32;
         const uint4 lo = ldg_stream(w_lo + k), hi = ldg_stream(w_hi + k);
-        const uint4 xv = has_x ? __ldg(reinterpret_cast<const uint4*>(x + k)) : make_uint4(0, 0, 0, 0);
+        const uint4 xv = has_x ? ld_act(x + k) : make_uint4(0, 0, 0, 0);
         mma_16816(acc, lo.x, hi.x, lo.y, hi.y, xv.x, xv.y);
         mma_16816(acc, lo.z, hi.z, lo.w, hi.w, xv.z, xv.w);
     }
@@ -96,7 +118,7 @@ gemv_nt_mma_kernel(const __half* __restrict__ A, const __half* __restrict__ Bt, 
         if (k < K) {
             lo = ldg_stream(Bt + (size_t)r_lo * K + k);
             hi = ldg_stream(Bt + (size_t)r_hi * K + k);
-            if (has_x) xv = __ldg(reinterpret_cast<const uint4*>(A + (size_t)g * K + k));
+            if (has_x) xv = ld_act(A + (size_t)g * K + k);
         }
         mma_16816(acc, lo.x, hi.x, lo.y, hi.y, xv.x, xv.y);
         mma_16816(acc, lo.z, hi.z, lo.w, hi.w, xv.z, xv.w);
@@ -139,9 +161,23 @@ int md_launch_gemv_nt(md_ctx* ctx, const __half* a, const __half* bt, __half* c,
         else if (K >= 4096 || N <= 2048) variant = 6;
         else variant = 2;
     }
-#define MD_GEMV_CASE(id, W, U)                                                                          \
-    case id:                                                                                            \
-        gemv_nt_mma_kernel<W, U><<<grid, W * 32, 0, ctx->stream>>>(a, bt, c, (int)M, (int)N, (int)K, ep); \
+    // With ctx->pdl the launch carries the programmatic-stream-serialization attribute: the kernel may
+    // start while its predecessor drains and orders itself with griddepcontrol.wait.  Only valid when
+    // the weights are not produced by an earlier kernel of the stream (true for registered weights).
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    const int Mi = (int)M, Ni = (int)N, Ki = (int)K;
+    cudaError_t le = cudaSuccess;
+#define MD_GEMV_CASE(id, W, U)                                                          \
+    case id:                                                                            \
+        cfg.blockDim = dim3(W * 32);                                                    \
+        le = cudaLaunchKernelEx(&cfg, gemv_nt_mma_kernel<W, U>, a, bt, c, Mi, Ni, Ki, ep); \
         break;
     switch (variant) {
         MD_GEMV_CASE(1, 4, 8)
@@ -154,6 +190,7 @@ int md_launch_gemv_nt(md_ctx* ctx, const __half* a, const __half* bt, __half* c,
             return md_fail(ctx, MD_ERR_INVALID_ARG, "unknown gemv variant %d", variant);
     }
 #undef MD_GEMV_CASE
+    if (le != cudaSuccess) return md_fail(ctx, MD_ERR_CUDA, "launch of gemv_nt_mma_kernel failed: %s", cudaGetErrorString(le));
     MD_LAUNCH_CHECK(ctx, "gemv_nt_mma_kernel");
     return MD_OK;
 }

@@ -54,6 +54,7 @@ struct md_ctx {
     bool capturing = false;  // between md_graph_begin and md_graph_end
     int gemv_variant = 0;    // md_set_option("gemv_variant")
     int tc_block_n = 0;      // md_set_option("tc_block_n")
+    int pdl = 0;             // md_set_option("pdl"): programmatic dependent launch for the GEMV kernels
 };
 
 int md_fail(md_ctx* ctx, int status, const char* fmt, ...);
@@ -203,9 +204,9 @@ __device__ __forceinline__ float md_epilogue_value(const md_epilogue& ep, float 
     if (ep.gelu) v = md_round_f16(md_gelu_f32(v));
     if (ep.residual) {
         const int rm = ep.residual_rows > 0 ? m % ep.residual_rows : m;
-        v = md_round_f16(v + __half2float(ep.residual[(size_t)rm * N + n]));
+        v = md_round_f16(v + __half2float(__ldcg(ep.residual + (size_t)rm * N + n)));
     }
-    if (ep.residual2) v = md_round_f16(v + __half2float(ep.residual2[(size_t)m * N + n]));
+    if (ep.residual2) v = md_round_f16(v + __half2float(__ldcg(ep.residual2 + (size_t)m * N + n)));
     return v;
 }
 #endif

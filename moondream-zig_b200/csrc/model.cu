@@ -388,6 +388,12 @@ static int enqueue_decode_step(md_text_model* model, md_text_request* const* req
     md_ctx* ctx = model->ctx;
     const md_text_weights& w = model->w;
     md_text_request* r0 = reqs[0];
+    // registered weights are never written on this stream: the GEMVs may overlap their predecessors' tails
+    struct PdlScope {
+        md_ctx* c; int old;
+        explicit PdlScope(md_ctx* cc) : c(cc), old(cc->pdl) { c->pdl = 1; }
+        ~PdlScope() { c->pdl = old; }
+    } pdl_scope(ctx);
     embed_kernel<<<(unsigned)batch, 256, 0, ctx->stream>>>(H(w.wte), r0->cur_token.as<unsigned long long>(),
                                                            r0->hidden.as<__half>(), (int)w.dim, (int)w.vocab);
     MD_LAUNCH_CHECK(ctx, "embed_kernel");
