@@ -343,35 +343,10 @@ sdpa_decode_kernel(DecodeParams p) {
     const bool last_split = split == p.splits - 1;
     const float scale = 0.125f;  // 1/sqrt(64)
 
-    // ---- stage q (and, fused, the new k and v) in shared memory
-    if (p.fused) {
-        const int hd = p.n_heads * DEC_D;
-        if (tid < DEC_D) raw_s[tid] = __half2float(p.q[head * DEC_D + tid]);
-        __syncthreads();
-        if (tid < DEC_D) q_s[tid] = md_round_f16(rope_elem(raw_s, tid, p.pos, p.rot_dim, p.rope_tab));
-        __syncthreads();
-        if (last_split) {
-            if (tid < DEC_D) raw_s[tid] = __half2float(p.q[hd + head * DEC_D + tid]);
-            __syncthreads();
-            if (tid < DEC_D) {
-                const __half kr = __float2half_rn(rope_elem(raw_s, tid, p.pos, p.rot_dim, p.rope_tab));
-                const __half vn = p.q[2 * hd + head * DEC_D + tid];
-                knew_s[tid] = __half2float(kr);
-                vnew_s[tid] = __half2float(vn);
-                p.k_w[head * p.k_head_stride + (long long)p.pos * DEC_D + tid] = kr;
-                p.v_w[head * p.k_head_stride + (long long)p.pos * DEC_D + tid] = vn;
-            }
-        }
-    } else {
-        if (tid < DEC_D) q_s[tid] = __half2float(p.q[head * DEC_D + tid]);
-    }
-    __syncthreads();
-
     const int sub = lane & 7, grp = lane >> 3;  // 8 lanes x 16 B cover one 128-byte key row
-    float qv[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) qv[i] = q_s[sub * 8 + i];
-
+    // ---- request this CTA's keys and values first: the cached prefix was written by earlier steps, so
+    //      under programmatic dependent launch these loads overlap the tail of the kernel that produces q
+    asm volatile("griddepcontrol.launch_dependents;");
     const __half* kh = p.k + head * p.k_head_stride;
     const __half* vh = p.v + head * p.k_head_stride;
     const int key_lo = split * DEC_KEYS + warp * (DEC_KEYS / DEC_WARPS);
@@ -390,6 +365,36 @@ sdpa_decode_kernel(DecodeParams p) {
         const int key = key_lo + it * 4 + grp;
         vreg[it] = valid[it] ? ldg_nc16(vh + (long long)key * DEC_D + sub * 8) : make_uint4(0, 0, 0, 0);
     }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // ---- stage q (and, fused, the new k and v) in shared memory
+    if (p.fused) {
+        const int hd = p.n_heads * DEC_D;
+        if (tid < DEC_D) raw_s[tid] = __half2float(__ldcg(p.q + head * DEC_D + tid));
+        __syncthreads();
+        if (tid < DEC_D) q_s[tid] = md_round_f16(rope_elem(raw_s, tid, p.pos, p.rot_dim, p.rope_tab));
+        __syncthreads();
+        if (last_split) {
+            if (tid < DEC_D) raw_s[tid] = __half2float(__ldcg(p.q + hd + head * DEC_D + tid));
+            __syncthreads();
+            if (tid < DEC_D) {
+                const __half kr = __float2half_rn(rope_elem(raw_s, tid, p.pos, p.rot_dim, p.rope_tab));
+                const __half vn = __ldcg(p.q + 2 * hd + head * DEC_D + tid);
+                knew_s[tid] = __half2float(kr);
+                vnew_s[tid] = __half2float(vn);
+                p.k_w[head * p.k_head_stride + (long long)p.pos * DEC_D + tid] = kr;
+                p.v_w[head * p.k_head_stride + (long long)p.pos * DEC_D + tid] = vn;
+            }
+        }
+    } else {
+        if (tid < DEC_D) q_s[tid] = __half2float(__ldcg(p.q + head * DEC_D + tid));
+    }
+    __syncthreads();
+
+    float qv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) qv[i] = q_s[sub * 8 + i];
+
     float sc[ITER];
     float m = -INFINITY;
 #pragma unroll
@@ -622,8 +627,17 @@ int md_launch_sdpa_decode_fused_devpos(md_ctx* ctx, const __half* qkv_row, __hal
     p.counters = ctx->counters;
     p.partial = reinterpret_cast<float*>(scratch);
     p.splits = max_splits;  // stride of the partial array; the kernel recomputes the live count
-    dim3 grid((unsigned)max_splits, (unsigned)p.n_heads);
-    sdpa_decode_kernel<<<grid, DEC_WARPS * 32, 0, ctx->stream>>>(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)max_splits, (unsigned)p.n_heads);
+    cfg.blockDim = dim3(DEC_WARPS * 32);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, sdpa_decode_kernel, p);
+    if (le != cudaSuccess) return md_fail(ctx, MD_ERR_CUDA, "launch of sdpa_decode_kernel failed: %s", cudaGetErrorString(le));
     MD_LAUNCH_CHECK(ctx, "sdpa_decode_kernel");
     return MD_OK;
 }

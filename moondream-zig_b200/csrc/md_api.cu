@@ -263,6 +263,8 @@ int md_set_option(md_ctx* ctx, const char* key, long value) {
     MD_NEED_CTX(ctx);
     MD_NEED(ctx, key, "md_set_option: null key");
     if (!strcmp(key, "gemv_variant")) { ctx->gemv_variant = (int)value; return MD_OK; }
+    if (!strcmp(key, "dualk_variant")) { ctx->dualk_variant = (int)value; return MD_OK; }
+    if (!strcmp(key, "fused_decode")) { ctx->fused_decode = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "pdl")) { ctx->pdl = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "tc_block_n")) {
         MD_NEED(ctx, value == 0 || value == 64 || value == 128 || value == 256, "tc_block_n must be 0, 64, 128 or 256");

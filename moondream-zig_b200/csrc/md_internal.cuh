@@ -54,6 +54,8 @@ struct md_ctx {
     bool capturing = false;  // between md_graph_begin and md_graph_end
     int gemv_variant = 0;    // md_set_option("gemv_variant")
     int tc_block_n = 0;      // md_set_option("tc_block_n")
+    int dualk_variant = 0;   // md_set_option("dualk_variant"): (warps, unroll) of gemv_dual_k_kernel
+    int fused_decode = 1;    // md_set_option("fused_decode"): decode layers as 3 fused kernels
     int pdl = 0;             // md_set_option("pdl"): programmatic dependent launch for the GEMV kernels
 };
 
@@ -112,6 +114,18 @@ struct md_push {
 // gemv.cu: C[M,N] = A[M,K] . Bt[N,K]^T for M <= 8, K % 8 == 0.
 int md_launch_gemv_nt(md_ctx* ctx, const __half* a, const __half* bt, __half* c, size_t M, size_t N, size_t K,
                       const md_epilogue& ep);
+// gemv_fused.cu: the decode layer's GEMVs fused with the glue around them (M <= 8 rows).
+//   ln_dual: y = LayerNorm(hidden); out1 = y W1^T + b1; out2 = gelu(y W2^T + b2)      (K = 2048)
+//   dual_k : hidden += (x1 W1^T + b1) + (x2 W2^T + b2), with the reference's f16 rounding points
+bool md_gemv_ln_dual_supported(size_t M, size_t K, size_t n1, size_t n2);
+int md_launch_gemv_ln_dual(md_ctx* ctx, const __half* hidden, const __half* ln_w, const __half* ln_b, float eps,
+                           const __half* w1, const __half* b1, __half* out1, size_t n1, const __half* w2,
+                           const __half* b2, __half* out2, size_t n2, size_t M, size_t K,
+                           unsigned long long* amax = nullptr);  // amax: optional [M] argmax keys of out1
+bool md_gemv_dual_k_supported(size_t M, size_t N, size_t k1, size_t k2);
+int md_launch_gemv_dual_k(md_ctx* ctx, const __half* x1, const __half* w1, const __half* b1, size_t k1,
+                          const __half* x2, const __half* w2, const __half* b2, size_t k2, __half* hidden, size_t N,
+                          size_t M);
 // gemm_simt.cu: any shape; b_layout 0 = [K,N], 1 = [N,K].
 int md_launch_gemm_simt(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
                         int b_layout, const md_epilogue& ep);

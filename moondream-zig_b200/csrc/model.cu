@@ -153,6 +153,21 @@ int text_layer(md_text_model* m, size_t layer, const LayerIO& io, size_t rows, b
     md_ctx* ctx = m->ctx;
     const md_text_weights& w = m->w;
     const size_t D = w.dim, F = w.hidden;
+    if (decode && ctx->fused_decode && md_gemv_ln_dual_supported(rows, D, 3 * D, F) &&
+        md_gemv_dual_k_supported(rows, D, D, F)) {
+        // Three kernels per layer: [LayerNorm + qkv + fc1] -> attention -> [out-proj + fc2 + residuals]
+        MD_TRY(md_launch_gemv_ln_dual(ctx, io.hidden, H(m->ln_w[layer]), H(m->ln_b[layer]), eps_of(w.eps_f16),
+                                      H(m->wqkv[layer]), H(m->bqkv[layer]), io.qkv, 3 * D, H(m->wfc1[layer]),
+                                      H(m->bfc1[layer]), io.fc1, F, rows, D));
+        for (size_t b = 0; b < rows; ++b) {
+            md_text_request* r = reqs[b];
+            MD_TRY(md_launch_sdpa_decode_fused_devpos(ctx, io.qkv + b * 3 * D, r->kc[layer], r->vc[layer], io.attn + b * D,
+                                                      w.n_heads, w.head_dim, w.max_seq, r->pos_dev, w.rot_dim,
+                                                      w.rope_theta));
+        }
+        return md_launch_gemv_dual_k(ctx, io.attn, H(m->wout[layer]), H(m->bout[layer]), D, io.fc1, H(m->wfc2[layer]),
+                                     H(m->bfc2[layer]), F, io.hidden, D, rows);
+    }
     MD_TRY(md_launch_layernorm(ctx, io.hidden, H(m->ln_w[layer]), H(m->ln_b[layer]), io.ln, rows, D, eps_of(w.eps_f16)));
     md_epilogue e_qkv;
     e_qkv.bias = H(m->bqkv[layer]);

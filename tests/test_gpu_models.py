@@ -86,6 +86,29 @@ def test_text_free_running_generation_and_graph_reuse(ctx, oracle, models_mod):
     req.close(); gpu.close()
 
 
+def test_text_fused_decode_layer_matches_unfused_kernels(ctx, models_mod):
+    """The 3-kernel decode layer (LayerNorm+qkv+fc1, attention, out-proj+fc2+residuals) against the same step
+    run as separate LayerNorm / GEMV kernels: same rounding points, so logits agree to the parity bar."""
+    w = text_weights(4006, n_layers=3, hidden=8192, vocab=4096)
+    gpu = models_mod.TextModel(ctx, w)
+    rng = np.random.default_rng(6)
+    embeds = w["wte"][rng.integers(0, 4096, 70)]
+    res = {}
+    for fused in (1, 0):
+        ctx.set_option("fused_decode", fused)
+        try:
+            req = gpu.request()
+            _, _, tok = gpu.forward(req, embeds)
+            forced = np.arange(1, 9, dtype=np.uint32) * 37 % 4096
+            res[fused] = gpu.generate(req, tok, 8, forced=forced, want_logits=True)
+            req.close()
+        finally:
+            ctx.set_option("fused_decode", 1)
+    for i in range(8):
+        assert_close_ref(res[1][1][i], res[0][1][i], f"fused vs unfused logits step {i}", rel=5e-3)
+    gpu.close()
+
+
 def test_text_batched_decode_equals_single_requests(ctx, models_mod):
     w = text_weights(4004, n_layers=2, hidden=512, vocab=2048)
     gpu = models_mod.TextModel(ctx, w)
