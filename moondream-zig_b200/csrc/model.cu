@@ -27,20 +27,36 @@ __global__ void embed_kernel(const __half* __restrict__ wte, const unsigned long
 }
 
 // End of a decode step for `batch` requests: record the sampled tokens, choose the next input
-// (teacher forcing or the sample), advance positions and the step counter.
-__global__ void advance_kernel(unsigned long long* cur_tokens, const unsigned long long* sampled, int batch,
-                               unsigned int* tokens_out, int n_steps, const unsigned int* forced, int* step,
-                               int* const* pos_ptrs) {
+// (teacher forcing or the sample), advance positions and the step counter, and gather the next
+// step's embeddings (text_model.zig:106-137) so the step needs no separate embedding kernel.
+// `sampled` holds token indices, or (keys != 0) the 64-bit argmax keys the fused lm_head leaves:
+// (ordered value << 32) | (0xFFFFFFFF - index); the keys are cleared for the next step.
+__global__ void __launch_bounds__(256)
+advance_kernel(unsigned long long* cur_tokens, unsigned long long* sampled, int keys, int batch,
+               unsigned int* tokens_out, int n_steps, const unsigned int* forced, int* step, int* const* pos_ptrs,
+               const __half* __restrict__ wte, __half* __restrict__ hidden, int dim, int vocab) {
+    __shared__ unsigned long long next_tok[8];
     const int b = threadIdx.x;
     const int s = *step;
     if (b < batch) {
-        const unsigned long long tok = sampled[b];
+        unsigned long long tok = sampled[b];
+        if (keys) {
+            tok = 0xFFFFFFFFull - (tok & 0xFFFFFFFFull);
+            sampled[b] = 0ull;
+        }
         if (s < n_steps) tokens_out[(size_t)b * n_steps + s] = (unsigned int)tok;
-        cur_tokens[b] = (forced && s < n_steps) ? (unsigned long long)forced[(size_t)b * n_steps + s] : tok;
+        const unsigned long long nxt =
+            (forced && s < n_steps) ? (unsigned long long)forced[(size_t)b * n_steps + s] : tok;
+        cur_tokens[b] = nxt;
+        next_tok[b] = nxt < (unsigned long long)vocab ? nxt : 0ull;
         *pos_ptrs[b] += 1;
     }
     __syncthreads();
     if (b == 0) *step = s + 1;
+    for (int r = 0; r < batch; ++r) {
+        const __half* src = wte + (size_t)next_tok[r] * dim;
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) hidden[(size_t)r * dim + i] = src[i];
+    }
 }
 
 __global__ void copy_logits_kernel(const __half* __restrict__ logits, __half* __restrict__ all, int vocab,
@@ -409,23 +425,30 @@ static int enqueue_decode_step(md_text_model* model, md_text_request* const* req
         explicit PdlScope(md_ctx* cc) : c(cc), old(cc->pdl) { c->pdl = 1; }
         ~PdlScope() { c->pdl = old; }
     } pdl_scope(ctx);
-    embed_kernel<<<(unsigned)batch, 256, 0, ctx->stream>>>(H(w.wte), r0->cur_token.as<unsigned long long>(),
-                                                           r0->hidden.as<__half>(), (int)w.dim, (int)w.vocab);
-    MD_LAUNCH_CHECK(ctx, "embed_kernel");
+    // hidden already holds the embeddings of the current tokens (generate_impl / the previous advance_kernel)
     const LayerIO io = io_of(r0);
     for (size_t l = 0; l < w.n_layers; ++l) MD_TRY(text_layer(model, l, io, batch, true, reqs, 0));
-    MD_TRY(text_lm_head(model, r0->hidden.as<__half>(), batch, r0->ln_last.as<__half>(), r0->logits.as<__half>(),
-                        r0->sampled.as<unsigned long long>()));
+    const bool fused_head = ctx->fused_decode && md_gemv_ln_dual_supported(batch, w.dim, w.vocab, 0);
+    if (fused_head) {
+        // final LayerNorm + lm_head + greedy argmax in one kernel (text_model.zig:325-345, sampling.zig:257-273)
+        MD_TRY(md_launch_gemv_ln_dual(ctx, r0->hidden.as<__half>(), H(w.ln_out_w), H(w.ln_out_b), eps_of(w.eps_f16),
+                                      H(w.lm_w), H(w.lm_b), r0->logits.as<__half>(), w.vocab, nullptr, nullptr, nullptr,
+                                      0, batch, w.dim, r0->sampled.as<unsigned long long>()));
+    } else {
+        MD_TRY(text_lm_head(model, r0->hidden.as<__half>(), batch, r0->ln_last.as<__half>(), r0->logits.as<__half>(),
+                            r0->sampled.as<unsigned long long>()));
+    }
     if (keep_logits) {
         copy_logits_kernel<<<32, 256, 0, ctx->stream>>>(r0->logits.as<__half>(), r0->logits_all.as<__half>(),
                                                         (int)w.vocab, r0->step.as<int>());
         MD_LAUNCH_CHECK(ctx, "copy_logits_kernel");
     }
-    advance_kernel<<<1, 32, 0, ctx->stream>>>(r0->cur_token.as<unsigned long long>(),
-                                              r0->sampled.as<unsigned long long>(), (int)batch,
-                                              r0->tokens_out.as<unsigned int>(), (int)n_steps,
-                                              forced ? r0->forced.as<unsigned int>() : nullptr, r0->step.as<int>(),
-                                              r0->pos_ptrs.as<int*>());
+    advance_kernel<<<1, 256, 0, ctx->stream>>>(r0->cur_token.as<unsigned long long>(),
+                                               r0->sampled.as<unsigned long long>(), fused_head ? 1 : 0, (int)batch,
+                                               r0->tokens_out.as<unsigned int>(), (int)n_steps,
+                                               forced ? r0->forced.as<unsigned int>() : nullptr, r0->step.as<int>(),
+                                               r0->pos_ptrs.as<int*>(), H(w.wte), r0->hidden.as<__half>(), (int)w.dim,
+                                               (int)w.vocab);
     MD_LAUNCH_CHECK(ctx, "advance_kernel");
     return MD_OK;
 }
@@ -460,6 +483,10 @@ static int generate_impl(md_text_model* model, md_text_request* const* reqs, siz
     MD_CUDA(ctx, cudaMemcpyAsync(r0->cur_token.p, cur, sizeof(cur), cudaMemcpyHostToDevice, ctx->stream));
     MD_CUDA(ctx, cudaMemcpyAsync(r0->pos_ptrs.p, pos_ptrs, sizeof(pos_ptrs), cudaMemcpyHostToDevice, ctx->stream));
     MD_CUDA(ctx, cudaMemsetAsync(r0->step.p, 0, sizeof(int), ctx->stream));
+    MD_CUDA(ctx, cudaMemsetAsync(r0->sampled.p, 0, 8 * sizeof(unsigned long long), ctx->stream));
+    embed_kernel<<<(unsigned)batch, 256, 0, ctx->stream>>>(H(w.wte), r0->cur_token.as<unsigned long long>(),
+                                                           r0->hidden.as<__half>(), (int)w.dim, (int)w.vocab);
+    MD_LAUNCH_CHECK(ctx, "embed_kernel");
     if (forced)
         MD_CUDA(ctx, cudaMemcpyAsync(r0->forced.p, forced, batch * n_steps * sizeof(unsigned int), cudaMemcpyHostToDevice,
                                      ctx->stream));
