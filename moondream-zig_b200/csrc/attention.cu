@@ -316,6 +316,10 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
     }
 }
 
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // rope.zig:50-65,223-230 for one head vector held in shared memory (f32 in, f16-rounded out).
 __device__ __forceinline__ float rope_elem(const float* x, int dd, int pos, int rot_dim, const float* tab) {
     if (dd >= rot_dim) return x[dd];
@@ -325,8 +329,13 @@ __device__ __forceinline__ float rope_elem(const float* x, int dd, int pos, int 
     return dd < half ? xr * cs.x - xi * cs.y : xr * cs.y + xi * cs.x;
 }
 
+// CLUSTER: the splits of one head form a thread-block cluster (16 CTAs along x); the partial results are
+// merged through distributed shared memory of the cluster's first CTA instead of global scratch, fences
+// and an atomic ticket.
+template <bool CLUSTER>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 sdpa_decode_kernel(DecodeParams p) {
+    __shared__ float cpart[CLUSTER ? 16 : 1][DEC_D + 2];
     __shared__ float q_s[DEC_D], knew_s[DEC_D], vnew_s[DEC_D], raw_s[DEC_D];
     __shared__ float red_m[DEC_WARPS], red_l[DEC_WARPS], red_o[DEC_WARPS][DEC_D];
     __shared__ int is_last;
@@ -338,7 +347,10 @@ sdpa_decode_kernel(DecodeParams p) {
         p.pos = *p.pos_ptr;
         p.kv_cache_len = p.pos;
         p.splits = max(1, (p.pos + DEC_KEYS - 1) / DEC_KEYS);
-        if (split >= p.splits) return;
+        if (split >= p.splits) {
+            if (CLUSTER) cluster_sync_all();  // the merging CTA waits for every CTA of the cluster
+            return;
+        }
     }
     const bool last_split = split == p.splits - 1;
     const float scale = 0.125f;  // 1/sqrt(64)
@@ -475,6 +487,32 @@ sdpa_decode_kernel(DecodeParams p) {
             O += red_o[w][tid] * f;
         }
     }
+    if (CLUSTER) {
+        // every CTA deposits (max, sum, out[64]) in slot `split` of the first CTA's shared memory
+        const uint32_t local = smem_u32(&cpart[split][0]);
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(0));
+        if (tid < DEC_D) asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (2 + tid) * 4), "f"(O) : "memory");
+        if (tid == 0) {
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(M) : "memory");
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + 4), "f"(L) : "memory");
+        }
+        cluster_sync_all();
+        if (split == 0 && tid < DEC_D) {
+            float Mg = -INFINITY;
+            for (int s2 = 0; s2 < p.splits; ++s2) Mg = fmaxf(Mg, cpart[s2][0]);
+            const float Mu = (Mg == -INFINITY) ? 0.f : Mg;
+            float Lg = 0.f, Og = 0.f;
+            for (int s2 = 0; s2 < p.splits; ++s2) {
+                const float ms = cpart[s2][0];
+                const float f = (ms == -INFINITY) ? 0.f : expf(ms - Mu);
+                Lg += cpart[s2][1] * f;
+                Og += cpart[s2][2 + tid] * f;
+            }
+            p.out[head * DEC_D + tid] = __float2half_rn(Lg > 0.f ? Og / Lg : 0.f);
+        }
+        return;
+    }
     if (p.splits == 1) {
         if (tid < DEC_D) p.out[head * DEC_D + tid] = __float2half_rn(L > 0.f ? O / L : 0.f);
         return;
@@ -583,7 +621,7 @@ static int decode_launch(md_ctx* ctx, DecodeParams& p) {
     p.counters = ctx->counters;
     p.partial = reinterpret_cast<float*>(scratch);
     dim3 grid((unsigned)p.splits, (unsigned)p.n_heads);
-    sdpa_decode_kernel<<<grid, DEC_WARPS * 32, 0, ctx->stream>>>(p);
+    sdpa_decode_kernel<false><<<grid, DEC_WARPS * 32, 0, ctx->stream>>>(p);
     MD_LAUNCH_CHECK(ctx, "sdpa_decode_kernel");
     return MD_OK;
 }
@@ -627,16 +665,39 @@ int md_launch_sdpa_decode_fused_devpos(md_ctx* ctx, const __half* qkv_row, __hal
     p.counters = ctx->counters;
     p.partial = reinterpret_cast<float*>(scratch);
     p.splits = max_splits;  // stride of the partial array; the kernel recomputes the live count
+    if (ctx->decode_cluster_ok < 0) {
+        const cudaError_t ce =
+            cudaFuncSetAttribute(sdpa_decode_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (ce != cudaSuccess) cudaGetLastError();
+        ctx->decode_cluster_ok = ce == cudaSuccess ? 1 : 0;
+    }
+    if (ctx->decode_cluster_mode >= 0) ctx->decode_cluster_ok = ctx->decode_cluster_ok && ctx->decode_cluster_mode;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)max_splits, (unsigned)p.n_heads);
     cfg.blockDim = dim3(DEC_WARPS * 32);
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    // A cluster of 16 CTAs (one per possible split) needs the non-portable cluster size; when the
+    // context could not enable it, or the cache is longer than 16 splits, the scratch-based merge runs.
+    const bool use_cluster = ctx->decode_cluster_ok && max_splits <= 16;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (use_cluster) {
+        cfg.gridDim = dim3(16u, (unsigned)p.n_heads);
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 16;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (ctx->pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = ctx->pdl ? 1 : 0;
-    const cudaError_t le = cudaLaunchKernelEx(&cfg, sdpa_decode_kernel, p);
+    cfg.numAttrs = na;
+    const cudaError_t le = use_cluster ? cudaLaunchKernelEx(&cfg, sdpa_decode_kernel<true>, p)
+                                       : cudaLaunchKernelEx(&cfg, sdpa_decode_kernel<false>, p);
     if (le != cudaSuccess) return md_fail(ctx, MD_ERR_CUDA, "launch of sdpa_decode_kernel failed: %s", cudaGetErrorString(le));
     MD_LAUNCH_CHECK(ctx, "sdpa_decode_kernel");
     return MD_OK;
@@ -756,7 +817,7 @@ extern "C" int md_sdpa_single_noalloc(const uint16_t* q, const uint16_t* k, cons
     p.splits = (int)((kv_len + DEC_KEYS - 1) / DEC_KEYS);
     p.counters = reinterpret_cast<unsigned int*>(base);
     p.partial = reinterpret_cast<float*>(base + NOALLOC_COUNTER_BYTES);
-    sdpa_decode_kernel<<<dim3((unsigned)p.splits, 32u), DEC_WARPS * 32, 0, stream>>>(p);
+    sdpa_decode_kernel<false><<<dim3((unsigned)p.splits, 32u), DEC_WARPS * 32, 0, stream>>>(p);
     e = cudaGetLastError();
     if (e != cudaSuccess)
         return noalloc_fail(MD_ERR_CUDA, err, err_cap, "md_sdpa_single_noalloc: launch failed: %s",

@@ -263,6 +263,11 @@ int md_set_option(md_ctx* ctx, const char* key, long value) {
     MD_NEED_CTX(ctx);
     MD_NEED(ctx, key, "md_set_option: null key");
     if (!strcmp(key, "gemv_variant")) { ctx->gemv_variant = (int)value; return MD_OK; }
+    if (!strcmp(key, "decode_cluster")) {
+        ctx->decode_cluster_mode = value ? 1 : 0;
+        ctx->decode_cluster_ok = -1;
+        return MD_OK;
+    }
     if (!strcmp(key, "dualk_variant")) { ctx->dualk_variant = (int)value; return MD_OK; }
     if (!strcmp(key, "fused_decode")) { ctx->fused_decode = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "pdl")) { ctx->pdl = value ? 1 : 0; return MD_OK; }

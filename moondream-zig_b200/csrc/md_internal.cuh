@@ -54,6 +54,8 @@ struct md_ctx {
     bool capturing = false;  // between md_graph_begin and md_graph_end
     int gemv_variant = 0;    // md_set_option("gemv_variant")
     int tc_block_n = 0;      // md_set_option("tc_block_n")
+    int decode_cluster_ok = -1;    // -1 unknown, 0/1: 16-CTA clusters usable for the decode attention merge
+    int decode_cluster_mode = -1;  // md_set_option("decode_cluster"): 0 forces the scratch-based merge
     int dualk_variant = 0;   // md_set_option("dualk_variant"): (warps, unroll) of gemv_dual_k_kernel
     int fused_decode = 1;    // md_set_option("fused_decode"): decode layers as 3 fused kernels
     int pdl = 0;             // md_set_option("pdl"): programmatic dependent launch for the GEMV kernels
