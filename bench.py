@@ -307,6 +307,7 @@ def main():
 
     if not args.no_extras and world == 1:
         line["extras"] = extras(ctx, torch, stream, tensor_peak, hbm_peak)
+        line["extras"].update(model_extras(ctx, torch))
     if colsplit is not None:
         line["extras"] = {"colsplit_gemm_8192": colsplit}
 
@@ -443,6 +444,85 @@ def extras(ctx, torch, stream, tensor_peak, hbm_peak):
                             "GB/s": round(algo_bytes(m, k, n) / us / 1e3, 1),
                             "frac_of_measured_tensor": round(tf / tensor_peak, 3)})
         del w
+    return out
+
+
+def model_extras(ctx, torch):
+    """End-to-end numbers of the callers around the hot path, random-init Moondream2 shapes generated on the
+    device: config 4 (prefill of 761 rows, 200 greedy decode steps, single stream and 8 batched streams)
+    and config 3 (vision encoder + projection for 1 / 5 / 13 crops)."""
+    import importlib
+    import __graft_entry__ as entry
+    models = importlib.import_module(entry.PKG_NAME + ".models")
+    g = torch.Generator(device="cuda").manual_seed(4000)
+
+    def n(*shape, std=0.02):
+        return (torch.randn(*shape, device="cuda", generator=g) * std).half()
+
+    L, D, F, V = 24, 2048, 8192, 51200
+    ones, zeros = torch.ones(D, device="cuda").half(), torch.zeros(D, device="cuda").half()
+    w = {"ln_w": [ones] * L, "ln_b": [zeros] * L,
+         "wqkv": [n(3 * D, D) for _ in range(L)], "bqkv": [n(3 * D) for _ in range(L)],
+         "wout": [n(D, D) for _ in range(L)], "bout": [n(D) for _ in range(L)],
+         "wfc1": [n(F, D) for _ in range(L)], "bfc1": [n(F) for _ in range(L)],
+         "wfc2": [n(D, F) for _ in range(L)], "bfc2": [n(D) for _ in range(L)],
+         "ln_out_w": ones, "ln_out_b": zeros, "lm_w": n(V, D), "lm_b": n(V), "wte": n(V, D)}
+    tm = models.TextModel(ctx, w)
+    embeds = w["wte"][torch.randint(0, V, (761,), device="cuda", generator=g)].cpu().numpy()
+    out = {}
+    req = tm.request()
+    for _ in range(3):
+        req.reset()
+        t0 = time.perf_counter()
+        _, _, tok = tm.forward(req, embeds, want_hidden=False, want_logits=False)
+        t1 = time.perf_counter()
+        tm.generate(req, tok, 200)
+        t2 = time.perf_counter()
+    weights_bytes = 24 * 100663296 + 209715200
+    kv_bytes = 196608 * 861   # mean kv_len over steps 762..961
+    out["text_config4"] = {
+        "prefill_761_ms": round((t1 - t0) * 1e3, 2), "decode_tok_s": round(200 / (t2 - t1), 1),
+        "us_per_token": round((t2 - t1) / 200 * 1e6, 1),
+        "hbm_GB/s": round((weights_bytes + kv_bytes) / ((t2 - t1) / 200) / 1e9, 1),
+        "note": "host wall clock around md_text_forward (H2D of the 761 embedding rows included) and md_text_generate "
+                "(200 graph replays + D2H of the tokens)"}
+    req.close()
+    reqs = [tm.request() for _ in range(8)]
+    for _ in range(2):
+        for r in reqs:
+            r.reset()
+            tm.forward(r, embeds, want_hidden=False, want_logits=False)
+        t1 = time.perf_counter()
+        tm.generate_batch(reqs, [1] * 8, 200)
+        t2 = time.perf_counter()
+    out["text_config4"]["decode_tok_s_8_streams"] = round(8 * 200 / (t2 - t1), 1)
+    for r in reqs:
+        r.close()
+    tm.close()
+    del w, tm
+    torch.cuda.empty_cache()
+
+    Lv, Dv, Fv = 27, 1152, 4304
+    onev, zerov = torch.ones(Dv, device="cuda").half(), torch.zeros(Dv, device="cuda").half()
+    vw = {"ln1_w": [onev] * Lv, "ln1_b": [zerov] * Lv, "ln2_w": [onev] * Lv, "ln2_b": [zerov] * Lv,
+          "wqkv": [n(Dv, 3 * Dv) for _ in range(Lv)], "bqkv": [n(3 * Dv) for _ in range(Lv)],
+          "wout": [n(Dv, Dv) for _ in range(Lv)], "bout": [n(Dv) for _ in range(Lv)],
+          "wfc1": [n(Dv, Fv) for _ in range(Lv)], "bfc1": [n(Fv) for _ in range(Lv)],
+          "wfc2": [n(Fv, Dv) for _ in range(Lv)], "bfc2": [n(Dv) for _ in range(Lv)],
+          "patch_w": n(588, Dv), "patch_b": n(Dv), "pos_emb": n(729, Dv), "norm_w": onev, "norm_b": zerov,
+          "proj_fc1_w": n(2 * Dv, 8192), "proj_fc1_b": n(8192), "proj_fc2_w": n(8192, 2048), "proj_fc2_b": n(2048)}
+    out["vision_config3"] = []
+    for crops in (1, 5, 13):
+        vm = models.VisionModel(ctx, vw, max_crops=crops)
+        img = np.random.default_rng(crops).integers(0, 256, (crops, 378, 378, 3), dtype=np.uint8)
+        for _ in range(4):
+            t0 = time.perf_counter()
+            vm.encode(img)
+            t1 = time.perf_counter()
+        flops = crops * 666.4e9 + 51.98e9
+        out["vision_config3"].append({"crops": crops, "ms": round((t1 - t0) * 1e3, 2),
+                                      "TFLOP/s": round(flops / (t1 - t0) / 1e12, 1)})
+        vm.close()
     return out
 
 

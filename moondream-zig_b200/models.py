@@ -30,6 +30,21 @@ class _VisW(C.Structure):
                 [(n, C.c_void_p) for n in ("patch_w", "patch_b", "pos_emb") + VIS_PER_LAYER + VIS_SINGLE])
 
 
+class _TorchBuf:
+    """A CUDA torch tensor used in place of an uploaded weight (kept alive by this wrapper)."""
+
+    def __init__(self, t):
+        self.t, self.ptr, self.shape = t, t.data_ptr(), tuple(t.shape)
+
+
+def _dev(ctx, a):
+    """numpy f16 array -> uploaded DevBuf; CUDA torch tensor (f16, contiguous) -> used in place."""
+    if hasattr(a, "data_ptr"):
+        assert a.is_cuda and a.is_contiguous() and a.element_size() == 2
+        return _TorchBuf(a)
+    return ctx.upload(np.ascontiguousarray(a, np.float16))
+
+
 def _f16_bits(v) -> int:
     return int(np.float16(v).view(np.uint16))
 
@@ -72,13 +87,13 @@ class TextModel:
         s.rope_theta, s.eps_f16 = theta, _f16_bits(eps)
         self._keep = []
         for name in TEXT_PER_LAYER:
-            bufs = [ctx.upload(np.ascontiguousarray(a, np.float16)) for a in weights[name]]
+            bufs = [_dev(ctx, a) for a in weights[name]]
             self.dev[name] = bufs
             arr = (C.c_void_p * L)(*[b.ptr for b in bufs])
             self._keep.append(arr)
             setattr(s, name, C.cast(arr, C.c_void_p))
         for name in TEXT_SINGLE:
-            b = ctx.upload(np.ascontiguousarray(weights[name], np.float16))
+            b = _dev(ctx, weights[name])
             self.dev[name] = b
             setattr(s, name, b.ptr)
         self.s = s
@@ -151,13 +166,13 @@ class VisionModel:
         s.eps_f16 = _f16_bits(eps)
         self._keep = []
         for name in VIS_PER_LAYER:
-            bufs = [ctx.upload(np.ascontiguousarray(a, np.float16)) for a in weights[name]]
+            bufs = [_dev(ctx, a) for a in weights[name]]
             self.dev[name] = bufs
             arr = (C.c_void_p * L)(*[b.ptr for b in bufs])
             self._keep.append(arr)
             setattr(s, name, C.cast(arr, C.c_void_p))
         for name in ("patch_w", "patch_b", "pos_emb") + VIS_SINGLE:
-            b = ctx.upload(np.ascontiguousarray(weights[name], np.float16))
+            b = _dev(ctx, weights[name])
             self.dev[name] = b
             setattr(s, name, b.ptr)
         self.s = s
