@@ -76,12 +76,16 @@ __global__ void __launch_bounds__(128)
 sdpa_mma_kernel(SdpaParams p) {
     constexpr int PITCH = D_PAD + 8;  // halves; 144 B or 176 B rows keep ldmatrix conflict-free
     constexpr int CHUNKS = D_PAD / 8, REAL_CHUNKS = D / 8;
-    __shared__ __align__(16) __half Qs[BQ][PITCH];
-    __shared__ __align__(16) __half Ks[BKV][PITCH];
-    __shared__ __align__(16) __half Vs[BKV][PITCH];
+    // dynamic shared memory: Q tile, then two K and two V tiles (double buffered)
+    extern __shared__ __align__(16) unsigned char sdpa_smem[];
+    __half (*Qs)[PITCH] = reinterpret_cast<__half (*)[PITCH]>(sdpa_smem);
+    __half (*Ks)[BKV][PITCH] = reinterpret_cast<__half (*)[BKV][PITCH]>(sdpa_smem + BQ * PITCH * 2);
+    __half (*Vs)[BKV][PITCH] = reinterpret_cast<__half (*)[BKV][PITCH]>(sdpa_smem + (BQ + 2 * BKV) * PITCH * 2);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int q0 = blockIdx.x * BQ, head = blockIdx.y, batch = blockIdx.z;
+    // causal: the last query blocks see the most keys; give them the lowest block ids so they start first
+    const int qblk = p.causal_pos >= 0 ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+    const int q0 = qblk * BQ, head = blockIdx.y, batch = blockIdx.z;
     const __half* qb = p.q + batch * p.q_batch + head * p.q_head;
     const __half* kb = p.k + batch * p.kv_batch + head * p.kv_head;
     const __half* vb = p.v + batch * p.kv_batch + head * p.kv_head;
@@ -112,18 +116,29 @@ sdpa_mma_kernel(SdpaParams p) {
     int kv_end = p.kv_len;
     if (p.causal_pos >= 0) kv_end = min(kv_end, p.causal_pos + min(q0 + BQ, p.q_len));
 
-    for (int k0 = 0; k0 < kv_end; k0 += BKV) {
+    // K/V tiles are double buffered: the loads of tile j+1 are in flight while tile j is consumed
+    auto load_tile = [&](int k0, int buf) {
         for (int idx = tid; idx < BKV * CHUNKS; idx += 128) {
             const int r = idx / CHUNKS, c = idx % CHUNKS;
             if (k0 + r < p.kv_len && c < REAL_CHUNKS) {
-                cp_async16(smem_u32(&Ks[r][c * 8]), kb + (long long)(k0 + r) * p.kv_row + c * 8);
-                cp_async16(smem_u32(&Vs[r][c * 8]), vb + (long long)(k0 + r) * p.kv_row + c * 8);
+                cp_async16(smem_u32(&Ks[buf][r][c * 8]), kb + (long long)(k0 + r) * p.kv_row + c * 8);
+                cp_async16(smem_u32(&Vs[buf][r][c * 8]), vb + (long long)(k0 + r) * p.kv_row + c * 8);
             } else {
-                *reinterpret_cast<uint4*>(&Ks[r][c * 8]) = make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(&Vs[r][c * 8]) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(&Ks[buf][r][c * 8]) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(&Vs[buf][r][c * 8]) = make_uint4(0, 0, 0, 0);
             }
         }
-        cp_async_wait_all();
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (kv_end > 0) load_tile(0, 0);
+    for (int k0 = 0, it = 0; k0 < kv_end; k0 += BKV, ++it) {
+        const int buf = it & 1;
+        if (k0 + BKV < kv_end) {
+            load_tile(k0 + BKV, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
         __syncthreads();
 
         float s[BKV / 8][4];
@@ -135,7 +150,7 @@ sdpa_mma_kernel(SdpaParams p) {
             for (int np = 0; np < BKV / 16; ++np) {
                 uint32_t b0, b1, b2, b3;
                 const int r = np * 16 + (lane & 7) + (lane >> 4) * 8, c = ks * 16 + ((lane >> 3) & 1) * 8;
-                ldsm_x4(smem_u32(&Ks[r][c]), b0, b1, b2, b3);
+                ldsm_x4(smem_u32(&Ks[buf][r][c]), b0, b1, b2, b3);
                 mma_16816(s[2 * np], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
                 mma_16816(s[2 * np + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
             }
@@ -198,7 +213,7 @@ sdpa_mma_kernel(SdpaParams p) {
             for (int dp = 0; dp < D_PAD / 16; ++dp) {
                 uint32_t b0, b1, b2, b3;
                 const int r = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = dp * 16 + (lane >> 4) * 8;
-                ldsm_x4_t(smem_u32(&Vs[r][c]), b0, b1, b2, b3);
+                ldsm_x4_t(smem_u32(&Vs[buf][r][c]), b0, b1, b2, b3);
                 mma_16816(o[2 * dp], a0, a1, a2, a3, b0, b1);
                 mma_16816(o[2 * dp + 1], a0, a1, a2, a3, b2, b3);
             }
@@ -600,8 +615,16 @@ int md_launch_sdpa(md_ctx* ctx, const __half* q, const __half* k, const __half* 
                         (o_row % 2 == 0) && (o_head % 2 == 0) && (o_batch % 2 == 0);
     if ((d == 64 || d == 72) && vec_ok) {
         dim3 grid((unsigned)((q_len + BQ - 1) / BQ), (unsigned)n_heads, (unsigned)batch);
-        if (d == 64) sdpa_mma_kernel<64, 64><<<grid, 128, 0, ctx->stream>>>(p);
-        else sdpa_mma_kernel<72, 80><<<grid, 128, 0, ctx->stream>>>(p);
+        // Q + 2 x (K, V) tiles of 64 rows; above the 48 KB default for d = 72, so opt in once
+        const int smem64 = (BQ + 4 * BKV) * (64 + 8) * 2, smem72 = (BQ + 4 * BKV) * (80 + 8) * 2;
+        static bool attr_set = false;
+        if (!attr_set) {
+            MD_CUDA(ctx, cudaFuncSetAttribute(sdpa_mma_kernel<64, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem64));
+            MD_CUDA(ctx, cudaFuncSetAttribute(sdpa_mma_kernel<72, 80>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem72));
+            attr_set = true;
+        }
+        if (d == 64) sdpa_mma_kernel<64, 64><<<grid, 128, smem64, ctx->stream>>>(p);
+        else sdpa_mma_kernel<72, 80><<<grid, 128, smem72, ctx->stream>>>(p);
         MD_LAUNCH_CHECK(ctx, "sdpa_mma_kernel");
         return MD_OK;
     }
