@@ -613,6 +613,14 @@ int md_launch_sdpa(md_ctx* ctx, const __half* q, const __half* k, const __half* 
     const bool vec_ok = aligned(q, q_row, q_head, q_batch) && aligned(k, kv_row, kv_head, kv_batch) &&
                         aligned(v, kv_row, kv_head, kv_batch) && (reinterpret_cast<uintptr_t>(out) % 4 == 0) &&
                         (o_row % 2 == 0) && (o_head % 2 == 0) && (o_batch % 2 == 0);
+    // tcgen05 path (attention_tc.cu) for the shapes with enough rows to fill its 128-query tiles
+    if (ctx->attn_tc != 0 && q_len > 0 && kv_len > 0 &&
+        md_sdpa_tc_supported(q, k, v, out, d, q_row, q_head, q_batch, kv_row, kv_head, kv_batch, o_row, o_head, o_batch,
+                             n_heads, batch) &&
+        (ctx->attn_tc == 1 || q_len > 64))
+        return md_launch_sdpa_tc(ctx, q, k, v, mask, out, n_heads, q_len, kv_len, d, q_row, q_head, kv_row, kv_head, o_row,
+                                 o_head, batch, q_batch, kv_batch, o_batch, causal_pos);
+    if (ctx->attn_tc == 1) return md_fail(ctx, MD_ERR_UNSUPPORTED, "attn_tc forced but the operands are not addressable");
     if ((d == 64 || d == 72) && vec_ok) {
         dim3 grid((unsigned)((q_len + BQ - 1) / BQ), (unsigned)n_heads, (unsigned)batch);
         // Q + 2 x (K, V) tiles of 64 rows; above the 48 KB default for d = 72, so opt in once

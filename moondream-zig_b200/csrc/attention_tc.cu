@@ -1,0 +1,475 @@
+// Multi-query attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
+//
+// Replaces attention.multiMasklessSDPA (attention.zig:125-234: ViT, 729 tokens, d = 72) and
+// attention.multiMaskedSDPA (attention.zig:416-541: decoder prefill, d = 64, causal) for the layouts
+// TMA can address; sdpa_mma_kernel (attention.cu) remains the path for everything else.
+//
+// One CTA = 128 queries of one (batch, head), 192 threads, two CTAs per SM:
+//   warp 0      TMA producer: Q once, then K and V tiles of 64 keys through a ring of stages.
+//   warp 1      one lane issues tcgen05.mma: S = Q K^T (128 x 64 x d into one of two S buffers in TMEM)
+//               and O += P V (128 x d x 64, accumulated in TMEM over all key tiles);
+//               tcgen05.commit signals completion.
+//   warps 2..5  one thread per query row: tcgen05.ld of its S row, mask / running max / exp2 in f32
+//               registers (no shuffles: a row lives in one thread), P written as f16 into one of two
+//               128B-swizzled shared-memory buffers (the A operand of the PV MMA).
+// O stays in TMEM.  The exponent reference of a row moves only when the row maximum has grown by more
+// than 2^8 since it was last set; only then do the softmax warps rescale that row of O in TMEM (rare
+// after the first tiles), so the usual tile costs one TMEM read of S and no read of O.  P therefore
+// holds values up to 2^8, well inside f16, and the row sum is kept in f32 on the same reference.
+// The issuer runs S(j+1) ahead of PV(j): the tensor pipe works on the next scores while the softmax
+// warps process tile j, and the second CTA of the SM fills the remaining gaps.
+//
+// Operands are addressed through 4-D tensor maps (d, row, head, batch) whose extents are exactly the
+// valid data, so everything outside (rows past kv_len, dims past d) is zero-filled by TMA: no stale
+// cache rows or neighbouring heads ever reach the tensor cores.
+// d = 72: dims 0-63 travel as a 128B-swizzled tile, dims 64-79 (64-71 data, the rest zero fill) as a
+// second, 32B-swizzled tile of 16 dims; S takes one more k-step over the tail and the PV product one
+// more MMA with N = 16.
+//
+// Numerics as the reference: scores, probability sums and the output accumulate in f32, one rounding
+// to f16 at the end (attention.zig:199-202,505-508); P is rounded to f16 for the PV product.
+// Every mbarrier wait is bounded (tc_common.cuh); a wait that gives up is reported through the
+// context's error word and the kernel still runs to its end and frees its TMEM.
+#include "md_internal.cuh"
+#include "tc_common.cuh"
+
+int md_make_map_4d(md_ctx* ctx, CUtensorMap* map, const void* ptr, const uint64_t dims[4], const uint64_t strides_bytes[3],
+                   uint32_t box0, const uint32_t box_d[3], int swizzle_bytes);
+
+namespace {
+
+using namespace tc;
+
+constexpr int ABQ = 128, ABKV = 64;
+constexpr float LOG2E_F = 1.4426950408889634f;
+constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units a row maximum may grow before O is rescaled
+
+struct AttnTcParams {
+    int q_len, kv_len, causal_pos;
+    float scale_log2;
+    const uint8_t* mask;  // [q_len, kv_len] or null
+    __half* out;
+    long long o_row, o_head, o_batch;
+    // 4-D tensor maps (dim 0 = head dimension d; dims 1..3 = row, head, batch in order of ascending stride):
+    // which map dimension carries the row / head / batch index, for q and for k, v
+    int q_dim_row, q_dim_head, q_dim_batch, kv_dim_row, kv_dim_head, kv_dim_batch;
+};
+
+struct AttnTcMaps {
+    CUtensorMap q, k, v;     // dims 0-63, 128B swizzle
+    CUtensorMap qt, kt, vt;  // dims 64-79 (d = 72 only), 32B swizzle
+};
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int D> struct AttnCfg {
+    static constexpr bool TAIL = D > 64;                     // a 16-dim, 32B-swizzled second tile
+    static constexpr int DPAD = TAIL ? 80 : 64;              // MMA extent of the head dimension
+    static constexpr int STAGES = TAIL ? 2 : 3;              // K/V ring depth
+    static constexpr int Q_MAIN = ABQ * 128, Q_TAIL = TAIL ? ABQ * 32 : 0;
+    static constexpr int KV_MAIN = ABKV * 128, KV_TAIL = TAIL ? ABKV * 32 : 0;
+    static constexpr int Q_BYTES = Q_MAIN + Q_TAIL;
+    static constexpr int STAGE_BYTES = 2 * (KV_MAIN + KV_TAIL);  // K main | V main | K tail | V tail
+    static constexpr int P_BYTES = ABQ * 128;                // 128 rows x 64 keys f16, two buffers
+    static constexpr int SMEM = 1024 + Q_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES + 256;  // 97.25 / 93.25 KB
+};
+
+template <int D>
+__global__ void __launch_bounds__(192, 2)
+attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflags* flags) {
+    using Cfg = AttnCfg<D>;
+    constexpr int ST = Cfg::STAGES;
+    constexpr bool TAIL = Cfg::TAIL;
+    constexpr uint32_t TMEM_COLS = 256;          // S0 @0, S1 @64, O @128 (64 or 80 columns)
+    constexpr uint32_t T_O = 128;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw);
+    const uint32_t sm_q = base, sm_qt = sm_q + Cfg::Q_MAIN;
+    const uint32_t sm_kv = sm_q + Cfg::Q_BYTES;   // per stage: K main | V main | K tail | V tail
+    const uint32_t sm_p = sm_kv + ST * Cfg::STAGE_BYTES;
+    uint8_t* p_ptr = base_ptr + Cfg::Q_BYTES + ST * Cfg::STAGE_BYTES;
+    const uint32_t bars = sm_p + 2 * Cfg::P_BYTES;
+    uint8_t* bars_ptr = p_ptr + 2 * Cfg::P_BYTES;
+    const uint32_t b_qfull = bars, b_kvfull = bars + 8, b_kvempty = b_kvfull + 8 * ST;
+    const uint32_t b_sfull = b_kvempty + 8 * ST, b_sempty = b_sfull + 16, b_pfull = b_sempty + 16;
+    const uint32_t b_pempty = b_pfull + 16;      // ends at bars + 8 + 16 * ST + 64 <= bars + 120
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_ptr + 128);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 132);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y, batch = blockIdx.z;
+    // causal: the last query blocks see the most keys; they get the lowest block ids and start first
+    const int qblk = p.causal_pos >= 0 ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+    const int q0 = qblk * ABQ;
+    int kv_end = p.kv_len;
+    if (p.causal_pos >= 0) kv_end = min(kv_end, p.causal_pos + min(q0 + ABQ, p.q_len));
+    const int nt = (kv_end + ABKV - 1) / ABKV;
+
+    if (threadIdx.x == 0) {
+        mbar_init(b_qfull, 1);
+        for (int s = 0; s < ST; ++s) {
+            mbar_init(b_kvfull + 8 * s, 1);
+            mbar_init(b_kvempty + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(b_sfull + 8 * b, 1);
+            mbar_init(b_sempty + 8 * b, 4);
+            mbar_init(b_pfull + 8 * b, 4);
+            mbar_init(b_pempty + 8 * b, 1);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(const_cast<uint32_t*>(tmem_slot))),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int cq[4] = {0, 0, 0, 0}, ck[4] = {0, 0, 0, 0};
+            cq[p.q_dim_row] = q0; cq[p.q_dim_head] = head; cq[p.q_dim_batch] = batch;
+            ck[p.kv_dim_head] = head; ck[p.kv_dim_batch] = batch;
+            mbar_expect_tx(b_qfull, Cfg::Q_BYTES);
+            tma_load_4d(sm_q, &tm.q, b_qfull, 0, cq[1], cq[2], cq[3]);
+            if (TAIL) tma_load_4d(sm_qt, &tm.qt, b_qfull, 64, cq[1], cq[2], cq[3]);
+            for (int j = 0; j < nt; ++j) {
+                const int st = j % ST;
+                mbar_wait(b_kvempty + 8 * st, (uint32_t)((j / ST) & 1) ^ 1u, abort_flag, flags, 11);
+                const uint32_t full = b_kvfull + 8 * st, dst = sm_kv + st * Cfg::STAGE_BYTES;
+                mbar_expect_tx(full, Cfg::STAGE_BYTES);
+                ck[p.kv_dim_row] = j * ABKV;
+                tma_load_4d(dst, &tm.k, full, 0, ck[1], ck[2], ck[3]);
+                tma_load_4d(dst + Cfg::KV_MAIN, &tm.v, full, 0, ck[1], ck[2], ck[3]);
+                if (TAIL) {
+                    tma_load_4d(dst + 2 * Cfg::KV_MAIN, &tm.kt, full, 64, ck[1], ck[2], ck[3]);
+                    tma_load_4d(dst + 2 * Cfg::KV_MAIN + Cfg::KV_TAIL, &tm.vt, full, 64, ck[1], ck[2], ck[3]);
+                }
+            }
+            if (*abort_flag) {  // let copies in flight land before the CTA's shared memory is released
+                const unsigned long long t0 = global_ns();
+                while (global_ns() - t0 < 500000ull) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc_s = (1u << 4) | ((uint32_t)(ABKV >> 3) << 17) | ((uint32_t)(ABQ >> 4) << 24);
+            const uint32_t idesc_pv = (1u << 4) | (1u << 16) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(ABQ >> 4) << 24);
+            const uint32_t idesc_pvt = (1u << 4) | (1u << 16) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(ABQ >> 4) << 24);
+            auto issue_pv = [&](int i) {
+                const int st = i % ST, pb = i & 1;
+                const uint32_t v_main = sm_kv + st * Cfg::STAGE_BYTES + Cfg::KV_MAIN;
+                const uint32_t v_tail = sm_kv + st * Cfg::STAGE_BYTES + 2 * Cfg::KV_MAIN + Cfg::KV_TAIL;
+                mbar_wait(b_pfull + 8 * pb, (uint32_t)((i >> 1) & 1), abort_flag, flags, 12);
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < ABKV / 16; ++ks) {
+                    const uint64_t da = make_desc(sm_p + pb * Cfg::P_BYTES + ks * 32, 16, 1024);
+                    const uint32_t acc = (i > 0 || ks > 0) ? 1u : 0u;
+                    // V is the MN-major B operand: 64 dims contiguous per key, 16 keys = 2048 B per k-step
+                    tc_mma_f16(tmem_base + T_O, da, make_desc(v_main + ks * (16 * 128), ABKV * 128, 1024), idesc_pv, acc);
+                    if (TAIL)  // 16 dims contiguous per key (32B swizzle), 16 keys = 512 B per k-step
+                        tc_mma_f16(tmem_base + T_O + 64, da, make_desc_sw(v_tail + ks * (16 * 32), 512, 256, 6),
+                                   idesc_pvt, acc);
+                }
+                tc_commit(b_pempty + 8 * pb);
+                tc_commit(b_kvempty + 8 * st);
+            };
+            mbar_wait(b_qfull, 0, abort_flag, flags, 14);
+            for (int j = 0; j < nt; ++j) {
+                const int st = j % ST, sb = j & 1;
+                const uint32_t k_main = sm_kv + st * Cfg::STAGE_BYTES, k_tail = k_main + 2 * Cfg::KV_MAIN;
+                mbar_wait(b_kvfull + 8 * st, (uint32_t)((j / ST) & 1), abort_flag, flags, 15);
+                mbar_wait(b_sempty + 8 * sb, (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, flags, 16);
+                tc_fence_after();
+                const uint32_t t_s = tmem_base + (uint32_t)(sb * 64);
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)
+                    tc_mma_f16(t_s, make_desc(sm_q + ks * 32, 16, 1024), make_desc(k_main + ks * 32, 16, 1024), idesc_s,
+                               ks > 0 ? 1u : 0u);
+                if (TAIL)
+                    tc_mma_f16(t_s, make_desc_sw(sm_qt, 16, 256, 6), make_desc_sw(k_tail, 16, 256, 6), idesc_s, 1u);
+                tc_commit(b_sfull + 8 * sb);
+                if (j > 0) issue_pv(j - 1);
+            }
+            if (nt > 0) issue_pv(nt - 1);
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax + output (warps 2..5)
+        const int quad = warp & 3, row = quad * 32 + lane, qi = q0 + row;
+        const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const bool row_ok = qi < p.q_len;
+        float m_run = -INFINITY, l_run = 0.f;  // exponent reference (log2 units) and row sum on that reference
+
+        for (int j = 0; j < nt; ++j) {
+            const int sb = j & 1, key0 = j * ABKV;
+            mbar_wait(b_sfull + 8 * sb, (uint32_t)((j >> 1) & 1), abort_flag, flags, 19);
+            tc_fence_after();
+            uint32_t s0[32], s1[32];
+            tc_ld_32x32(t_lane + (uint32_t)(sb * 64), s0);
+            tc_ld_32x32(t_lane + (uint32_t)(sb * 64 + 32), s1);
+            tc_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(b_sempty + 8 * sb);
+
+            // tiles wholly inside the valid, visible region (all but the last ones) skip the per-key tests
+            const bool interior = !p.mask && key0 + ABKV <= p.kv_len &&
+                                  (p.causal_pos < 0 || key0 + ABKV - 1 <= p.causal_pos + q0 + quad * 32);
+            if (!interior) {
+#pragma unroll
+                for (int e = 0; e < 64; ++e) {
+                    const int key = key0 + e;
+                    bool vis = row_ok && key < p.kv_len;
+                    if (p.causal_pos >= 0) vis = vis && key <= p.causal_pos + qi;
+                    if (vis && p.mask) vis = p.mask[(long long)qi * p.kv_len + key] != 0;
+                    if (!vis) {
+                        if (e < 32) s0[e] = 0xff800000u; else s1[e - 32] = 0xff800000u;  // -inf
+                    }
+                }
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+                mx0 = fmaxf(mx0, __uint_as_float(s0[e]));
+                mx1 = fmaxf(mx1, __uint_as_float(s0[e + 1]));
+                mx2 = fmaxf(mx2, __uint_as_float(s1[e]));
+                mx3 = fmaxf(mx3, __uint_as_float(s1[e + 1]));
+            }
+            const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;  // -inf stays -inf (scale > 0)
+
+            if (j == 0) {
+                m_run = mt;
+            } else if (__any_sync(0xffffffffu, mt > m_run + RESCALE_THRESHOLD)) {
+                // move this warp's rows to their new maxima: O(row) *= 2^(old - new), once PV(j-1) has landed
+                const float m_new = fmaxf(m_run, mt);
+                const float corr = (m_new == -INFINITY) ? 1.f : ex2_fast(m_run - m_new);
+                l_run *= corr;
+                m_run = m_new;
+                mbar_wait(b_pempty + 8 * ((j - 1) & 1), (uint32_t)(((j - 1) >> 1) & 1), abort_flag, flags, 21);
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < Cfg::DPAD / 16; ++c) {
+                    uint32_t r[16];
+                    tc_ld_32x16(t_lane + T_O + c * 16, r);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * corr);
+                    tc_st_32x16(t_lane + T_O + c * 16, r);
+                }
+                tc_wait_st();
+                tc_fence_before();
+            }
+            const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+
+            float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+            uint32_t pk[32];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                const float a0 = ex2_fast(fmaf(__uint_as_float(s0[2 * e]), p.scale_log2, neg_m));
+                const float a1 = ex2_fast(fmaf(__uint_as_float(s0[2 * e + 1]), p.scale_log2, neg_m));
+                const float b0 = ex2_fast(fmaf(__uint_as_float(s1[2 * e]), p.scale_log2, neg_m));
+                const float b1 = ex2_fast(fmaf(__uint_as_float(s1[2 * e + 1]), p.scale_log2, neg_m));
+                rs0 += a0; rs1 += a1; rs2 += b0; rs3 += b1;
+                const __half2 ha = __floats2half2_rn(a0, a1), hb = __floats2half2_rn(b0, b1);
+                pk[e] = *reinterpret_cast<const uint32_t*>(&ha);
+                pk[16 + e] = *reinterpret_cast<const uint32_t*>(&hb);
+            }
+            l_run += (rs0 + rs1) + (rs2 + rs3);
+
+            // P buffer sb is free once PV(j-2) has consumed it
+            mbar_wait(b_pempty + 8 * sb, (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, flags, 20);
+            uint8_t* prow = p_ptr + sb * Cfg::P_BYTES + row * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) * 16)) =
+                    make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            fence_async_smem();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(b_pfull + 8 * sb);
+        }
+
+        if (nt > 0) {
+            mbar_wait(b_pempty + 8 * ((nt - 1) & 1), (uint32_t)(((nt - 1) >> 1) & 1), abort_flag, flags, 18);
+            tc_fence_after();
+        }
+        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+        __half* orow = p.out + batch * p.o_batch + head * p.o_head + (long long)qi * p.o_row;
+#pragma unroll
+        for (int c = 0; c < Cfg::DPAD / 16; ++c) {
+            uint32_t r[16];
+            if (nt > 0) {
+                tc_ld_32x16(t_lane + T_O + c * 16, r);
+                tc_wait_ld();
+            } else {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) r[e] = 0u;
+            }
+            if (row_ok) {
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    if (c * 16 + g * 8 < D) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __half2 h = __floats2half2_rn(__uint_as_float(r[g * 8 + 2 * e]) * inv,
+                                                                __uint_as_float(r[g * 8 + 2 * e + 1]) * inv);
+                            w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                        }
+                        *reinterpret_cast<uint4*>(orow + c * 16 + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                     : "memory");
+    }
+}
+
+}  // namespace
+
+namespace {
+
+// Orders (row, head, batch) by ascending stride for a 4-D tensor map whose dim 0 is the head dimension.
+// An extent of 1 never moves, so its stride is free: it goes last with a stride past everything else.
+struct MapPlan {
+    uint64_t dims[4], strides_bytes[3];
+    int dim_of[3];  // map dimension (1..3) of row, head, batch
+};
+
+bool plan_map(MapPlan& mp, size_t d, const size_t extent[3], const size_t stride[3]) {
+    int order[3] = {0, 1, 2};
+    auto key = [&](int r) { return extent[r] == 1 ? ~0ull : (unsigned long long)stride[r]; };
+    for (int i = 0; i < 3; ++i)
+        for (int j = i + 1; j < 3; ++j)
+            if (key(order[j]) < key(order[i])) { int t = order[i]; order[i] = order[j]; order[j] = t; }
+    mp.dims[0] = d;
+    unsigned long long next_free = (d + 7) / 8 * 8;  // stride (elements) that clears every dimension placed so far
+    for (int i = 0; i < 3; ++i) {
+        const int r = order[i];
+        unsigned long long st = extent[r] == 1 ? next_free : (unsigned long long)stride[r];
+        if (st == 0 || (st % 8) != 0 || st * 2 >= (1ull << 40) || extent[r] == 0 || extent[r] > (1ull << 31)) return false;
+        mp.dims[i + 1] = extent[r];
+        mp.strides_bytes[i] = st * 2;
+        mp.dim_of[r] = i + 1;
+        const unsigned long long span = st * extent[r];
+        if (span > next_free) next_free = (span + 7) / 8 * 8;
+    }
+    return true;
+}
+
+template <int D>
+int launch_attn_tc(md_ctx* ctx, const AttnTcMaps& maps, const AttnTcParams& p, dim3 grid) {
+    auto kern = attn_tc_kernel<D>;
+    const uint32_t cfg_bit = 1u << (D == 64 ? 8 : 9);
+    if (!(ctx->tc_configured & cfg_bit)) {
+        MD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<D>::SMEM));
+        ctx->tc_configured |= cfg_bit;
+    }
+    kern<<<grid, 192, AttnCfg<D>::SMEM, ctx->stream>>>(maps, p, ctx->flags);
+    MD_LAUNCH_CHECK(ctx, "attn_tc_kernel");
+    return MD_OK;
+}
+
+}  // namespace
+
+// True when the tcgen05 attention can address these operands: d = 64 or 72, 16-byte aligned bases and strides.
+bool md_sdpa_tc_supported(const void* q, const void* k, const void* v, const void* out, size_t d, size_t q_row,
+                          size_t q_head, size_t q_batch, size_t kv_row, size_t kv_head, size_t kv_batch, size_t o_row,
+                          size_t o_head, size_t o_batch, size_t n_heads, size_t batch) {
+    if (d != 64 && d != 72) return false;
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+         reinterpret_cast<uintptr_t>(out)) & 15)
+        return false;
+    const size_t st[] = {q_row, kv_row, o_row, n_heads > 1 ? q_head : 8, n_heads > 1 ? kv_head : 8,
+                         n_heads > 1 ? o_head : 8, batch > 1 ? q_batch : 8, batch > 1 ? kv_batch : 8,
+                         batch > 1 ? o_batch : 8};
+    for (size_t s : st)
+        if (s == 0 || (s % 8) != 0) return false;
+    return n_heads <= 65535 && batch <= 65535;
+}
+
+int md_launch_sdpa_tc(md_ctx* ctx, const __half* q, const __half* k, const __half* v, const uint8_t* mask, __half* out,
+                      size_t n_heads, size_t q_len, size_t kv_len, size_t d, size_t q_row, size_t q_head, size_t kv_row,
+                      size_t kv_head, size_t o_row, size_t o_head, size_t batch, size_t q_batch, size_t kv_batch,
+                      size_t o_batch, int causal_pos) {
+    if (!md_sdpa_tc_supported(q, k, v, out, d, q_row, q_head, q_batch, kv_row, kv_head, kv_batch, o_row, o_head, o_batch,
+                              n_heads, batch))
+        return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 attention needs d = 64 or 72 and 16-byte aligned operands");
+    MapPlan mq, mk;
+    const size_t eq[3] = {q_len, n_heads, batch}, sq[3] = {q_row, q_head, q_batch};
+    const size_t ek[3] = {kv_len, n_heads, batch}, sk[3] = {kv_row, kv_head, kv_batch};
+    if (!plan_map(mq, d, eq, sq) || !plan_map(mk, d, ek, sk))
+        return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 attention: strides not addressable by a tensor map");
+    AttnTcMaps maps;
+    uint32_t boxq[3] = {1, 1, 1}, boxk[3] = {1, 1, 1};
+    boxq[mq.dim_of[0] - 1] = ABQ;
+    boxk[mk.dim_of[0] - 1] = ABKV;
+    MD_TRY(md_make_map_4d(ctx, &maps.q, q, mq.dims, mq.strides_bytes, 64, boxq, 128));
+    MD_TRY(md_make_map_4d(ctx, &maps.k, k, mk.dims, mk.strides_bytes, 64, boxk, 128));
+    MD_TRY(md_make_map_4d(ctx, &maps.v, v, mk.dims, mk.strides_bytes, 64, boxk, 128));
+    if (d > 64) {
+        MD_TRY(md_make_map_4d(ctx, &maps.qt, q, mq.dims, mq.strides_bytes, 16, boxq, 32));
+        MD_TRY(md_make_map_4d(ctx, &maps.kt, k, mk.dims, mk.strides_bytes, 16, boxk, 32));
+        MD_TRY(md_make_map_4d(ctx, &maps.vt, v, mk.dims, mk.strides_bytes, 16, boxk, 32));
+    } else {
+        maps.qt = maps.q; maps.kt = maps.k; maps.vt = maps.v;
+    }
+    AttnTcParams p;
+    p.q_len = (int)q_len; p.kv_len = (int)kv_len; p.causal_pos = causal_pos;
+    p.scale_log2 = (1.0f / sqrtf((float)d)) * LOG2E_F;
+    p.mask = mask; p.out = out;
+    p.o_row = (long long)o_row; p.o_head = (long long)o_head; p.o_batch = (long long)o_batch;
+    p.q_dim_row = mq.dim_of[0]; p.q_dim_head = mq.dim_of[1]; p.q_dim_batch = mq.dim_of[2];
+    p.kv_dim_row = mk.dim_of[0]; p.kv_dim_head = mk.dim_of[1]; p.kv_dim_batch = mk.dim_of[2];
+    dim3 grid((unsigned)((q_len + ABQ - 1) / ABQ), (unsigned)n_heads, (unsigned)batch);
+    return d == 64 ? launch_attn_tc<64>(ctx, maps, p, grid) : launch_attn_tc<72>(ctx, maps, p, grid);
+}

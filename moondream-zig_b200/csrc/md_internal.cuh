@@ -59,6 +59,7 @@ struct md_ctx {
     int dualk_variant = 0;   // md_set_option("dualk_variant"): (warps, unroll) of gemv_dual_k_kernel
     int fused_decode = 1;    // md_set_option("fused_decode"): decode layers as 3 fused kernels
     int pdl = 0;             // md_set_option("pdl"): programmatic dependent launch for the GEMV kernels
+    int attn_tc = -1;        // md_set_option("attn_tc"): -1 auto, 0 mma.sync attention only, 1 tcgen05 attention only
 };
 
 int md_fail(md_ctx* ctx, int status, const char* fmt, ...);
@@ -145,6 +146,14 @@ int md_launch_sdpa(md_ctx* ctx, const __half* q, const __half* k, const __half* 
                    // strides in elements: q/out row stride and head stride, k/v row stride and head stride
                    size_t q_row, size_t q_head, size_t kv_row, size_t kv_head, size_t o_row, size_t o_head,
                    size_t batch, size_t q_batch, size_t kv_batch, size_t o_batch, int causal_pos);
+// attention_tc.cu: the same contract on tcgen05 tensor cores (d = 64 or 72, 16-byte aligned operands)
+bool md_sdpa_tc_supported(const void* q, const void* k, const void* v, const void* out, size_t d, size_t q_row,
+                          size_t q_head, size_t q_batch, size_t kv_row, size_t kv_head, size_t kv_batch, size_t o_row,
+                          size_t o_head, size_t o_batch, size_t n_heads, size_t batch);
+int md_launch_sdpa_tc(md_ctx* ctx, const __half* q, const __half* k, const __half* v, const uint8_t* mask, __half* out,
+                      size_t n_heads, size_t q_len, size_t kv_len, size_t d, size_t q_row, size_t q_head, size_t kv_row,
+                      size_t kv_head, size_t o_row, size_t o_head, size_t batch, size_t q_batch, size_t kv_batch,
+                      size_t o_batch, int causal_pos);
 int md_launch_sdpa_single(md_ctx* ctx, const __half* q, const __half* k, const __half* v, const uint8_t* mask,
                           __half* out, size_t kv_len);
 int md_launch_sdpa_decode_fused(md_ctx* ctx, const __half* qkv_row, __half* kc, __half* vc, __half* out,
