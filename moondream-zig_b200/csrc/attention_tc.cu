@@ -5,7 +5,7 @@
 // TMA can address; sdpa_mma_kernel (attention.cu) remains the path for everything else.
 //
 // One CTA = 128 queries of one (batch, head), 192 threads, two CTAs per SM:
-//   warp 0      TMA producer: Q once, then K and V tiles of 64 keys through a ring of stages.
+//   warp 0      TMA producer: Q once, then K and V tiles of 64 keys through their own rings of stages.
 //   warp 1      one lane issues tcgen05.mma: S = Q K^T (128 x 64 x d into one of two S buffers in TMEM)
 //               and O += P V (128 x d x 64, accumulated in TMEM over all key tiles);
 //               tcgen05.commit signals completion.
@@ -95,13 +95,13 @@ __device__ __forceinline__ float ex2_fast(float x) {
 template <int D> struct AttnCfg {
     static constexpr bool TAIL = D > 64;                     // a 16-dim, 32B-swizzled second tile
     static constexpr int DPAD = TAIL ? 80 : 64;              // MMA extent of the head dimension
-    static constexpr int STAGES = TAIL ? 2 : 3;              // K/V ring depth
+    static constexpr int STAGES = TAIL ? 2 : 3;              // depth of the K ring and of the V ring
     static constexpr int Q_MAIN = ABQ * 128, Q_TAIL = TAIL ? ABQ * 32 : 0;
     static constexpr int KV_MAIN = ABKV * 128, KV_TAIL = TAIL ? ABKV * 32 : 0;
     static constexpr int Q_BYTES = Q_MAIN + Q_TAIL;
-    static constexpr int STAGE_BYTES = 2 * (KV_MAIN + KV_TAIL);  // K main | V main | K tail | V tail
+    static constexpr int STAGE_BYTES = KV_MAIN + KV_TAIL;    // one K (or V) tile: main | tail
     static constexpr int P_BYTES = ABQ * 128;                // 128 rows x 64 keys f16, two buffers
-    static constexpr int SMEM = 1024 + Q_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES + 256;  // 97.25 / 93.25 KB
+    static constexpr int SMEM = 1024 + Q_BYTES + 2 * STAGES * STAGE_BYTES + 2 * P_BYTES + 256;  // 97.25 / 93.25 KB
 };
 
 template <int D>
@@ -117,16 +117,19 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - raw);
     const uint32_t sm_q = base, sm_qt = sm_q + Cfg::Q_MAIN;
-    const uint32_t sm_kv = sm_q + Cfg::Q_BYTES;   // per stage: K main | V main | K tail | V tail
-    const uint32_t sm_p = sm_kv + ST * Cfg::STAGE_BYTES;
-    uint8_t* p_ptr = base_ptr + Cfg::Q_BYTES + ST * Cfg::STAGE_BYTES;
+    // K and V travel through separate rings: a K stage is free again as soon as S(j) has been computed,
+    // a V stage only after PV(j), two MMAs later; one shared ring would hold the next K load back
+    const uint32_t sm_k = sm_q + Cfg::Q_BYTES, sm_v = sm_k + ST * Cfg::STAGE_BYTES;  // per stage: main | tail
+    const uint32_t sm_p = sm_v + ST * Cfg::STAGE_BYTES;
+    uint8_t* p_ptr = base_ptr + Cfg::Q_BYTES + 2 * ST * Cfg::STAGE_BYTES;
     const uint32_t bars = sm_p + 2 * Cfg::P_BYTES;
     uint8_t* bars_ptr = p_ptr + 2 * Cfg::P_BYTES;
-    const uint32_t b_qfull = bars, b_kvfull = bars + 8, b_kvempty = b_kvfull + 8 * ST;
-    const uint32_t b_sfull = b_kvempty + 8 * ST, b_sempty = b_sfull + 16, b_pfull = b_sempty + 16;
-    const uint32_t b_pempty = b_pfull + 16;      // ends at bars + 8 + 16 * ST + 64 <= bars + 120
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_ptr + 128);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 132);
+    const uint32_t b_qfull = bars, b_kfull = bars + 8, b_kempty = b_kfull + 8 * ST, b_vfull = b_kempty + 8 * ST;
+    const uint32_t b_vempty = b_vfull + 8 * ST;
+    const uint32_t b_sfull = b_vempty + 8 * ST, b_sempty = b_sfull + 16, b_pfull = b_sempty + 16;
+    const uint32_t b_pempty = b_pfull + 16;      // ends at bars + 8 + 32 * ST + 64 <= bars + 168
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_ptr + 176);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 180);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y, batch = blockIdx.z;
@@ -140,8 +143,10 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
     if (threadIdx.x == 0) {
         mbar_init(b_qfull, 1);
         for (int s = 0; s < ST; ++s) {
-            mbar_init(b_kvfull + 8 * s, 1);
-            mbar_init(b_kvempty + 8 * s, 1);
+            mbar_init(b_kfull + 8 * s, 1);
+            mbar_init(b_kempty + 8 * s, 1);
+            mbar_init(b_vfull + 8 * s, 1);
+            mbar_init(b_vempty + 8 * s, 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(b_sfull + 8 * b, 1);
@@ -175,16 +180,18 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
             if (TAIL) tma_load_4d(sm_qt, &tm.qt, b_qfull, 64, cq[1], cq[2], cq[3]);
             for (int j = 0; j < nt; ++j) {
                 const int st = j % ST;
-                mbar_wait(b_kvempty + 8 * st, (uint32_t)((j / ST) & 1) ^ 1u, abort_flag, flags, 11);
-                const uint32_t full = b_kvfull + 8 * st, dst = sm_kv + st * Cfg::STAGE_BYTES;
-                mbar_expect_tx(full, Cfg::STAGE_BYTES);
+                const uint32_t par = (uint32_t)((j / ST) & 1) ^ 1u;
                 ck[p.kv_dim_row] = j * ABKV;
-                tma_load_4d(dst, &tm.k, full, 0, ck[1], ck[2], ck[3]);
-                tma_load_4d(dst + Cfg::KV_MAIN, &tm.v, full, 0, ck[1], ck[2], ck[3]);
-                if (TAIL) {
-                    tma_load_4d(dst + 2 * Cfg::KV_MAIN, &tm.kt, full, 64, ck[1], ck[2], ck[3]);
-                    tma_load_4d(dst + 2 * Cfg::KV_MAIN + Cfg::KV_TAIL, &tm.vt, full, 64, ck[1], ck[2], ck[3]);
-                }
+                mbar_wait(b_kempty + 8 * st, par, abort_flag, flags, 11);
+                const uint32_t kfull = b_kfull + 8 * st, kdst = sm_k + st * Cfg::STAGE_BYTES;
+                mbar_expect_tx(kfull, Cfg::STAGE_BYTES);
+                tma_load_4d(kdst, &tm.k, kfull, 0, ck[1], ck[2], ck[3]);
+                if (TAIL) tma_load_4d(kdst + Cfg::KV_MAIN, &tm.kt, kfull, 64, ck[1], ck[2], ck[3]);
+                mbar_wait(b_vempty + 8 * st, par, abort_flag, flags, 10);
+                const uint32_t vfull = b_vfull + 8 * st, vdst = sm_v + st * Cfg::STAGE_BYTES;
+                mbar_expect_tx(vfull, Cfg::STAGE_BYTES);
+                tma_load_4d(vdst, &tm.v, vfull, 0, ck[1], ck[2], ck[3]);
+                if (TAIL) tma_load_4d(vdst + Cfg::KV_MAIN, &tm.vt, vfull, 64, ck[1], ck[2], ck[3]);
             }
             if (*abort_flag) {  // let copies in flight land before the CTA's shared memory is released
                 const unsigned long long t0 = global_ns();
@@ -199,8 +206,8 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
             const uint32_t idesc_pvt = (1u << 4) | (1u << 16) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(ABQ >> 4) << 24);
             auto issue_pv = [&](int i) {
                 const int st = i % ST, pb = i & 1;
-                const uint32_t v_main = sm_kv + st * Cfg::STAGE_BYTES + Cfg::KV_MAIN;
-                const uint32_t v_tail = sm_kv + st * Cfg::STAGE_BYTES + 2 * Cfg::KV_MAIN + Cfg::KV_TAIL;
+                const uint32_t v_main = sm_v + st * Cfg::STAGE_BYTES, v_tail = v_main + Cfg::KV_MAIN;
+                mbar_wait(b_vfull + 8 * st, (uint32_t)((i / ST) & 1), abort_flag, flags, 13);
                 mbar_wait(b_pfull + 8 * pb, (uint32_t)((i >> 1) & 1), abort_flag, flags, 12);
                 tc_fence_after();
 #pragma unroll
@@ -214,13 +221,13 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
                                    idesc_pvt, acc);
                 }
                 tc_commit(b_pempty + 8 * pb);
-                tc_commit(b_kvempty + 8 * st);
+                tc_commit(b_vempty + 8 * st);
             };
             mbar_wait(b_qfull, 0, abort_flag, flags, 14);
             for (int j = 0; j < nt; ++j) {
                 const int st = j % ST, sb = j & 1;
-                const uint32_t k_main = sm_kv + st * Cfg::STAGE_BYTES, k_tail = k_main + 2 * Cfg::KV_MAIN;
-                mbar_wait(b_kvfull + 8 * st, (uint32_t)((j / ST) & 1), abort_flag, flags, 15);
+                const uint32_t k_main = sm_k + st * Cfg::STAGE_BYTES, k_tail = k_main + Cfg::KV_MAIN;
+                mbar_wait(b_kfull + 8 * st, (uint32_t)((j / ST) & 1), abort_flag, flags, 15);
                 mbar_wait(b_sempty + 8 * sb, (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, flags, 16);
                 tc_fence_after();
                 const uint32_t t_s = tmem_base + (uint32_t)(sb * 64);
@@ -231,6 +238,7 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
                 if (TAIL)
                     tc_mma_f16(t_s, make_desc_sw(sm_qt, 16, 256, 6), make_desc_sw(k_tail, 16, 256, 6), idesc_s, 1u);
                 tc_commit(b_sfull + 8 * sb);
+                tc_commit(b_kempty + 8 * st);
                 if (j > 0) issue_pv(j - 1);
             }
             if (nt > 0) issue_pv(nt - 1);
