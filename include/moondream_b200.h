@@ -84,7 +84,15 @@ int md_set_gemm_mode(md_ctx* ctx, int mode);
  *   "tc_block_n"    0 = automatic, 64 / 128 / 256 = fixed tile width of the tcgen05 GEMM
  *   "pdl"           1 = launch the GEMV kernels with programmatic dependent launch: a kernel starts
  *                   streaming its weights while its predecessor on the stream drains.  Only for streams
- *                   on which no earlier kernel writes the weight matrices (registered weights). */
+ *                   on which no earlier kernel writes the weight matrices (registered weights).
+ *   "fused_decode"  1 (default) = a decode layer runs as three fused kernels, 0 = one kernel per reference op
+ *   "dualk_variant" 0..4 = (warps, unroll) of the out-proj + fc2 kernel of the fused decode layer
+ *   "decode_cluster" 0 = merge the decode attention splits through global scratch instead of a CTA cluster
+ *   "attn_tc"       -1 (default) = tcgen05 attention when the operands allow it and q_len > 64,
+ *                   0 = mma.sync attention only, 1 = tcgen05 only (MD_ERR_UNSUPPORTED otherwise)
+ *   "persistent_decode" 1 = a decode step runs as one cooperative persistent kernel (default 0: measured
+ *                   slower than the three-kernel layers on B200, kept as an alternative)
+ *   "persist_trace" 1 = md_text_generate prints the phase timings of the persistent step to stderr */
 int md_set_option(md_ctx* ctx, const char* key, long value);
 
 /* ---- CUDA graphs -------------------------------------------------------------------

@@ -312,7 +312,6 @@ struct DecodeParams {
     int splits;
     const float* rope_tab;  // fused: (cos, sin) table [positions][rot_dim/2][2] (rope.zig:32-128)
     const int* pos_ptr;     // fused + graph replay: position read from device memory, else null
-    md_prefetch pf;         // weights of the kernel after this one (this kernel leaves HBM nearly idle)
 };
 
 __device__ __forceinline__ uint4 ldg_nc16(const void* p) {
@@ -357,7 +356,6 @@ sdpa_decode_kernel(DecodeParams p) {
     __shared__ int is_last;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int head = blockIdx.y, split = blockIdx.x;
-    if (warp == 0) md_issue_l2_prefetch(p.pf, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y, lane, 32);
     if (p.pos_ptr) {
         // Position held in device memory (graph replay): the grid is sized for the longest
         // context, CTAs beyond the splits this position needs leave at once.
@@ -692,8 +690,6 @@ int md_launch_sdpa_decode_fused_devpos(md_ctx* ctx, const __half* qkv_row, __hal
     p.n_heads = (int)n_heads; p.fused = 1; p.rot_dim = (int)rot_dim; p.theta = theta;
     MD_TRY(md_rope_cached(ctx, rot_dim, theta, max_seq, &p.rope_tab));
     p.pos_ptr = pos_dev;
-    p.pf = ctx->next_prefetch;
-    ctx->next_prefetch = md_prefetch();
     const int max_splits = (int)((max_seq + DEC_KEYS - 1) / DEC_KEYS);
     void* scratch = nullptr;
     MD_TRY(md_scratch(ctx, (size_t)p.n_heads * max_splits * (DEC_D + 2) * sizeof(float), &scratch));

@@ -26,11 +26,12 @@ struct md_persist_params {
     unsigned long long* amax;  // [M] greedy-argmax keys (value, then lower index), zero before the step
     float* att_scratch;        // [M][32][max_splits][66] partial (max, sum, out[64]) of the attention splits
     unsigned int* att_counters;  // [M * 32] arrival tickets, zero before and after the step
-    unsigned int* grid_counter;  // grid barrier, zero before the step
+    unsigned int* grid_counter;  // [4] grid barriers, zero before the step
     const float* rope_tab;     // [max_seq][16][2] (cos, sin)
     int M, n_layers, vocab, max_seq, max_splits;
     float eps;
     md_devflags* flags;
+    unsigned long long* trace;  // optional [2][256] timestamps (ns) of the first and last CTA, for tuning
 };
 
 // True when the model has the geometry the kernel is specialised for.

@@ -78,7 +78,6 @@ struct LnDualParams {
     __half* out2;                    // [M][n2]
     int n1, n2, M;
     unsigned long long* amax;        // optional [M]: running argmax keys of out1 (greedy sampling), see below
-    md_prefetch pf;                  // weights of the kernel after this one
 };
 
 // MM = compile-time bound on the number of activation rows (1, 2, 4 or 8): keeps the register
@@ -110,7 +109,6 @@ gemv_ln_dual_kernel(LnDualParams p) {
     }
     // LayerNorm parameters are weights too
     const uint4 gw = ldg_stream(p.ln_w + tid * 8), gb = ldg_stream(p.ln_b + tid * 8);
-    if (warp == 0) md_issue_l2_prefetch(p.pf, blockIdx.x, gridDim.x, lane, 32);
     pdl_wait();
 
     // ---- LayerNorm of the M rows into shared memory (two-pass f32, one f16 rounding)
@@ -247,7 +245,6 @@ struct DualKParams {
     const __half *x2, *w2, *b2;   // [M][k2], [N][k2], [N]
     __half* hidden;               // [M][N], updated in place
     int N, k1, k2, M;
-    md_prefetch pf;               // weights of the kernel after this one
 };
 
 template <int DK_WARPS, int UNROLL>
@@ -280,11 +277,7 @@ gemv_dual_k_kernel(DualKParams p) {
                 lo[j] = hi[j] = make_uint4(0, 0, 0, 0);
             }
         }
-        if (!waited) {
-            if (warp == 0) md_issue_l2_prefetch(p.pf, blockIdx.x, gridDim.x, lane, 32);
-            pdl_wait();
-            waited = true;
-        }
+        if (!waited) { pdl_wait(); waited = true; }
 #pragma unroll
         for (int j = 0; j < UNROLL; ++j) {
             const int u = u0 + j * DK_WARPS;
@@ -365,8 +358,6 @@ int md_launch_gemv_ln_dual(md_ctx* ctx, const __half* hidden, const __half* ln_w
     p.w1 = w1; p.b1 = b1; p.out1 = out1; p.w2 = w2; p.b2 = b2; p.out2 = out2;
     p.n1 = (int)n1; p.n2 = (int)n2; p.M = (int)M;
     p.amax = amax;
-    p.pf = ctx->next_prefetch;
-    ctx->next_prefetch = md_prefetch();
     const unsigned grid = (unsigned)((n1 + n2) / 16);
     if (M == 1) return launch_pdl(ctx, gemv_ln_dual_kernel<1>, grid, LN_WARPS * 32, p, "gemv_ln_dual_kernel");
     if (M == 2) return launch_pdl(ctx, gemv_ln_dual_kernel<2>, grid, LN_WARPS * 32, p, "gemv_ln_dual_kernel");
@@ -386,8 +377,6 @@ int md_launch_gemv_dual_k(md_ctx* ctx, const __half* x1, const __half* w1, const
     DualKParams p;
     p.x1 = x1; p.w1 = w1; p.b1 = b1; p.x2 = x2; p.w2 = w2; p.b2 = b2; p.hidden = hidden;
     p.N = (int)N; p.k1 = (int)k1; p.k2 = (int)k2; p.M = (int)M;
-    p.pf = ctx->next_prefetch;
-    ctx->next_prefetch = md_prefetch();
     const unsigned grid = (unsigned)((N + 7) / 8);
     switch (ctx->dualk_variant) {
         case 1: return launch_pdl(ctx, gemv_dual_k_kernel<16, 5>, grid, 16 * 32, p, "gemv_dual_k_kernel");

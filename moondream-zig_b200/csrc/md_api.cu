@@ -271,8 +271,8 @@ int md_set_option(md_ctx* ctx, const char* key, long value) {
     if (!strcmp(key, "dualk_variant")) { ctx->dualk_variant = (int)value; return MD_OK; }
     if (!strcmp(key, "fused_decode")) { ctx->fused_decode = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "pdl")) { ctx->pdl = value ? 1 : 0; return MD_OK; }
+    if (!strcmp(key, "persist_trace")) { ctx->persist_trace = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "persistent_decode")) { ctx->persistent_decode = value ? 1 : 0; return MD_OK; }
-    if (!strcmp(key, "l2_prefetch")) { ctx->l2_prefetch = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "attn_tc")) { ctx->attn_tc = value < 0 ? -1 : value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "tc_block_n")) {
         MD_NEED(ctx, value == 0 || value == 64 || value == 128 || value == 256, "tc_block_n must be 0, 64, 128 or 256");

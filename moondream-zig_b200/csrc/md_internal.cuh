@@ -16,37 +16,6 @@
 
 // Device-side error word: bit 0 = a bounded wait gave up.  One word per context,
 // zeroed at md_init and re-zeroed by md_sync after it has been reported.
-// Weights the NEXT kernel of a decode step will stream: the current kernel asks the TMA unit to pull
-// them into L2 (fire and forget), so HBM keeps working through this kernel's own fill and drain phases
-// and through the attention kernel, which leaves HBM nearly idle.  Two ranges (e.g. out-proj and fc2).
-struct md_prefetch {
-    const void* ptr[2] = {nullptr, nullptr};
-    unsigned long long bytes[2] = {0, 0};  // multiples of 16; 0 = none
-};
-#ifdef __CUDACC__
-// Called by `nthreads` threads (tid 0..nthreads-1) of every CTA; CTA `cta` of `nctas` covers its own
-// contiguous share of each range in 4 KB bulk prefetches.  Ranges start 16-byte aligned.
-__device__ __forceinline__ void md_issue_l2_prefetch(const md_prefetch& pf, unsigned cta, unsigned nctas, unsigned tid,
-                                                     unsigned nthreads) {
-    constexpr unsigned long long CH = 4096;
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const unsigned long long bytes = pf.bytes[i];
-        if (bytes == 0) continue;
-        const unsigned long long chunks = (bytes + CH - 1) / CH, per = (chunks + nctas - 1) / nctas;
-        const unsigned long long c0 = per * cta, c1 = c0 + per < chunks ? c0 + per : chunks;
-        for (unsigned long long c = c0 + tid; c < c1; c += nthreads) {
-            const unsigned long long off = c * CH;
-            const unsigned sz = (unsigned)((bytes - off < CH ? bytes - off : CH) & ~15ull);
-            if (sz)
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(static_cast<const char*>(pf.ptr[i]) + off),
-                             "r"(sz)
-                             : "memory");
-        }
-    }
-}
-#endif
-
 struct md_devflags {
     unsigned int error;
     unsigned int where;  // site id of the first wait that gave up
@@ -90,9 +59,8 @@ struct md_ctx {
     int dualk_variant = 0;   // md_set_option("dualk_variant"): (warps, unroll) of gemv_dual_k_kernel
     int fused_decode = 1;    // md_set_option("fused_decode"): decode layers as 3 fused kernels
     int pdl = 0;             // md_set_option("pdl"): programmatic dependent launch for the GEMV kernels
+    int persist_trace = 0;      // md_set_option("persist_trace"): print phase timings of the persistent step (tuning aid)
     int persistent_decode = 0;  // md_set_option("persistent_decode"): one persistent kernel per decode step
-    int l2_prefetch = 0;     // md_set_option("l2_prefetch"): decode kernels request the next kernel's weights into L2
-    md_prefetch next_prefetch;  // consumed (and cleared) by the next launch of a kernel that can issue it
     int attn_tc = -1;        // md_set_option("attn_tc"): -1 auto, 0 mma.sync attention only, 1 tcgen05 attention only
 };
 

@@ -40,7 +40,7 @@ advance_kernel(unsigned long long* cur_tokens, unsigned long long* sampled, int 
     __shared__ unsigned long long next_tok[8];
     const int b = threadIdx.x;
     const int s = *step;
-    if (grid_counter && b == 0) *grid_counter = 0u;  // the persistent step's barrier starts every step at zero
+    if (grid_counter && b < 4) grid_counter[b] = 0u;  // the persistent step's barriers start every step at zero
     if (b < batch) {
         unsigned long long tok = sampled[b];
         if (keys) {
@@ -177,29 +177,12 @@ int text_layer(md_text_model* m, size_t layer, const LayerIO& io, size_t rows, b
     const size_t D = w.dim, F = w.hidden;
     if (decode && ctx->fused_decode && md_gemv_ln_dual_supported(rows, D, 3 * D, F) &&
         md_gemv_dual_k_supported(rows, D, D, F)) {
-        // Three kernels per layer: [LayerNorm + qkv + fc1] -> attention -> [out-proj + fc2 + residuals].
-        // Each asks for the weights of the one after it to be pulled into L2 while it runs: the first for
-        // out-proj + fc2 of this layer, the attention (HBM nearly idle) for qkv + fc1 of the next layer
-        // (or the head of lm_head after the last layer).
-        const bool pf_on = ctx->l2_prefetch != 0;
-        if (pf_on) {
-            ctx->next_prefetch.ptr[0] = m->wout[layer]; ctx->next_prefetch.bytes[0] = D * D * 2;
-            ctx->next_prefetch.ptr[1] = m->wfc2[layer]; ctx->next_prefetch.bytes[1] = D * F * 2;
-        }
+        // Three kernels per layer: [LayerNorm + qkv + fc1] -> attention -> [out-proj + fc2 + residuals]
         MD_TRY(md_launch_gemv_ln_dual(ctx, io.hidden, H(m->ln_w[layer]), H(m->ln_b[layer]), eps_of(w.eps_f16),
                                       H(m->wqkv[layer]), H(m->bqkv[layer]), io.qkv, 3 * D, H(m->wfc1[layer]),
                                       H(m->bfc1[layer]), io.fc1, F, rows, D));
         for (size_t b = 0; b < rows; ++b) {
             md_text_request* r = reqs[b];
-            if (pf_on && b == 0) {
-                if (layer + 1 < w.n_layers) {
-                    ctx->next_prefetch.ptr[0] = m->wqkv[layer + 1]; ctx->next_prefetch.bytes[0] = 3 * D * D * 2;
-                    ctx->next_prefetch.ptr[1] = m->wfc1[layer + 1]; ctx->next_prefetch.bytes[1] = D * F * 2;
-                } else {
-                    ctx->next_prefetch.ptr[0] = w.lm_w;
-                    ctx->next_prefetch.bytes[0] = std::min<size_t>(w.vocab * D * 2, (size_t)64 << 20);
-                }
-            }
             MD_TRY(md_launch_sdpa_decode_fused_devpos(ctx, io.qkv + b * 3 * D, r->kc[layer], r->vc[layer], io.attn + b * D,
                                                       w.n_heads, w.head_dim, w.max_seq, r->pos_dev, w.rot_dim,
                                                       w.rope_theta));
@@ -466,6 +449,7 @@ static int enqueue_decode_step(md_text_model* model, md_text_request* const* req
         pp.max_splits = (int)((w.max_seq + 31) / 32);
         pp.eps = eps_of(w.eps_f16);
         pp.flags = ctx->flags;
+        pp.trace = ctx->persist_trace ? reinterpret_cast<unsigned long long*>(r0->persist_ctr.as<unsigned int>() + 264) : nullptr;
         MD_TRY(md_launch_decode_persistent(ctx, pp));
     } else {
         for (size_t l = 0; l < w.n_layers; ++l) MD_TRY(text_layer(model, l, io, batch, true, reqs, 0));
@@ -554,9 +538,9 @@ static int generate_impl(md_text_model* model, md_text_request* const* reqs, siz
         for (size_t b = 0; b < batch; ++b) tab.pos[b] = reqs[b]->pos_dev;
         MD_TRY(r0->persist_tab.ensure(ctx, sizeof(tab)));
         MD_TRY(r0->persist_scratch.ensure(ctx, md_decode_persistent_scratch_bytes(8, w.max_seq)));
-        MD_TRY(r0->persist_ctr.ensure(ctx, 260 * sizeof(unsigned int)));
+        MD_TRY(r0->persist_ctr.ensure(ctx, (264 + 1024) * sizeof(unsigned int)));
         MD_CUDA(ctx, cudaMemcpyAsync(r0->persist_tab.p, &tab, sizeof(tab), cudaMemcpyHostToDevice, ctx->stream));
-        MD_CUDA(ctx, cudaMemsetAsync(r0->persist_ctr.p, 0, 260 * sizeof(unsigned int), ctx->stream));
+        MD_CUDA(ctx, cudaMemsetAsync(r0->persist_ctr.p, 0, (264 + 1024) * sizeof(unsigned int), ctx->stream));
         MD_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // tab is a stack object
         r0->persist_batch = batch;
     }
@@ -599,6 +583,23 @@ static int generate_impl(md_text_model* model, md_text_request* const* reqs, siz
         MD_CUDA(ctx, cudaMemcpyAsync(logits_out, r0->logits_all.p, n_steps * w.vocab * 2, cudaMemcpyDeviceToHost,
                                      ctx->stream));
     const int st = md_check_flags(ctx);
+    if (ctx->persist_trace && r0->persist_batch == batch && st == MD_OK) {
+        // tuning aid: phase durations (us) of the last step on the first and last CTA, layers averaged
+        std::vector<unsigned long long> tr(512);
+        cudaMemcpy(tr.data(), r0->persist_ctr.as<unsigned int>() + 264, 512 * 8, cudaMemcpyDeviceToHost);
+        static const char* names[7] = {"ln", "phaseA", "wait_qkv", "attn", "wait_fc1", "phaseC", "sync_hidden"};
+        for (int which = 0; which < 2; ++which) {
+            const unsigned long long* t = tr.data() + which * 256;
+            double acc[7] = {0};
+            for (size_t l = 0; l < w.n_layers; ++l)
+                for (int k = 0; k < 7; ++k) acc[k] += (double)(t[1 + l * 7 + k] - t[l * 7 + k]);
+            fprintf(stderr, "[persist_trace] cta %s:", which ? "last" : "0");
+            for (int k = 0; k < 7; ++k) fprintf(stderr, " %s %.2f", names[k], acc[k] / w.n_layers / 1e3);
+            const size_t e = w.n_layers * 7;
+            fprintf(stderr, " | head_ln %.2f head %.2f total %.1f us\n", (t[e + 1] - t[e]) / 1e3,
+                    (t[e + 2] - t[e + 1]) / 1e3, (t[e + 2] - t[0]) / 1e3);
+        }
+    }
     if (graph && batch != 1) md_graph_destroy(ctx, graph);
     return st;
 }
