@@ -190,25 +190,65 @@ def main():
     ctx.set_option("pdl", 1)
 
     ws_h, xs_h = make_inputs()
-    ws = [torch.from_numpy(w).cuda() for w in ws_h]
+    # every one of the 20 problems owns its weight matrix, as in the reference's benchmark (a fresh B per case):
+    # 1.24 GB of distinct weights per step, so no byte can be served twice from L2 inside a step either
+    ws0 = [torch.from_numpy(w).cuda() for w in ws_h]
+    wsm = {(m, i): (ws0[i] if m == MS[0] else torch.roll(ws0[i], shifts=m, dims=0).contiguous())
+           for m in MS for i in range(len(SHAPES))}
     xs = {key: torch.from_numpy(x).cuda() for key, x in xs_h.items()}
     ys = {(m, i): torch.empty((m, n), dtype=torch.float16, device="cuda") for m in MS for i, (k, n) in enumerate(SHAPES)}
 
     def sweep():
         for m in MS:
             for i, (k, n) in enumerate(SHAPES):
-                ctx.hgemm_nt(xs[(m, i)].data_ptr(), ws[i].data_ptr(), m, n, k, out=ys[(m, i)].data_ptr())
+                ctx.hgemm_nt(xs[(m, i)].data_ptr(), wsm[(m, i)].data_ptr(), m, n, k, out=ys[(m, i)].data_ptr())
 
     # one eager pass (sets up everything), a parity spot check against torch f32, then capture
     sweep()
     ctx.sync()
     for key in [(1, 0), (8, 4)]:
-        ref = xs[key].float() @ ws[key[1]].float().T
+        ref = xs[key].float() @ wsm[key].float().T
         err = (ys[key].float() - ref).abs().max().item()
         assert err <= 1e-2 * ref.abs().max().item(), f"parity check failed for {key}: {err}"
+    # The 20 products of a sweep are independent problems with their own operands.  They are recorded as
+    # SWEEP_BRANCHES parallel chains of one graph (fork / join with events inside the capture), so that the launch
+    # gaps and drain phases of one chain are filled by the other chains' memory traffic; inside a chain
+    # consecutive launches stay programmatically dependent.  Launches are dealt to the chains largest first.
+    branches = max(1, int(os.environ.get("BENCH_SWEEP_BRANCHES", SWEEP_BRANCHES)))
+    order = sorted(((m, i) for m in MS for i in range(len(SHAPES))), key=lambda mi: -SHAPES[mi[1]][0] * SHAPES[mi[1]][1])
+    chains, load = [[] for _ in range(branches)], [0] * branches
+    for m, i in order:
+        b = load.index(min(load))
+        chains[b].append((m, i))
+        load[b] += SHAPES[i][0] * SHAPES[i][1]
+    side = [torch.cuda.Stream() for _ in range(branches - 1)]
+
+    def sweep_branched():
+        fork = torch.cuda.Event()
+        fork.record(stream)
+        joins = []
+        for b, chain in enumerate(chains):
+            st = stream if b == 0 else side[b - 1]
+            if b:
+                st.wait_event(fork)
+                ctx.set_stream(st.cuda_stream)
+            for m, i in chain:
+                k, n = SHAPES[i]
+                ctx.hgemm_nt(xs[(m, i)].data_ptr(), wsm[(m, i)].data_ptr(), m, n, k, out=ys[(m, i)].data_ptr())
+            if b:
+                ev = torch.cuda.Event()
+                ev.record(st)
+                joins.append(ev)
+                ctx.set_stream(stream.cuda_stream)
+        for ev in joins:
+            stream.wait_event(ev)
+
     n0 = ctx.launch_count()
     ctx.graph_begin()
-    sweep()
+    if branches > 1:
+        sweep_branched()
+    else:
+        sweep()
     graph = ctx.graph_end()
     launches_per_step = ctx.launch_count() - n0
 
@@ -249,7 +289,7 @@ def main():
     def e2e_sweep():
         for m in MS:
             for i, (k, n) in enumerate(SHAPES):
-                st = ctx.lib.md_hgemm_nt(ctx.h, pin_x[(m, i)].data_ptr(), ws[i].data_ptr(), pin_y[(m, i)].data_ptr(),
+                st = ctx.lib.md_hgemm_nt(ctx.h, pin_x[(m, i)].data_ptr(), wsm[(m, i)].data_ptr(), pin_y[(m, i)].data_ptr(),
                                          m, n, k)
                 if st != 0:
                     raise RuntimeError(ctx.lib.md_last_error(ctx.h).decode())
@@ -273,7 +313,7 @@ def main():
     e2e_val = world * STEP_BYTES / (t.item() / e2e_steps) / 1e9
     h2d = sum(m * k * 2 for m in MS for k, n in SHAPES)
     d2h = sum(m * n * 2 for m in MS for k, n in SHAPES)
-    err = (pin_y[(8, 4)].float() - (xs[(8, 4)].float() @ ws[4].float().T).cpu()).abs().max().item()
+    err = (pin_y[(8, 4)].float() - (xs[(8, 4)].float() @ wsm[(8, 4)].float().T).cpu()).abs().max().item()
     assert err < 0.2, f"e2e parity check failed: {err}"
 
     colsplit = None
@@ -294,7 +334,7 @@ def main():
         "data": "synthetic",
         "config": {"workload": "decode GEMV sweep: M in {1,2,4,8} x Phi-1.5 layer shapes (BASELINE config 2)",
                    "bytes_per_step": STEP_BYTES, "launches_per_step": launches_per_step,
-                   "l2": "inputs larger than L2 (1.24 GB per step, every weight reused only after 310 MB of other traffic)",
+                   "l2": "inputs larger than L2: 20 distinct weight matrices, 1.24 GB per step, each read once per step",
                    "replay": "one CUDA graph per step", "parallelism": f"replicas x{world}"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                      "traffic": TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": peak_kind, "kernel": "gemv_nt_mma_kernel",
@@ -338,6 +378,7 @@ def main():
 # profiles/gemv_nt_mma_kernel__decode_gemv_sweep.md: 280.41 MB measured over the three captured launches
 # (fc1, fc2, lm_head at M = 1) against 276.97 MB of algorithmic bytes, a factor of 1.0124; traffic grows in
 # proportion to the weight bytes, so the average launch of the sweep is scaled by the same factor.
+SWEEP_BRANCHES = 4  # parallel chains the sweep graph is recorded as
 TRAFFIC_BYTES_PER_LAUNCH = int(round(1.0124 * STEP_BYTES / 20))
 
 
