@@ -78,6 +78,7 @@ struct LnDualParams {
     __half* out2;                    // [M][n2]
     int n1, n2, M;
     unsigned long long* amax;        // optional [M]: running argmax keys of out1 (greedy sampling), see below
+    int gelu1;                       // GELU on segment 1 as well (fc1 alone as segment 1)
 };
 
 // MM = compile-time bound on the number of activation rows (1, 2, 4 or 8): keeps the register
@@ -218,7 +219,7 @@ gemv_ln_dual_kernel(LnDualParams p) {
             for (int w = 0; w < LN_WARPS; ++w) sum += partial[w][r][m];
             float val = md_round_f16(sum);
             val = md_round_f16(val + __half2float((seg2 ? p.b2 : p.b1)[n]));
-            if (seg2) val = md_round_f16(md_gelu_f32(val));
+            if (seg2 || p.gelu1) val = md_round_f16(md_gelu_f32(val));
             (seg2 ? p.out2 : p.out1)[(size_t)m * n_seg + n] = __float2half_rn(val);
             // Greedy sampling folded into the lm_head (sampling.zig:257-273: first strict maximum of the f16
             // logits): a 64-bit key orders by value, then by LOWER index; one atomicMax per CTA and row.
@@ -331,11 +332,20 @@ int launch_pdl(md_ctx* ctx, Kern kern, unsigned grid, unsigned block, const Para
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(block);
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (ctx->pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (ctx->launch_priority) {
+        attr[na].id = cudaLaunchAttributePriority;
+        attr[na].val.priority = ctx->launch_priority;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    cfg.numAttrs = na;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
     if (e != cudaSuccess) return md_fail(ctx, MD_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e));
     ctx->launches++;
@@ -350,7 +360,8 @@ bool md_gemv_ln_dual_supported(size_t M, size_t K, size_t n1, size_t n2) {
 
 int md_launch_gemv_ln_dual(md_ctx* ctx, const __half* hidden, const __half* ln_w, const __half* ln_b, float eps,
                            const __half* w1, const __half* b1, __half* out1, size_t n1, const __half* w2,
-                           const __half* b2, __half* out2, size_t n2, size_t M, size_t K, unsigned long long* amax) {
+                           const __half* b2, __half* out2, size_t n2, size_t M, size_t K, unsigned long long* amax,
+                           bool gelu1) {
     if (!md_gemv_ln_dual_supported(M, K, n1, n2))
         return md_fail(ctx, MD_ERR_UNSUPPORTED, "gemv_ln_dual: unsupported shape M=%zu K=%zu n1=%zu n2=%zu", M, K, n1, n2);
     LnDualParams p;
@@ -358,6 +369,7 @@ int md_launch_gemv_ln_dual(md_ctx* ctx, const __half* hidden, const __half* ln_w
     p.w1 = w1; p.b1 = b1; p.out1 = out1; p.w2 = w2; p.b2 = b2; p.out2 = out2;
     p.n1 = (int)n1; p.n2 = (int)n2; p.M = (int)M;
     p.amax = amax;
+    p.gelu1 = gelu1 ? 1 : 0;
     const unsigned grid = (unsigned)((n1 + n2) / 16);
     if (M == 1) return launch_pdl(ctx, gemv_ln_dual_kernel<1>, grid, LN_WARPS * 32, p, "gemv_ln_dual_kernel");
     if (M == 2) return launch_pdl(ctx, gemv_ln_dual_kernel<2>, grid, LN_WARPS * 32, p, "gemv_ln_dual_kernel");

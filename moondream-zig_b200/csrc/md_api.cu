@@ -174,6 +174,10 @@ int md_init(md_ctx** out, int device) {
     };
     if (cudaSetDevice(device) != cudaSuccess) return bail("cudaSetDevice");
     if (cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess) return bail("stream");
+    {
+        int least = 0, greatest = 0;
+        if (cudaDeviceGetStreamPriorityRange(&least, &greatest) == cudaSuccess) ctx->prio_high = greatest;
+    }
     ctx->stream = ctx->own_stream;
     if (cudaMalloc(&ctx->flags, sizeof(md_devflags)) != cudaSuccess) return bail("cudaMalloc flags");
     if (cudaMemset(ctx->flags, 0, sizeof(md_devflags)) != cudaSuccess) return bail("cudaMemset flags");
@@ -197,6 +201,9 @@ int md_destroy(md_ctx* ctx) {
     if (ctx->rope_tab) cudaFree(ctx->rope_tab);
     if (ctx->flags) cudaFree(ctx->flags);
     if (ctx->flags_host) cudaFreeHost(ctx->flags_host);
+    if (ctx->side_stream) cudaStreamDestroy(ctx->side_stream);
+    if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
+    if (ctx->ev_side) cudaEventDestroy(ctx->ev_side);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
     return MD_OK;
@@ -271,6 +278,7 @@ int md_set_option(md_ctx* ctx, const char* key, long value) {
     if (!strcmp(key, "dualk_variant")) { ctx->dualk_variant = (int)value; return MD_OK; }
     if (!strcmp(key, "fused_decode")) { ctx->fused_decode = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "pdl")) { ctx->pdl = value ? 1 : 0; return MD_OK; }
+    if (!strcmp(key, "decode_fork")) { ctx->decode_fork = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "persist_trace")) { ctx->persist_trace = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "persistent_decode")) { ctx->persistent_decode = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "attn_tc")) { ctx->attn_tc = value < 0 ? -1 : value ? 1 : 0; return MD_OK; }

@@ -59,6 +59,11 @@ struct md_ctx {
     int dualk_variant = 0;   // md_set_option("dualk_variant"): (warps, unroll) of gemv_dual_k_kernel
     int fused_decode = 1;    // md_set_option("fused_decode"): decode layers as 3 fused kernels
     int pdl = 0;             // md_set_option("pdl"): programmatic dependent launch for the GEMV kernels
+    int decode_fork = 1;        // md_set_option("decode_fork"): a decode layer runs as two concurrent kernel chains
+    cudaStream_t side_stream = nullptr;  // second chain of the forked decode layer
+    int prio_high = 0;          // greatest stream priority of the device
+    int launch_priority = 0;    // != 0: kernels launched through cudaLaunchKernelEx carry this priority
+    cudaEvent_t ev_fork = nullptr, ev_side = nullptr;
     int persist_trace = 0;      // md_set_option("persist_trace"): print phase timings of the persistent step (tuning aid)
     int persistent_decode = 0;  // md_set_option("persistent_decode"): one persistent kernel per decode step
     int attn_tc = -1;        // md_set_option("attn_tc"): -1 auto, 0 mma.sync attention only, 1 tcgen05 attention only
@@ -126,7 +131,8 @@ bool md_gemv_ln_dual_supported(size_t M, size_t K, size_t n1, size_t n2);
 int md_launch_gemv_ln_dual(md_ctx* ctx, const __half* hidden, const __half* ln_w, const __half* ln_b, float eps,
                            const __half* w1, const __half* b1, __half* out1, size_t n1, const __half* w2,
                            const __half* b2, __half* out2, size_t n2, size_t M, size_t K,
-                           unsigned long long* amax = nullptr);  // amax: optional [M] argmax keys of out1
+                           unsigned long long* amax = nullptr,  // amax: optional [M] argmax keys of out1
+                           bool gelu1 = false);                 // GELU on segment 1 too
 bool md_gemv_dual_k_supported(size_t M, size_t N, size_t k1, size_t k2);
 int md_launch_gemv_dual_k(md_ctx* ctx, const __half* x1, const __half* w1, const __half* b1, size_t k1,
                           const __half* x2, const __half* w2, const __half* b2, size_t k2, __half* hidden, size_t N,

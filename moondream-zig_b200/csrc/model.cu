@@ -177,6 +177,56 @@ int text_layer(md_text_model* m, size_t layer, const LayerIO& io, size_t rows, b
     const size_t D = w.dim, F = w.hidden;
     if (decode && ctx->fused_decode && md_gemv_ln_dual_supported(rows, D, 3 * D, F) &&
         md_gemv_dual_k_supported(rows, D, D, F)) {
+        if (ctx->decode_fork) {
+            // Two concurrent chains per layer, so that the weight stream of the MLP fills the time the attention
+            // chain spends on latency (q/k/v projection -> attention -> out-projection move 33 MB, the MLP 67 MB):
+            //   main: [LayerNorm + qkv] -> attention ------------------> [out-proj + bias + mlp_out + hidden]
+            //   side: [LayerNorm + fc1 + GELU] -> [fc2 + bias -> mlp_out] --^
+            // Same rounding points as the reference: attn_out = f16(f16(acc) + b), mlp_out likewise,
+            // attn_out += mlp_out, hidden += attn_out (text_model.zig:162-171).
+            if (!ctx->side_stream) {
+                MD_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking));
+                MD_CUDA(ctx, cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming));
+                MD_CUDA(ctx, cudaEventCreateWithFlags(&ctx->ev_side, cudaEventDisableTiming));
+            }
+            cudaStream_t main_stream = ctx->stream;
+            MD_CUDA(ctx, cudaEventRecord(ctx->ev_fork, main_stream));            // hidden of the previous layer is final
+            MD_CUDA(ctx, cudaStreamWaitEvent(ctx->side_stream, ctx->ev_fork, 0));
+            ctx->stream = ctx->side_stream;
+            int st = md_launch_gemv_ln_dual(ctx, io.hidden, H(m->ln_w[layer]), H(m->ln_b[layer]), eps_of(w.eps_f16),
+                                            H(m->wfc1[layer]), H(m->bfc1[layer]), io.fc1, F, nullptr, nullptr, nullptr, 0,
+                                            rows, D, nullptr, true);
+            if (st == MD_OK) {
+                md_epilogue e_fc2;
+                e_fc2.bias = H(m->bfc2[layer]);
+                st = md_launch_gemv_nt(ctx, io.fc1, H(m->wfc2[layer]), io.attn_out, rows, D, F, e_fc2);
+            }
+            if (st == MD_OK && cudaEventRecord(ctx->ev_side, ctx->side_stream) != cudaSuccess)
+                st = md_fail(ctx, MD_ERR_CUDA, "cudaEventRecord on the side stream failed");
+            ctx->stream = main_stream;
+            MD_TRY(st);
+            // the attention chain is the critical path: its kernels take SM slots ahead of the MLP chain's
+            struct PrioScope {
+                md_ctx* c;
+                explicit PrioScope(md_ctx* cc) : c(cc) { c->launch_priority = c->prio_high; }
+                ~PrioScope() { c->launch_priority = 0; }
+            } prio_scope(ctx);
+            MD_TRY(md_launch_gemv_ln_dual(ctx, io.hidden, H(m->ln_w[layer]), H(m->ln_b[layer]), eps_of(w.eps_f16),
+                                          H(m->wqkv[layer]), H(m->bqkv[layer]), io.qkv, 3 * D, nullptr, nullptr, nullptr, 0,
+                                          rows, D));
+            for (size_t b = 0; b < rows; ++b) {
+                md_text_request* r = reqs[b];
+                MD_TRY(md_launch_sdpa_decode_fused_devpos(ctx, io.qkv + b * 3 * D, r->kc[layer], r->vc[layer],
+                                                          io.attn + b * D, w.n_heads, w.head_dim, w.max_seq, r->pos_dev,
+                                                          w.rot_dim, w.rope_theta));
+            }
+            MD_CUDA(ctx, cudaStreamWaitEvent(main_stream, ctx->ev_side, 0));
+            md_epilogue e_out;
+            e_out.bias = H(m->bout[layer]);
+            e_out.residual = io.attn_out;   // mlp_out
+            e_out.residual2 = io.hidden;    // updated in place: every element is read and written by one thread
+            return md_launch_gemv_nt(ctx, io.attn, H(m->wout[layer]), io.hidden, rows, D, D, e_out);
+        }
         // Three kernels per layer: [LayerNorm + qkv + fc1] -> attention -> [out-proj + fc2 + residuals]
         MD_TRY(md_launch_gemv_ln_dual(ctx, io.hidden, H(m->ln_w[layer]), H(m->ln_b[layer]), eps_of(w.eps_f16),
                                       H(m->wqkv[layer]), H(m->bqkv[layer]), io.qkv, 3 * D, H(m->wfc1[layer]),
