@@ -74,6 +74,8 @@ constexpr int BQ = 64, BKV = 64;
 template <int D, int D_PAD>
 __global__ void __launch_bounds__(128)
 sdpa_mma_kernel(SdpaParams p) {
+    md_pdl_launch_dependents();
+    md_pdl_wait();
     constexpr int PITCH = D_PAD + 8;  // halves; 144 B or 176 B rows keep ldmatrix conflict-free
     constexpr int CHUNKS = D_PAD / 8, REAL_CHUNKS = D / 8;
     // dynamic shared memory: Q tile, then two K and two V tiles (double buffered)
@@ -566,6 +568,8 @@ __global__ void __launch_bounds__(128)
 rope_cache_write_kernel(const __half* __restrict__ qkv, __half* __restrict__ q_rot, __half* __restrict__ kc,
                         __half* __restrict__ vc, int S, int H, int d, int max_seq, int pos, int rot_dim,
                         const float* __restrict__ tab) {
+    md_pdl_launch_dependents();
+    md_pdl_wait();
     const int s = blockIdx.x, hd = H * d;
     const __half* row = qkv + (long long)s * 3 * hd;
     const int half = rot_dim / 2;
@@ -631,10 +635,8 @@ int md_launch_sdpa(md_ctx* ctx, const __half* q, const __half* k, const __half* 
             MD_CUDA(ctx, cudaFuncSetAttribute(sdpa_mma_kernel<72, 80>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem72));
             attr_set = true;
         }
-        if (d == 64) sdpa_mma_kernel<64, 64><<<grid, 128, smem64, ctx->stream>>>(p);
-        else sdpa_mma_kernel<72, 80><<<grid, 128, smem72, ctx->stream>>>(p);
-        MD_LAUNCH_CHECK(ctx, "sdpa_mma_kernel");
-        return MD_OK;
+        if (d == 64) return md_launch_ex(ctx, sdpa_mma_kernel<64, 64>, grid, dim3(128), smem64, "sdpa_mma_kernel", p);
+        return md_launch_ex(ctx, sdpa_mma_kernel<72, 80>, grid, dim3(128), smem72, "sdpa_mma_kernel", p);
     }
     const size_t warps = q_len * n_heads;
     dim3 grid((unsigned)((warps + 3) / 4), (unsigned)batch);
@@ -744,9 +746,8 @@ int md_launch_rope_cache_write(md_ctx* ctx, const __half* qkv, __half* q_rot, __
     if (S == 0) return MD_OK;
     const float* tab = nullptr;
     MD_TRY(md_rope_cached(ctx, rot_dim, theta, max_seq, &tab));
-    rope_cache_write_kernel<<<(unsigned)S, 128, 0, ctx->stream>>>(qkv, q_rot, kc, vc, (int)S, (int)n_heads, (int)d,
-                                                                  (int)max_seq, (int)pos, (int)rot_dim, tab);
-    MD_LAUNCH_CHECK(ctx, "rope_cache_write_kernel");
+    MD_TRY(md_launch_ex(ctx, rope_cache_write_kernel, dim3((unsigned)S), dim3(128), 0, "rope_cache_write_kernel", qkv, q_rot,
+                        kc, vc, (int)S, (int)n_heads, (int)d, (int)max_seq, (int)pos, (int)rot_dim, tab));
     return MD_OK;
 }
 

@@ -140,6 +140,7 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
     if (p.causal_pos >= 0) kv_end = min(kv_end, p.causal_pos + min(q0 + ABQ, p.q_len));
     const int nt = (kv_end + ABKV - 1) / ABKV;
 
+    md_pdl_launch_dependents();
     if (threadIdx.x == 0) {
         mbar_init(b_qfull, 1);
         for (int s = 0; s < ST; ++s) {
@@ -168,6 +169,7 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    md_pdl_wait();
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -204,41 +206,55 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
             const uint32_t idesc_s = (1u << 4) | ((uint32_t)(ABKV >> 3) << 17) | ((uint32_t)(ABQ >> 4) << 24);
             const uint32_t idesc_pv = (1u << 4) | (1u << 16) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(ABQ >> 4) << 24);
             const uint32_t idesc_pvt = (1u << 4) | (1u << 16) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(ABQ >> 4) << 24);
+            // descriptors as 32-bit halves (tc_common.cuh): constant high words, low words advanced by adds; the
+            // ring slot (j % ST) and its wait parity are kept as running counters instead of divisions
+            const uint32_t hi128 = desc_hi(1024, 2), hi32 = desc_hi(256, 6);
+            const uint32_t q_lo = desc_lo(sm_q, 16), qt_lo = desc_lo(sm_qt, 16);
+            const uint32_t k_lo0 = desc_lo(sm_k, 16), kt_lo0 = desc_lo(sm_k + Cfg::KV_MAIN, 16);
+            const uint32_t p_lo0 = desc_lo(sm_p, 16);
+            const uint32_t v_lo0 = desc_lo(sm_v, ABKV * 128), vt_lo0 = desc_lo(sm_v + Cfg::KV_MAIN, 512);
+            constexpr uint32_t STAGE16 = Cfg::STAGE_BYTES >> 4, P16 = Cfg::P_BYTES >> 4;
+            uint32_t pv_st = 0, pv_par = 0;  // ring slot and parity of the next PV product
             auto issue_pv = [&](int i) {
-                const int st = i % ST, pb = i & 1;
-                const uint32_t v_main = sm_v + st * Cfg::STAGE_BYTES, v_tail = v_main + Cfg::KV_MAIN;
-                mbar_wait(b_vfull + 8 * st, (uint32_t)((i / ST) & 1), abort_flag, flags, 13);
+                const uint32_t pb = (uint32_t)i & 1u;
+                mbar_wait(b_vfull + 8 * pv_st, pv_par, abort_flag, flags, 13);
                 mbar_wait(b_pfull + 8 * pb, (uint32_t)((i >> 1) & 1), abort_flag, flags, 12);
                 tc_fence_after();
+                const uint32_t p_lo = p_lo0 + pb * P16, v_lo = v_lo0 + pv_st * STAGE16, vt_lo = vt_lo0 + pv_st * STAGE16;
+                // V is the MN-major B operand: 64 dims contiguous per key, 16 keys = 2048 B per k-step; the tail
+                // holds 16 dims per key (32B swizzle), 16 keys = 512 B per k-step
+                if (i == 0) {
+                    tc_mma_f16_parts<false>(tmem_base + T_O, p_lo, hi128, v_lo, hi128, idesc_pv);
+                    if (TAIL) tc_mma_f16_parts<false>(tmem_base + T_O + 64, p_lo, hi128, vt_lo, hi32, idesc_pvt);
+                } else {
+                    tc_mma_f16_parts<true>(tmem_base + T_O, p_lo, hi128, v_lo, hi128, idesc_pv);
+                    if (TAIL) tc_mma_f16_parts<true>(tmem_base + T_O + 64, p_lo, hi128, vt_lo, hi32, idesc_pvt);
+                }
 #pragma unroll
-                for (int ks = 0; ks < ABKV / 16; ++ks) {
-                    const uint64_t da = make_desc(sm_p + pb * Cfg::P_BYTES + ks * 32, 16, 1024);
-                    const uint32_t acc = (i > 0 || ks > 0) ? 1u : 0u;
-                    // V is the MN-major B operand: 64 dims contiguous per key, 16 keys = 2048 B per k-step
-                    tc_mma_f16(tmem_base + T_O, da, make_desc(v_main + ks * (16 * 128), ABKV * 128, 1024), idesc_pv, acc);
-                    if (TAIL)  // 16 dims contiguous per key (32B swizzle), 16 keys = 512 B per k-step
-                        tc_mma_f16(tmem_base + T_O + 64, da, make_desc_sw(v_tail + ks * (16 * 32), 512, 256, 6),
-                                   idesc_pvt, acc);
+                for (int ks = 1; ks < ABKV / 16; ++ks) {
+                    tc_mma_f16_parts<true>(tmem_base + T_O, p_lo + ks * 2, hi128, v_lo + ks * 128, hi128, idesc_pv);
+                    if (TAIL)
+                        tc_mma_f16_parts<true>(tmem_base + T_O + 64, p_lo + ks * 2, hi128, vt_lo + ks * 32, hi32, idesc_pvt);
                 }
                 tc_commit(b_pempty + 8 * pb);
-                tc_commit(b_vempty + 8 * st);
+                tc_commit(b_vempty + 8 * pv_st);
+                if (++pv_st == ST) { pv_st = 0; pv_par ^= 1u; }
             };
             mbar_wait(b_qfull, 0, abort_flag, flags, 14);
+            uint32_t st = 0, par = 0;
             for (int j = 0; j < nt; ++j) {
-                const int st = j % ST, sb = j & 1;
-                const uint32_t k_main = sm_k + st * Cfg::STAGE_BYTES, k_tail = k_main + Cfg::KV_MAIN;
-                mbar_wait(b_kfull + 8 * st, (uint32_t)((j / ST) & 1), abort_flag, flags, 15);
+                const uint32_t sb = (uint32_t)j & 1u;
+                mbar_wait(b_kfull + 8 * st, par, abort_flag, flags, 15);
                 mbar_wait(b_sempty + 8 * sb, (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, flags, 16);
                 tc_fence_after();
-                const uint32_t t_s = tmem_base + (uint32_t)(sb * 64);
+                const uint32_t t_s = tmem_base + sb * 64u, k_lo = k_lo0 + st * STAGE16;
+                tc_mma_f16_parts<false>(t_s, q_lo, hi128, k_lo, hi128, idesc_s);
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                    tc_mma_f16(t_s, make_desc(sm_q + ks * 32, 16, 1024), make_desc(k_main + ks * 32, 16, 1024), idesc_s,
-                               ks > 0 ? 1u : 0u);
-                if (TAIL)
-                    tc_mma_f16(t_s, make_desc_sw(sm_qt, 16, 256, 6), make_desc_sw(k_tail, 16, 256, 6), idesc_s, 1u);
+                for (int ks = 1; ks < 4; ++ks) tc_mma_f16_parts<true>(t_s, q_lo + ks * 2, hi128, k_lo + ks * 2, hi128, idesc_s);
+                if (TAIL) tc_mma_f16_parts<true>(t_s, qt_lo, hi32, kt_lo0 + st * STAGE16, hi32, idesc_s);
                 tc_commit(b_sfull + 8 * sb);
                 tc_commit(b_kempty + 8 * st);
+                if (++st == ST) { st = 0; par ^= 1u; }
                 if (j > 0) issue_pv(j - 1);
             }
             if (nt > 0) issue_pv(nt - 1);
@@ -422,9 +438,7 @@ int launch_attn_tc(md_ctx* ctx, const AttnTcMaps& maps, const AttnTcParams& p, d
         MD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<D>::SMEM));
         ctx->tc_configured |= cfg_bit;
     }
-    kern<<<grid, 192, AttnCfg<D>::SMEM, ctx->stream>>>(maps, p, ctx->flags);
-    MD_LAUNCH_CHECK(ctx, "attn_tc_kernel");
-    return MD_OK;
+    return md_launch_ex(ctx, kern, grid, dim3(192), AttnCfg<D>::SMEM, "attn_tc_kernel", maps, p, ctx->flags);
 }
 
 }  // namespace

@@ -71,6 +71,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
 
+    // programmatic dependent launch: the successor may start its own set-up now; this kernel sets up its
+    // barriers and tensor memory, then waits for its predecessor before any global access
+    md_pdl_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full + 8 * s, 1);
@@ -94,6 +97,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    md_pdl_wait();
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -130,6 +134,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if (lane == 0) {
             const uint32_t idesc = (1u << 4) | ((B_MN_MAJOR ? 1u : 0u) << 16) | ((uint32_t)(BLOCK_N >> 3) << 17) |
                                    ((uint32_t)(BLOCK_M >> 4) << 24);
+            // descriptors as 32-bit halves: constant high words, low words advanced by adds (tc_common.cuh)
+            // K-major operand: 16 k = 32 B further along the swizzled row; MN-major B: 16 k-rows = 2048 B
+            constexpr uint32_t A_KSTEP = (UMMA_K * 2) >> 4, B_KSTEP = (B_MN_MAJOR ? UMMA_K * 128 : UMMA_K * 2) >> 4;
+            const uint32_t a_hi = desc_hi(1024, 2), b_hi = desc_hi(1024, 2);
+            const uint32_t a_lo0 = desc_lo(smem_a, 16), b_lo0 = desc_lo(smem_b, B_MN_MAJOR ? 64 * BLOCK_K * 2 : 16);
             int stage = 0;
             uint32_t phase = 0;
             int local = 0;
@@ -142,16 +151,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 for (int kb = 0; kb < num_kb; ++kb) {
                     mbar_wait(bar_full + 8 * stage, phase, abort_flag, flags, 3);
                     tc_fence_after();
-                    const uint32_t a_addr = smem_a + stage * A_STAGE_BYTES;
-                    const uint32_t b_addr = smem_b + stage * B_STAGE_BYTES;
+                    const uint32_t a_lo = a_lo0 + (uint32_t)stage * (A_STAGE_BYTES >> 4);
+                    const uint32_t b_lo = b_lo0 + (uint32_t)stage * (B_STAGE_BYTES >> 4);
+                    if (kb == 0) tc_mma_f16_parts<false>(tmem_d, a_lo, a_hi, b_lo, b_hi, idesc);
+                    else tc_mma_f16_parts<true>(tmem_d, a_lo, a_hi, b_lo, b_hi, idesc);
 #pragma unroll
-                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-                        const uint64_t da = make_desc(a_addr + k * (UMMA_K * 2), 16, 1024);
-                        const uint64_t db = B_MN_MAJOR
-                                                ? make_desc(b_addr + k * (UMMA_K * 128), 64 * BLOCK_K * 2, 1024)
-                                                : make_desc(b_addr + k * (UMMA_K * 2), 16, 1024);
-                        tc_mma_f16(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                    }
+                    for (int k = 1; k < BLOCK_K / UMMA_K; ++k)
+                        tc_mma_f16_parts<true>(tmem_d, a_lo + k * A_KSTEP, a_hi, b_lo + k * B_KSTEP, b_hi, idesc);
                     tc_commit(bar_empty + 8 * stage);  // frees the smem stage once these MMAs retire
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -328,10 +334,8 @@ int launch(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, s
         MD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         ctx->tc_configured |= cfg_bit;
     }
-    kern<<<grid, NUM_THREADS, smem, ctx->stream>>>(tm_a, tm_b, tm_c, (int)M, (int)N, (int)K, tiles_m, num_tiles, ep,
-                                                   push, ctx->flags);
-    MD_LAUNCH_CHECK(ctx, "gemm_tc_kernel");
-    return MD_OK;
+    return md_launch_ex(ctx, kern, dim3((unsigned)grid), dim3(NUM_THREADS), smem, "gemm_tc_kernel", tm_a, tm_b, tm_c, (int)M,
+                        (int)N, (int)K, tiles_m, num_tiles, ep, push, ctx->flags);
 }
 
 }  // namespace

@@ -21,6 +21,8 @@ layernorm_kernel(const __half* __restrict__ x, const __half* __restrict__ w, con
     __shared__ float red[THREADS / 32];
     __shared__ float bcast;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    md_pdl_launch_dependents();
+    md_pdl_wait();
     const __half* xr = x + (size_t)blockIdx.x * cols;
     float v[PER_THREAD];
     float sum = 0.f;
@@ -226,15 +228,13 @@ unsigned grid_for(size_t n, int block, int sm_count) {
 int md_launch_layernorm(md_ctx* ctx, const __half* x, const __half* w, const __half* b, __half* y, size_t rows,
                         size_t cols, float eps) {
     if (rows == 0) return MD_OK;
-    if (cols <= 256 * 8) {
-        layernorm_kernel<256, 8><<<(unsigned)rows, 256, 0, ctx->stream>>>(x, w, b, y, (int)cols, eps);
-    } else if (cols <= 1024 * 16) {
-        layernorm_kernel<1024, 16><<<(unsigned)rows, 1024, 0, ctx->stream>>>(x, w, b, y, (int)cols, eps);
-    } else {
-        return md_fail(ctx, MD_ERR_UNSUPPORTED, "layernorm rows longer than 16384 are not supported (%zu)", cols);
-    }
-    MD_LAUNCH_CHECK(ctx, "layernorm_kernel");
-    return MD_OK;
+    if (cols <= 256 * 8)
+        return md_launch_ex(ctx, layernorm_kernel<256, 8>, dim3((unsigned)rows), dim3(256), 0, "layernorm_kernel", x, w, b,
+                            y, (int)cols, eps);
+    if (cols <= 1024 * 16)
+        return md_launch_ex(ctx, layernorm_kernel<1024, 16>, dim3((unsigned)rows), dim3(1024), 0, "layernorm_kernel", x, w,
+                            b, y, (int)cols, eps);
+    return md_fail(ctx, MD_ERR_UNSUPPORTED, "layernorm rows longer than 16384 are not supported (%zu)", cols);
 }
 
 int md_launch_gelu(md_ctx* ctx, __half* x, size_t n) {

@@ -83,6 +83,44 @@ int md_fail(md_ctx* ctx, int status, const char* fmt, ...);
         if (_s != MD_OK) return _s;     \
     } while (0)
 
+// Launch through cudaLaunchKernelEx so that the context's launch attributes apply: with ctx->pdl the kernel
+// is programmatically dependent on its predecessor in the stream (it may start while that one drains; it must
+// execute griddepcontrol.wait before touching anything an earlier kernel produces or still reads), and
+// ctx->launch_priority, when set, is attached as the launch priority.
+#ifdef __CUDACC__
+template <class... KArgs, class... Args>
+int md_launch_ex(md_ctx* ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, const char* name,
+                 Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (ctx->pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (ctx->launch_priority) {
+        attr[na].id = cudaLaunchAttributePriority;
+        attr[na].val.priority = ctx->launch_priority;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) return md_fail(ctx, MD_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e));
+    ctx->launches++;
+    return MD_OK;
+}
+// Device side of the protocol: let the successor start its prologue, then wait for the predecessor.
+__device__ __forceinline__ void md_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void md_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
+
+
 // The context's rope table for (rot_dim, theta), covering at least `rows` positions; built on first use.
 int md_rope_cached(md_ctx* ctx, size_t rot_dim, float theta, size_t rows, const float** out);
 // Ensure ctx->scratch holds at least `bytes`.

@@ -131,6 +131,16 @@ struct md_text_request {
 
 namespace {
 
+// While alive, the kernels that implement the programmatic-dependent-launch protocol (GEMV, tcgen05 GEMM and
+// attention, LayerNorm, rope) are launched dependent on their predecessor: each starts its set-up while the
+// previous one drains and waits (griddepcontrol.wait) before touching global memory.
+struct PdlScope {
+    md_ctx* c;
+    int old;
+    explicit PdlScope(md_ctx* cc) : c(cc), old(cc->pdl) { c->pdl = 1; }
+    ~PdlScope() { c->pdl = old; }
+};
+
 const __half* H(const uint16_t* p) { return reinterpret_cast<const __half*>(p); }
 __half* H(uint16_t* p) { return reinterpret_cast<__half*>(p); }
 
@@ -431,6 +441,7 @@ int md_text_forward(md_text_model* model, md_text_request* req, const uint16_t* 
     const size_t pos0 = req->pos;
     // S == 1 takes the decode kernels (text_model.zig:284-290 switches on seq_len == 1 as well)
     auto body = [&]() -> int {
+        PdlScope pdl_scope(ctx);
         for (size_t l = 0; l < w.n_layers; ++l) MD_TRY(text_layer(model, l, io, S, S == 1, reqs, pos0));
         set_int_kernel<<<1, 1, 0, ctx->stream>>>(req->pos_dev, (int)(pos0 + S));
         MD_LAUNCH_CHECK(ctx, "set_int_kernel");
@@ -476,11 +487,7 @@ static int enqueue_decode_step(md_text_model* model, md_text_request* const* req
     const md_text_weights& w = model->w;
     md_text_request* r0 = reqs[0];
     // registered weights are never written on this stream: the GEMVs may overlap their predecessors' tails
-    struct PdlScope {
-        md_ctx* c; int old;
-        explicit PdlScope(md_ctx* cc) : c(cc), old(cc->pdl) { c->pdl = 1; }
-        ~PdlScope() { c->pdl = old; }
-    } pdl_scope(ctx);
+    PdlScope pdl_scope(ctx);
     // hidden already holds the embeddings of the current tokens (generate_impl / the previous advance_kernel)
     const LayerIO io = io_of(r0);
     const bool persistent = r0->persist_batch == batch;
@@ -751,6 +758,7 @@ int md_vision_encode(md_vision_model* m, const uint8_t* crops_u8, size_t crops, 
     const uint8_t* img = m->img.as<uint8_t>();
     __half* ln = m->ln.as<__half>();
     auto body = [&]() -> int {
+    PdlScope pdl_scope(ctx);
     __half *x = m->x.as<__half>(), *qkv = m->qkv.as<__half>(), *att = m->att.as<__half>(),
            *fc1 = m->fc1.as<__half>();
     MD_TRY(md_launch_patchify(ctx, img, m->patches.as<__half>(), crops, w.img, w.img, w.patch, m->patch_dim_padded));
