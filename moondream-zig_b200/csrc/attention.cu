@@ -712,13 +712,8 @@ int md_launch_sdpa_decode_fused_devpos(md_ctx* ctx, const __half* qkv_row, __hal
     // A cluster of 16 CTAs (one per possible split) needs the non-portable cluster size; when the
     // context could not enable it, or the cache is longer than 16 splits, the scratch-based merge runs.
     const bool use_cluster = ctx->decode_cluster_ok && max_splits <= 16;
-    cudaLaunchAttribute attr[3];
+    cudaLaunchAttribute attr[2];
     int na = 0;
-    if (ctx->launch_priority) {
-        attr[na].id = cudaLaunchAttributePriority;
-        attr[na].val.priority = ctx->launch_priority;
-        ++na;
-    }
     if (use_cluster) {
         cfg.gridDim = dim3(16u, (unsigned)p.n_heads);
         attr[na].id = cudaLaunchAttributeClusterDimension;

@@ -167,20 +167,11 @@ int md_launch_gemv_nt(md_ctx* ctx, const __half* a, const __half* bt, __half* c,
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[2];
-    int na = 0;
-    if (ctx->pdl) {
-        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[na].val.programmaticStreamSerializationAllowed = 1;
-        ++na;
-    }
-    if (ctx->launch_priority) {
-        attr[na].id = cudaLaunchAttributePriority;
-        attr[na].val.priority = ctx->launch_priority;
-        ++na;
-    }
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = na;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
     const int Mi = (int)M, Ni = (int)N, Ki = (int)K;
     cudaError_t le = cudaSuccess;
 #define MD_GEMV_CASE(id, W, U)                                                          \

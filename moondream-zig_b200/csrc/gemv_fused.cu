@@ -332,20 +332,11 @@ int launch_pdl(md_ctx* ctx, Kern kern, unsigned grid, unsigned block, const Para
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(block);
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[2];
-    int na = 0;
-    if (ctx->pdl) {
-        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[na].val.programmaticStreamSerializationAllowed = 1;
-        ++na;
-    }
-    if (ctx->launch_priority) {
-        attr[na].id = cudaLaunchAttributePriority;
-        attr[na].val.priority = ctx->launch_priority;
-        ++na;
-    }
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = na;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
     if (e != cudaSuccess) return md_fail(ctx, MD_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e));
     ctx->launches++;

@@ -174,10 +174,6 @@ int md_init(md_ctx** out, int device) {
     };
     if (cudaSetDevice(device) != cudaSuccess) return bail("cudaSetDevice");
     if (cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess) return bail("stream");
-    {
-        int least = 0, greatest = 0;
-        if (cudaDeviceGetStreamPriorityRange(&least, &greatest) == cudaSuccess) ctx->prio_high = greatest;
-    }
     ctx->stream = ctx->own_stream;
     if (cudaMalloc(&ctx->flags, sizeof(md_devflags)) != cudaSuccess) return bail("cudaMalloc flags");
     if (cudaMemset(ctx->flags, 0, sizeof(md_devflags)) != cudaSuccess) return bail("cudaMemset flags");

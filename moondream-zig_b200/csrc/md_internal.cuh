@@ -61,8 +61,6 @@ struct md_ctx {
     int pdl = 0;             // md_set_option("pdl"): programmatic dependent launch for the GEMV kernels
     int decode_fork = 1;        // md_set_option("decode_fork"): a decode layer runs as two concurrent kernel chains
     cudaStream_t side_stream = nullptr;  // second chain of the forked decode layer
-    int prio_high = 0;          // greatest stream priority of the device
-    int launch_priority = 0;    // != 0: kernels launched through cudaLaunchKernelEx carry this priority
     cudaEvent_t ev_fork = nullptr, ev_side = nullptr;
     int persist_trace = 0;      // md_set_option("persist_trace"): print phase timings of the persistent step (tuning aid)
     int persistent_decode = 0;  // md_set_option("persistent_decode"): one persistent kernel per decode step
@@ -85,8 +83,7 @@ int md_fail(md_ctx* ctx, int status, const char* fmt, ...);
 
 // Launch through cudaLaunchKernelEx so that the context's launch attributes apply: with ctx->pdl the kernel
 // is programmatically dependent on its predecessor in the stream (it may start while that one drains; it must
-// execute griddepcontrol.wait before touching anything an earlier kernel produces or still reads), and
-// ctx->launch_priority, when set, is attached as the launch priority.
+// execute griddepcontrol.wait before touching anything an earlier kernel produces or still reads).
 #ifdef __CUDACC__
 template <class... KArgs, class... Args>
 int md_launch_ex(md_ctx* ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, const char* name,
@@ -96,20 +93,11 @@ int md_launch_ex(md_ctx* ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, siz
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[2];
-    int na = 0;
-    if (ctx->pdl) {
-        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[na].val.programmaticStreamSerializationAllowed = 1;
-        ++na;
-    }
-    if (ctx->launch_priority) {
-        attr[na].id = cudaLaunchAttributePriority;
-        attr[na].val.priority = ctx->launch_priority;
-        ++na;
-    }
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = na;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
     if (e != cudaSuccess) return md_fail(ctx, MD_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e));
     ctx->launches++;

@@ -215,12 +215,8 @@ int text_layer(md_text_model* m, size_t layer, const LayerIO& io, size_t rows, b
                 st = md_fail(ctx, MD_ERR_CUDA, "cudaEventRecord on the side stream failed");
             ctx->stream = main_stream;
             MD_TRY(st);
-            // the attention chain is the critical path: its kernels take SM slots ahead of the MLP chain's
-            struct PrioScope {
-                md_ctx* c;
-                explicit PrioScope(md_ctx* cc) : c(cc) { c->launch_priority = c->prio_high; }
-                ~PrioScope() { c->launch_priority = 0; }
-            } prio_scope(ctx);
+            // (launch priorities for either chain were measured and made the step slower: both chains run at
+            // the stream's priority)
             MD_TRY(md_launch_gemv_ln_dual(ctx, io.hidden, H(m->ln_w[layer]), H(m->ln_b[layer]), eps_of(w.eps_f16),
                                           H(m->wqkv[layer]), H(m->bqkv[layer]), io.qkv, 3 * D, nullptr, nullptr, nullptr, 0,
                                           rows, D));
