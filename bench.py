@@ -340,7 +340,7 @@ def main():
                      "traffic": TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": peak_kind, "kernel": "gemv_nt_mma_kernel",
                      "frac_of_nominal_8tbs": achieved / 8000.0},
         "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "note": "md_hgemm_nt with pinned HOST activations/outputs per call, weights registered once"},
+                "note": "md_hgemm_nt with pinned HOST activations/outputs per call (activations copied up, results written by the kernel into the pinned host buffer), weights registered once"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }

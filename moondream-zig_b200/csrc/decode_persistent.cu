@@ -184,7 +184,7 @@ __device__ bool grid_wait(const PCtx& c, const unsigned int* counter, unsigned i
                 if ((++spin & 255u) == 0u) {
                     const bool failed_elsewhere = *reinterpret_cast<volatile unsigned int*>(&c.flags->error) != 0u;
                     if (failed_elsewhere || global_ns() - t0 > GRID_WAIT_NS) {
-                        if (atomicOr(&c.flags->error, 1u) == 0u) c.flags->where = 40;
+                        md_flag_timeout(c.flags, 40);
                         *c.abort_flag = 1;
                         break;
                     }

@@ -63,6 +63,24 @@ int md_stage_in(md_ctx* ctx, int slot, const void* user, size_t bytes, md_arg* o
     return MD_OK;
 }
 
+// Output that plain stores of a kernel may write in place when the caller's buffer is pinned, mapped host memory
+// and small (the GEMV results): no staging buffer and no device-to-host copy, the call ends with the stream
+// synchronize alone.  Anything else goes through md_stage_out.
+int md_stage_out_mapped(md_ctx* ctx, int slot, void* user, size_t bytes, md_arg* out) {
+    cudaPointerAttributes attr;
+    if (bytes > 0 && bytes <= ((size_t)1 << 20) && !ctx->capturing &&
+        cudaPointerGetAttributes(&attr, user) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer) {
+        out->user = user;
+        out->bytes = bytes;
+        out->dev = attr.devicePointer;
+        out->staged = false;
+        out->mapped = true;
+        return MD_OK;
+    }
+    cudaGetLastError();
+    return md_stage_out(ctx, slot, user, bytes, out);
+}
+
 int md_stage_out(md_ctx* ctx, int slot, void* user, size_t bytes, md_arg* out) {
     out->user = user;
     out->bytes = bytes;
@@ -78,20 +96,33 @@ int md_stage_out(md_ctx* ctx, int slot, void* user, size_t bytes, md_arg* out) {
     return MD_OK;
 }
 
-int md_check_flags(md_ctx* ctx) {
-    MD_CUDA(ctx, cudaMemcpyAsync(ctx->flags_host, ctx->flags, sizeof(md_devflags), cudaMemcpyDeviceToHost,
-                                 ctx->stream));
-    MD_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    if (ctx->flags_host->error) {
-        const unsigned where = ctx->flags_host->where;
-        cudaMemsetAsync(ctx->flags, 0, sizeof(md_devflags), ctx->stream);
-        cudaStreamSynchronize(ctx->stream);
-        return md_fail(ctx, MD_ERR_TIMEOUT, "a device-side wait gave up (site %u); results are invalid", where);
+static int reset_flags(md_ctx* ctx) {
+    md_devflags init;
+    init.error = 0;
+    init.where = 0;
+    init.mirror = nullptr;
+    *ctx->mirror_host = 0;
+    if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&init.mirror), ctx->mirror_host, 0) != cudaSuccess) {
+        cudaGetLastError();
+        init.mirror = nullptr;
     }
+    MD_CUDA(ctx, cudaMemcpy(ctx->flags, &init, sizeof(init), cudaMemcpyHostToDevice));
     return MD_OK;
 }
 
+// Synchronises the stream and reports a device-side wait that gave up.  The common case costs no copy: the
+// kernels raise a word in mapped host memory together with the device flag.
+int md_check_flags(md_ctx* ctx) {
+    MD_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (*reinterpret_cast<volatile unsigned int*>(ctx->mirror_host) == 0u) return MD_OK;
+    MD_CUDA(ctx, cudaMemcpy(ctx->flags_host, ctx->flags, sizeof(md_devflags), cudaMemcpyDeviceToHost));
+    const unsigned where = ctx->flags_host->where;
+    MD_TRY(reset_flags(ctx));
+    return md_fail(ctx, MD_ERR_TIMEOUT, "a device-side wait gave up (site %u); results are invalid", where);
+}
+
 int md_finish_out(md_ctx* ctx, md_arg* out) {
+    if (out->mapped) return md_check_flags(ctx);  // the kernel wrote the caller's buffer: wait for it
     if (!out->staged) return MD_OK;
     if (out->bytes)
         MD_CUDA(ctx, cudaMemcpyAsync(const_cast<void*>(out->user), out->dev, out->bytes, cudaMemcpyDeviceToHost,
@@ -176,8 +207,10 @@ int md_init(md_ctx** out, int device) {
     if (cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess) return bail("stream");
     ctx->stream = ctx->own_stream;
     if (cudaMalloc(&ctx->flags, sizeof(md_devflags)) != cudaSuccess) return bail("cudaMalloc flags");
-    if (cudaMemset(ctx->flags, 0, sizeof(md_devflags)) != cudaSuccess) return bail("cudaMemset flags");
     if (cudaMallocHost(&ctx->flags_host, sizeof(md_devflags)) != cudaSuccess) return bail("cudaMallocHost");
+    if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->mirror_host), sizeof(unsigned int), cudaHostAllocMapped) != cudaSuccess)
+        return bail("cudaHostAlloc mirror");
+    if (reset_flags(ctx) != MD_OK) return bail("flag initialisation");
     if (cudaMalloc(&ctx->counters, 1024) != cudaSuccess) return bail("cudaMalloc counters");
     if (cudaMemset(ctx->counters, 0, 1024) != cudaSuccess) return bail("cudaMemset counters");
     ctx->scratch_cap = (size_t)16 << 20;
@@ -197,6 +230,7 @@ int md_destroy(md_ctx* ctx) {
     if (ctx->rope_tab) cudaFree(ctx->rope_tab);
     if (ctx->flags) cudaFree(ctx->flags);
     if (ctx->flags_host) cudaFreeHost(ctx->flags_host);
+    if (ctx->mirror_host) cudaFreeHost(ctx->mirror_host);
     if (ctx->side_stream) cudaStreamDestroy(ctx->side_stream);
     if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
     if (ctx->ev_side) cudaEventDestroy(ctx->ev_side);
@@ -375,7 +409,12 @@ static int hgemm_entry(md_ctx* ctx, const uint16_t* a, const uint16_t* b, uint16
     md_arg A, B, Cc;
     MD_TRY(md_stage_in(ctx, 0, a, M * K * 2, &A));
     MD_TRY(md_stage_in(ctx, 1, b, N * K * 2, &B));
-    MD_TRY(md_stage_out(ctx, 2, c, M * N * 2, &Cc));
+    // the GEMV kernel (same conditions as in md_gemm_dispatch) writes with plain stores, which may target
+    // mapped host memory; the TMA-store epilogue of the tcgen05 GEMM always gets device memory
+    const bool gemv = ctx->gemm_mode == 0 && b_layout == 1 && M >= 1 && M <= 8 && K > 0 && (K % 8) == 0 &&
+                      ((reinterpret_cast<uintptr_t>(A.dev) | reinterpret_cast<uintptr_t>(B.dev)) & 15) == 0;
+    if (gemv) MD_TRY(md_stage_out_mapped(ctx, 2, c, M * N * 2, &Cc));
+    else MD_TRY(md_stage_out(ctx, 2, c, M * N * 2, &Cc));
     md_epilogue ep;
     MD_TRY(md_gemm_dispatch(ctx, (const __half*)A.dev, (const __half*)B.dev, (__half*)Cc.dev, M, N, K, b_layout, ep));
     return md_finish_out(ctx, &Cc);

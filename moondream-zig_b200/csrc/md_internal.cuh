@@ -18,8 +18,22 @@
 // zeroed at md_init and re-zeroed by md_sync after it has been reported.
 struct md_devflags {
     unsigned int error;
-    unsigned int where;  // site id of the first wait that gave up
+    unsigned int where;    // site id of the first wait that gave up
+    unsigned int* mirror;  // word in mapped pinned host memory, set to 1 together with `error`: the host can
+                           // tell "nothing went wrong" after a stream synchronize without a copy
 };
+#ifdef __CUDACC__
+// Record that a bounded device-side wait gave up at `site` (first site wins).
+__device__ __forceinline__ void md_flag_timeout(md_devflags* flags, unsigned site) {
+    if (atomicOr(&flags->error, 1u) == 0u) {
+        flags->where = site;
+        if (flags->mirror) {
+            *reinterpret_cast<volatile unsigned int*>(flags->mirror) = 1u;
+            __threadfence_system();
+        }
+    }
+}
+#endif
 
 struct md_graph {
     cudaGraph_t graph = nullptr;
@@ -32,7 +46,8 @@ struct md_ctx {
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;
     md_devflags* flags = nullptr;       // device
-    md_devflags* flags_host = nullptr;  // pinned host mirror
+    md_devflags* flags_host = nullptr;  // pinned host copy of *flags (read back when the mirror word is set)
+    unsigned int* mirror_host = nullptr;  // pinned, mapped: the word md_devflags::mirror points at
     std::string last_error;
     uint64_t launches = 0;
     int gemm_mode = 0;
@@ -121,11 +136,15 @@ struct md_arg {
     void* dev = nullptr;
     size_t bytes = 0;
     bool staged = false;
+    bool mapped = false;  // output written by the kernel straight into mapped pinned host memory
 };
 // Bring an input to the device (no-op for device pointers). slot selects the staging buffer.
 int md_stage_in(md_ctx* ctx, int slot, const void* user, size_t bytes, md_arg* out);
 // Reserve device space for an output (no-op for device pointers).
 int md_stage_out(md_ctx* ctx, int slot, void* user, size_t bytes, md_arg* out);
+// As md_stage_out, but a small output in pinned, mapped host memory is handed to the kernel directly
+// (only for kernels that write with plain stores).
+int md_stage_out_mapped(md_ctx* ctx, int slot, void* user, size_t bytes, md_arg* out);
 // Copy a staged output back and wait; for device outputs nothing happens.
 int md_finish_out(md_ctx* ctx, md_arg* out);
 // After a drop-in call whose output was a host buffer: check the device error word.

@@ -45,7 +45,7 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
         if (*abort_flag) return false;
         if ((spin & 63u) == 63u && global_ns() - t0 > WAIT_BUDGET_NS) {
             *abort_flag = 1;
-            if (atomicOr(&flags->error, 1u) == 0u) flags->where = site;
+            md_flag_timeout(flags, site);
             return false;
         }
     }
