@@ -374,7 +374,7 @@ int md_launch_gemm_tc_ex(md_ctx* ctx, const __half* a, const __half* b, __half* 
     int bn = 64;
     if (M > 64) {
         const int cand[3] = {256, 128, 64};
-        const double eff[3] = {1.0, 0.9, 0.65};
+        const double eff[3] = {1.0, 0.78, 0.65};
         double best = 0;
         for (int i = 0; i < 3; ++i) {
             const size_t t = tiles(cand[i]);
