@@ -11,8 +11,11 @@
  *   - hgemm (NN) against the in-test naive f32-accumulate product with the
  *     tolerances of src/core/matmul_test.zig:108-152 and the cases at :154-367
  *   - sgemm 2x2 known answer, src/core/matmul_test.zig:371-400
+ *   - LayerNorm (normalised rows, zero variance) and broadcast add (bias,
+ *     positional embedding, general), src/core/ops_test.zig:1773-1866,
+ *     1886-1935, 2547-2640
  * hgemm_trans (NT + GEMV), the three SDPA variants, rope, softmax, GELU,
- * LayerNorm, the KV cache and argmax have NO reference test: for those rows
+ * the KV cache and argmax have NO reference test: for those rows
  * PARITY IS UNPINNED; they are validated against float64 restatements of the
  * formulas and algebraic properties.
  *

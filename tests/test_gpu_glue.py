@@ -15,6 +15,24 @@ def test_layernorm(ctx, oracle, rows, cols):
     assert_close_ref(ctx.layernorm(x, w, b, rows, cols), oracle.layernorm(x, w, b), "layernorm", rel=2e-3)
 
 
+def test_layernorm_and_broadcast_add_reference_cases(ctx):
+    """The reference's own known-answer cases for the glue (ops_test.zig:1773-1824, 1849-1866, 2547-2640),
+    through the C ABI."""
+    x = np.array([[-1, 0, 1], [-1, 0, 1]], np.float16)
+    w, b = np.ones(3, np.float16), np.zeros(3, np.float16)
+    y = ctx.layernorm(x, w, b, 2, 3).astype(np.float32)
+    mean = y[0].mean()
+    assert abs(mean) < 1e-5 and abs(((y[0] - mean) ** 2).mean() - 1.0) < 0.01
+    assert np.isfinite(ctx.layernorm(np.ones((2, 3), np.float16), w, b, 2, 3).astype(np.float32)).all()
+    a = np.arange(24, dtype=np.float16).reshape(2, 12)
+    bb = (np.arange(12) * 2).astype(np.float16)
+    np.testing.assert_allclose(ctx.bias_add(a.copy(), bb, 2, 12).astype(np.float32),
+                               (a + bb[None, :]).astype(np.float32), rtol=1e-3)
+    a = np.arange(12, dtype=np.float16).reshape(3, 4)
+    np.testing.assert_allclose(ctx.bias_add(a.copy(), (np.arange(4) * 2).astype(np.float16), 3, 4).astype(np.float32),
+                               [[0, 3, 6, 9], [4, 7, 10, 13], [8, 11, 14, 17]], rtol=1e-3)
+
+
 def test_gelu_bias_add(ctx, oracle):
     rng = np.random.default_rng(0)
     x = f16_normal(rng, (300, 4304), 2.0)

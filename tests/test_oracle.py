@@ -210,6 +210,41 @@ def test_layernorm(oracle, rows, cols):
     assert_close_ref(oracle.layernorm(x, w, b), ref, "layernorm", rel=2e-3)
 
 
+def test_layernorm_reference_cases(oracle):
+    """The reference's own LayerNorm tests (ops_test.zig:1773-1824 "layerNorm basic functionality" and
+    :1849-1866 "zero variance"): rows [-1, 0, 1] with unit weight and zero bias normalise to mean ~ 0 and
+    variance ~ 1 within the test's tolerances; a constant row stays finite thanks to epsilon."""
+    x = np.array([[-1, 0, 1], [-1, 0, 1]], np.float16)
+    w, b = np.ones(3, np.float16), np.zeros(3, np.float16)
+    y = oracle.layernorm(x, w, b, np.float16(1e-5)).astype(np.float32)
+    assert y.shape == x.shape
+    mean = y[0].mean()
+    assert abs(mean) < 1e-5
+    assert abs(((y[0] - mean) ** 2).mean() - 1.0) < 0.01
+    const = oracle.layernorm(np.ones((2, 3), np.float16), w, b, np.float16(1e-5))
+    assert np.isfinite(const.astype(np.float32)).all()
+
+
+def test_broadcast_add_reference_cases(oracle):
+    """ops_test.zig:2547-2640 (broadcast_add_simd: positional-embedding, bias and general case) and :1886-1935
+    (broadcast_add basic), with the tests' own expected values; relative tolerance 0.001 as there."""
+    a = np.arange(24, dtype=np.float16).reshape(2, 12)            # [2,3,4] + [1,3,4]
+    b = (np.arange(12) * 2).astype(np.float16)
+    got = oracle.bias_add(a, b).astype(np.float32)
+    exp = (np.arange(24, dtype=np.float16).reshape(2, 12) + b[None, :]).astype(np.float32)
+    np.testing.assert_allclose(got, exp, rtol=1e-3)
+    a = np.arange(12, dtype=np.float16).reshape(3, 4)             # [3,4] + [4]
+    b = (np.arange(4) * 2).astype(np.float16)
+    np.testing.assert_allclose(oracle.bias_add(a, b).astype(np.float32),
+                               [[0, 3, 6, 9], [4, 7, 10, 13], [8, 11, 14, 17]], rtol=1e-3)
+    a = np.arange(6, dtype=np.float16).reshape(2, 3)              # [2,3] + [1,3]
+    b = (np.arange(3) * 2).astype(np.float16)
+    np.testing.assert_allclose(oracle.bias_add(a, b).astype(np.float32), [[0, 3, 6], [3, 6, 9]], rtol=1e-3)
+    a = np.arange(6, dtype=np.float16).reshape(2, 3)              # [2,3] + [3] of ones
+    np.testing.assert_allclose(oracle.bias_add(a, np.ones(3, np.float16)).astype(np.float32), [[1, 2, 3], [4, 5, 6]],
+                               atol=1e-6)
+
+
 def test_gelu_constants_and_values(oracle):
     x = np.linspace(-6, 6, 2001).astype(np.float16)
     c, a = 0.7978515625, 0.044708251953125            # f16(sqrt(f16(2/pi))), f16(0.044715)
