@@ -62,6 +62,12 @@ const char* md_last_error(const md_ctx* ctx);
 /* Wait for everything enqueued on the context's stream; reports MD_ERR_TIMEOUT if
  * any kernel since the last md_sync gave up on a bounded wait. */
 int md_sync(md_ctx* ctx);
+/* Self-test of the failure path (no counterpart in the reference): enqueues one small kernel whose only
+ * thread waits on a barrier that nothing ever completes.  The wait is bounded like every wait in this
+ * library: it gives up after `limit_ms` milliseconds (1..2000), records the failure and the kernel ends
+ * normally.  The next md_sync() (or the next call with a host output) then returns MD_ERR_TIMEOUT, after
+ * which the context is clean and usable again.  Nothing faults or hangs. */
+int md_selftest_bounded_wait(md_ctx* ctx, unsigned limit_ms);
 /* Use an existing cudaStream_t (e.g. the harness's stream) instead of the
  * context's own.  NULL restores the context's own stream. */
 int md_set_stream(md_ctx* ctx, void* cuda_stream);

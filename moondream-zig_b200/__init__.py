@@ -129,6 +129,10 @@ class Context:
     def sync(self):
         self._check(self.lib.md_sync(self.h))
 
+    def selftest_bounded_wait(self, limit_ms: int = 50):
+        """Enqueue the kernel whose bounded wait runs out after limit_ms; the next sync raises MD_ERR_TIMEOUT."""
+        self._check(self.lib.md_selftest_bounded_wait(self.h, C.c_uint(limit_ms)))
+
     def set_stream(self, cuda_stream: int | None):
         self._check(self.lib.md_set_stream(self.h, C.c_void_p(cuda_stream or 0)))
 

@@ -417,3 +417,24 @@ int md_make_map_4d(md_ctx* ctx, CUtensorMap* map, const void* ptr, const uint64_
     if (r != CUDA_SUCCESS) return md_fail(ctx, MD_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled (4-D) failed with CUresult %d", (int)r);
     return MD_OK;
 }
+
+// ---------------------------------------------------------------------------- failure-path self-test
+namespace {
+// One thread waits on an mbarrier that expects an arrival nobody makes, through the same bounded wait as the
+// kernels above, with a short budget; it gives up, records site 99 and the kernel ends normally.
+__global__ void selftest_wait_kernel(md_devflags* flags, unsigned long long budget_ns) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    const uint32_t b = smem_u32(&bar);
+    abort_flag = 0;
+    mbar_init(b, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_wait_slow(b, 0, &abort_flag, flags, 99, budget_ns);
+}
+}  // namespace
+
+int md_launch_selftest_wait(md_ctx* ctx, unsigned limit_ms) {
+    selftest_wait_kernel<<<1, 1, 0, ctx->stream>>>(ctx->flags, (unsigned long long)limit_ms * 1000000ull);
+    MD_LAUNCH_CHECK(ctx, "selftest_wait_kernel");
+    return MD_OK;
+}

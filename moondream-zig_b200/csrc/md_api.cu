@@ -246,6 +246,13 @@ int md_sync(md_ctx* ctx) {
     return md_check_flags(ctx);
 }
 
+int md_selftest_bounded_wait(md_ctx* ctx, unsigned limit_ms) {
+    MD_NEED_CTX(ctx);
+    MD_NEED(ctx, limit_ms >= 1 && limit_ms <= 2000, "md_selftest_bounded_wait: limit_ms must be 1..2000");
+    MD_NEED(ctx, !ctx->capturing, "md_selftest_bounded_wait: not while a graph is being captured");
+    return md_launch_selftest_wait(ctx, limit_ms);
+}
+
 int md_set_stream(md_ctx* ctx, void* cuda_stream) {
     MD_NEED_CTX(ctx);
     ctx->stream = cuda_stream ? reinterpret_cast<cudaStream_t>(cuda_stream) : ctx->own_stream;

@@ -193,6 +193,9 @@ int md_launch_gemm_tc(md_ctx* ctx, const __half* a, const __half* b, __half* c, 
 int md_launch_gemm_tc_ex(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
                          int b_layout, const md_epilogue& ep, size_t ldc, const md_push& push);
 
+// gemm_tc.cu: a kernel whose bounded wait runs out on purpose (md_selftest_bounded_wait)
+int md_launch_selftest_wait(md_ctx* ctx, unsigned limit_ms);
+
 // attention.cu
 int md_launch_sdpa(md_ctx* ctx, const __half* q, const __half* k, const __half* v, const uint8_t* mask, __half* out,
                    size_t n_heads, size_t q_len, size_t kv_len, size_t d,

@@ -38,12 +38,13 @@ constexpr unsigned long long WAIT_BUDGET_NS = 1000000000ull;  // 1 s
 
 // Bounded wait.  Returns false (and records the failure) instead of spinning forever.
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                            md_devflags* flags, unsigned site) {
+                                            md_devflags* flags, unsigned site,
+                                            unsigned long long budget_ns = WAIT_BUDGET_NS) {
     const unsigned long long t0 = global_ns();
     for (unsigned spin = 0;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if ((spin & 63u) == 63u && global_ns() - t0 > WAIT_BUDGET_NS) {
+        if ((spin & 63u) == 63u && global_ns() - t0 > budget_ns) {
             *abort_flag = 1;
             md_flag_timeout(flags, site);
             return false;
