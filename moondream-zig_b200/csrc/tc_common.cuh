@@ -80,16 +80,8 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                           uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// The same instruction with the descriptors given as 32-bit halves.  The issuing thread is a single lane, so
+// tcgen05.mma (kind::f16, one CTA) with the shared-memory descriptors given as 32-bit halves (layout below).
+// The issuing thread is a single lane, so
 // every instruction it spends between two MMAs is tensor-pipe idle time when the MMAs are small: the high words
 // (stride offset, version, swizzle) are loop constants and the low words (address | leading offset) advance by
 // plain 32-bit adds.  ACC = true accumulates into D, false overwrites it.
@@ -145,25 +137,14 @@ __device__ __forceinline__ void load8(const __half* p, float (&f)[8]) {
     }
 }
 
-// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
-//   K-major operand (rows of 64 halves = 128 B, 8-row groups 1024 B apart):
-//       leading offset unused (1), stride offset 1024 B.
-//   MN-major operand (64-element chunks of the MN dimension contiguous, k rows 128 B apart,
-//   8-k-row groups 1024 B apart, successive 64-element chunks `lbo_bytes` apart).
-// `layout` is the swizzle field of the descriptor: 2 = 128-byte swizzle, 4 = 64-byte, 6 = 32-byte, 0 = none.
-__device__ __forceinline__ uint64_t make_desc_sw(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
-                                                 uint32_t layout) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
-    d |= (uint64_t)1 << 46;  // version
-    d |= (uint64_t)layout << 61;
-    return d;
-}
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    return make_desc_sw(smem_addr, lbo_bytes, sbo_bytes, 2);
-}
-
+// Shared-memory matrix descriptor (version 1, sm_100) as built by desc_lo / desc_hi:
+//   bits 0-13 address >> 4, 16-29 leading byte offset >> 4, 32-45 stride byte offset >> 4, 46 version,
+//   61-63 swizzle (2 = 128-byte, 4 = 64-byte, 6 = 32-byte, 0 = none).
+//   K-major operand, 128B swizzle (rows of 64 halves = 128 B, 8-row groups 1024 B apart): leading offset
+//   unused (16), stride offset 1024 B; 16 k further = +32 B.
+//   MN-major operand, 128B swizzle (64-element chunks of the MN dimension contiguous, k rows 128 B apart,
+//   8-k-row groups 1024 B apart): leading offset = distance of successive 64-element chunks, stride offset
+//   1024 B; 16 k further = +2048 B.
+//   32B swizzle: rows of 16 halves = 32 B, 8-row groups 256 B apart (stride offset 256 B).
 
 }  // namespace tc
