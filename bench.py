@@ -374,11 +374,11 @@ def main():
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of gemv_nt_mma_kernel from the ncu capture summarised in
-# profiles/gemv_nt_mma_kernel__decode_gemv_sweep.md: 280.41 MB measured over the three captured launches
-# (fc1, fc2, lm_head at M = 1) against 276.97 MB of algorithmic bytes, a factor of 1.0124; traffic grows in
-# proportion to the weight bytes, so the average launch of the sweep is scaled by the same factor.
 SWEEP_BRANCHES = 4  # parallel chains the sweep graph is recorded as
+# dram__bytes_read.sum + dram__bytes_write.sum of gemv_nt_mma_kernel from an ncu capture of this workload (its
+# summary sits under profiles/): 280.41 MB measured over the three captured launches (fc1, fc2, lm_head at
+# M = 1) against 276.97 MB of algorithmic bytes, a factor of 1.0124; traffic grows in proportion to the weight
+# bytes, so the average launch of the sweep is scaled by the same factor.
 TRAFFIC_BYTES_PER_LAUNCH = int(round(1.0124 * STEP_BYTES / 20))
 
 
@@ -431,7 +431,7 @@ def colsplit_extras(ctx, torch, dist, stream, world, rank):
 
 
 def extras(ctx, torch, stream, tensor_peak, hbm_peak):
-    """Side measurements quoted in DESIGN.md: per-shape GEMV GB/s (rotating weight copies so every
+    """Side measurements: per-shape GEMV GB/s (rotating weight copies so every
     launch streams from HBM), config 1 (64x2048 . 2048x8192) and large GEMMs on the tcgen05 kernel."""
     out = {"gemv": [], "gemm": []}
 

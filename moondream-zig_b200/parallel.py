@@ -1,7 +1,6 @@
 """Multi-GPU plumbing for the hot path: one process per GPU, torch.distributed for rendezvous.
 
-Two things shard (SURVEY of the reference: it has no distributed code at all, so the split is
-this library's):
+Two things shard (the reference has no distributed code at all, so the split is this library's):
 
 * independent requests -> replicas.  Every GPU holds the full weights; request i runs on GPU
   i mod world.  No collective on the data path (``partition_requests``).
