@@ -319,6 +319,7 @@ def main():
     colsplit = None
     if world > 1 and not args.no_extras:
         colsplit = colsplit_extras(ctx, torch, dist, stream, world, rank)
+        decode_replicas = decode_replicas_extras(ctx, torch, dist, world)
 
     if rank != 0:
         ctx.sync()
@@ -349,7 +350,7 @@ def main():
         line["extras"] = extras(ctx, torch, stream, tensor_peak, hbm_peak)
         line["extras"].update(model_extras(ctx, torch))
     if colsplit is not None:
-        line["extras"] = {"colsplit_gemm_8192": colsplit}
+        line["extras"] = {"colsplit_gemm_8192": colsplit, "decode_config4_replicas": decode_replicas}
 
     # ---- CPU baseline: the oracle on this box's host cores, bounded sample
     from oracle import oracle
@@ -488,14 +489,11 @@ def extras(ctx, torch, stream, tensor_peak, hbm_peak):
     return out
 
 
-def model_extras(ctx, torch):
-    """End-to-end numbers of the callers around the hot path, random-init Moondream2 shapes generated on the
-    device: config 4 (prefill of 761 rows, 200 greedy decode steps, single stream and 8 batched streams)
-    and config 3 (vision encoder + projection for 1 / 5 / 13 crops)."""
+def build_text_model(ctx, torch, g):
+    """Random-init Moondream2 text decoder (24 layers, dim 2048, MLP 8192, vocab 51200) generated on the device."""
     import importlib
     import __graft_entry__ as entry
     models = importlib.import_module(entry.PKG_NAME + ".models")
-    g = torch.Generator(device="cuda").manual_seed(4000)
 
     def n(*shape, std=0.02):
         return (torch.randn(*shape, device="cuda", generator=g) * std).half()
@@ -510,24 +508,60 @@ def model_extras(ctx, torch):
          "ln_out_w": ones, "ln_out_b": zeros, "lm_w": n(V, D), "lm_b": n(V), "wte": n(V, D)}
     tm = models.TextModel(ctx, w)
     embeds = w["wte"][torch.randint(0, V, (761,), device="cuda", generator=g)].cpu().numpy()
-    out = {}
+    return models, n, w, tm, embeds
+
+
+def decode_config4(tm, embeds, sync=None):
+    """Config 4 on one request: prefill of 761 rows, 200 greedy steps. Returns (prefill seconds, decode seconds) of
+    the last of three repetitions; `sync` (a cross-rank barrier) runs before the timed decode when given."""
     req = tm.request()
     for _ in range(3):
         req.reset()
         t0 = time.perf_counter()
         _, _, tok = tm.forward(req, embeds, want_hidden=False, want_logits=False)
         t1 = time.perf_counter()
+        if sync:
+            sync()
+            t1 = time.perf_counter()
         tm.generate(req, tok, 200)
         t2 = time.perf_counter()
+    req.close()
+    return t1 - t0, t2 - t1
+
+
+def decode_replicas_extras(ctx, torch, dist, world):
+    """Decode tokens/s with one request per GPU (independent requests are partitioned over the GPUs: every rank holds
+    a full replica and decodes its own request, no collective on the data path).  Aggregate = world x 200 tokens
+    over the slowest rank's decode time."""
+    g = torch.Generator(device="cuda").manual_seed(4000)
+    _, _, w, tm, embeds = build_text_model(ctx, torch, g)
+    _, dec = decode_config4(tm, embeds, sync=dist.barrier)
+    t = torch.tensor([dec], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    tm.close()
+    del w, tm
+    torch.cuda.empty_cache()
+    return {"requests": world, "steps": 200, "prefill_rows": 761, "decode_tok_s_aggregate": round(world * 200 / t.item(), 1),
+            "decode_tok_s_per_gpu": round(200 / t.item(), 1),
+            "note": "one request per GPU, host wall clock around md_text_generate, max over ranks"}
+
+
+def model_extras(ctx, torch):
+    """End-to-end numbers of the callers around the hot path, random-init Moondream2 shapes generated on the
+    device: config 4 (prefill of 761 rows, 200 greedy decode steps, single stream and 8 batched streams)
+    and config 3 (vision encoder + projection for 1 / 5 / 13 crops)."""
+    g = torch.Generator(device="cuda").manual_seed(4000)
+    models, n, w, tm, embeds = build_text_model(ctx, torch, g)
+    out = {}
+    pre, dec = decode_config4(tm, embeds)
     weights_bytes = 24 * 100663296 + 209715200
     kv_bytes = 196608 * 861   # mean kv_len over steps 762..961
     out["text_config4"] = {
-        "prefill_761_ms": round((t1 - t0) * 1e3, 2), "decode_tok_s": round(200 / (t2 - t1), 1),
-        "us_per_token": round((t2 - t1) / 200 * 1e6, 1),
-        "hbm_GB/s": round((weights_bytes + kv_bytes) / ((t2 - t1) / 200) / 1e9, 1),
+        "prefill_761_ms": round(pre * 1e3, 2), "decode_tok_s": round(200 / dec, 1),
+        "us_per_token": round(dec / 200 * 1e6, 1),
+        "hbm_GB/s": round((weights_bytes + kv_bytes) / (dec / 200) / 1e9, 1),
         "note": "host wall clock around md_text_forward (H2D of the 761 embedding rows included) and md_text_generate "
                 "(200 graph replays + D2H of the tokens)"}
-    req.close()
     reqs = [tm.request() for _ in range(8)]
     for _ in range(2):
         for r in reqs:
