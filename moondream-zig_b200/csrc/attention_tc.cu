@@ -142,6 +142,15 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
 
     md_pdl_launch_dependents();
     if (threadIdx.x == 0) {
+        // the descriptors are kernel parameters: fetching them does not depend on the predecessor kernel
+        tma_prefetch_map(&tm.q);
+        tma_prefetch_map(&tm.k);
+        tma_prefetch_map(&tm.v);
+        if (TAIL) {
+            tma_prefetch_map(&tm.qt);
+            tma_prefetch_map(&tm.kt);
+            tma_prefetch_map(&tm.vt);
+        }
         mbar_init(b_qfull, 1);
         for (int s = 0; s < ST; ++s) {
             mbar_init(b_kfull + 8 * s, 1);

@@ -75,6 +75,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     // barriers and tensor memory, then waits for its predecessor before any global access
     md_pdl_launch_dependents();
     if (threadIdx.x == 0) {
+        // the descriptors are kernel parameters: fetching them does not depend on the predecessor kernel
+        tma_prefetch_map(&tm_a);
+        tma_prefetch_map(&tm_b);
+        tma_prefetch_map(&tm_c);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
