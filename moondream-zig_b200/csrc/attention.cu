@@ -563,7 +563,65 @@ sdpa_decode_kernel(DecodeParams p) {
     if (tid == 0) p.counters[head] = 0;  // ready for the next launch
 }
 
-// qkv [S, 3*H*d] -> rotated q [S, H*d], rotated k and raw v appended to the cache at pos..pos+S-1.
+// qkv [S, 3*H*d] -> rotated q [S, H*d], rotated k and raw v appended to the cache at pos..pos+S-1,
+// 8 dims (16 bytes) per thread: thread -> (row s, head h, 8-dim piece c).  A rotated piece needs its
+// partner piece half a rotary width away; both are single 16-byte loads.  Needs d % 8 == 0 and rot_dim % 16 == 0.
+__global__ void __launch_bounds__(256)
+rope_cache_write_vec_kernel(const __half* __restrict__ qkv, __half* __restrict__ q_rot, __half* __restrict__ kc,
+                            __half* __restrict__ vc, int S, int H, int d, int max_seq, int pos, int rot_dim,
+                            const float* __restrict__ tab) {
+    md_pdl_launch_dependents();
+    md_pdl_wait();
+    const int pieces = d >> 3, hd = H * d, half = rot_dim >> 1;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)S * H * pieces) return;
+    const int c = (int)(idx % pieces), h = (int)((idx / pieces) % H), s = (int)(idx / ((long long)pieces * H));
+    const int dd0 = c * 8;
+    const __half* row = qkv + (long long)s * 3 * hd + h * d;
+    auto ld8 = [](const __half* p, float (&f)[8]) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p);
+        const __half2* hh = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 x = __half22float2(hh[i]);
+            f[2 * i] = x.x;
+            f[2 * i + 1] = x.y;
+        }
+    };
+    auto st8 = [](__half* p, const float (&f)[8]) {
+        uint4 u;
+        __half2* hh = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) hh[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = u;
+    };
+    const long long cidx = ((long long)h * max_seq + pos + s) * d + dd0;
+    *reinterpret_cast<uint4*>(vc + cidx) = *reinterpret_cast<const uint4*>(row + 2 * hd + dd0);
+    if (dd0 >= rot_dim) {
+        *reinterpret_cast<uint4*>(q_rot + (long long)s * hd + h * d + dd0) = *reinterpret_cast<const uint4*>(row + dd0);
+        *reinterpret_cast<uint4*>(kc + cidx) = *reinterpret_cast<const uint4*>(row + hd + dd0);
+        return;
+    }
+    const bool lower = dd0 < half;
+    const int j0 = lower ? dd0 : dd0 - half, partner = lower ? dd0 + half : dd0 - half;
+    float q[8], qp[8], k[8], kp[8], qo[8], ko[8];
+    ld8(row + dd0, q);
+    ld8(row + partner, qp);
+    ld8(row + hd + dd0, k);
+    ld8(row + hd + partner, kp);
+    const float2* cs = reinterpret_cast<const float2*>(tab + ((size_t)(pos + s) * half + j0) * 2);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float cc = cs[i].x, sn = cs[i].y;
+        // lower half: x[j] * cos - x[j + half] * sin; upper half: x[j] * sin + x[j + half] * cos (rope.zig:130-216)
+        qo[i] = lower ? q[i] * cc - qp[i] * sn : qp[i] * sn + q[i] * cc;
+        ko[i] = lower ? k[i] * cc - kp[i] * sn : kp[i] * sn + k[i] * cc;
+    }
+    st8(q_rot + (long long)s * hd + h * d + dd0, qo);
+    st8(kc + cidx, ko);
+}
+
+// The same step one element per thread iteration, for head dims or rotary widths the vector form cannot take.
 __global__ void __launch_bounds__(128)
 rope_cache_write_kernel(const __half* __restrict__ qkv, __half* __restrict__ q_rot, __half* __restrict__ kc,
                         __half* __restrict__ vc, int S, int H, int d, int max_seq, int pos, int rot_dim,
@@ -741,8 +799,18 @@ int md_launch_rope_cache_write(md_ctx* ctx, const __half* qkv, __half* q_rot, __
     if (S == 0) return MD_OK;
     const float* tab = nullptr;
     MD_TRY(md_rope_cached(ctx, rot_dim, theta, max_seq, &tab));
-    MD_TRY(md_launch_ex(ctx, rope_cache_write_kernel, dim3((unsigned)S), dim3(128), 0, "rope_cache_write_kernel", qkv, q_rot,
-                        kc, vc, (int)S, (int)n_heads, (int)d, (int)max_seq, (int)pos, (int)rot_dim, tab));
+    const bool vec = (d % 8) == 0 && (rot_dim % 16) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_rot) | reinterpret_cast<uintptr_t>(kc) |
+                       reinterpret_cast<uintptr_t>(vc)) & 15) == 0;
+    if (vec) {
+        const size_t units = S * n_heads * (d / 8);
+        MD_TRY(md_launch_ex(ctx, rope_cache_write_vec_kernel, dim3((unsigned)((units + 255) / 256)), dim3(256), 0,
+                            "rope_cache_write_vec_kernel", qkv, q_rot, kc, vc, (int)S, (int)n_heads, (int)d, (int)max_seq,
+                            (int)pos, (int)rot_dim, tab));
+    } else {
+        MD_TRY(md_launch_ex(ctx, rope_cache_write_kernel, dim3((unsigned)S), dim3(128), 0, "rope_cache_write_kernel", qkv,
+                            q_rot, kc, vc, (int)S, (int)n_heads, (int)d, (int)max_seq, (int)pos, (int)rot_dim, tab));
+    }
     return MD_OK;
 }
 
