@@ -9,6 +9,10 @@
 //               shared-memory descriptors; accumulators live in TMEM, two buffers of
 //               BLOCK_N columns so the epilogue of tile i overlaps the main loop of tile i+1.
 //               tcgen05.commit releases smem stages and publishes finished accumulators.
+//               Large problems use a 256 x 256 tile: two 128-row sub-tiles of A against one B
+//               tile per k-block (two MMAs per k-step, accumulators in TMEM columns 0-255 and
+//               256-511), because the kernel is bound by the bytes an SM pulls from L2 per flop:
+//               64 KB per 1024 tensor cycles instead of 48 KB per 512.
 //   warps 2..9  epilogue: tcgen05.ld (32 lanes x 32 columns) -> fused glue -> f16 ->
 //               swizzled smem -> TMA store (clips the M and N tails).
 // Tails: TMA zero-fills out-of-bounds loads and clips out-of-bounds stores, so any M, N, K
@@ -30,34 +34,42 @@ constexpr int NUM_THREADS = (2 + EPI_WARPS) * 32;
 constexpr int SMEM_LIMIT = 232448;                       // 227 KiB opt-in maximum
 constexpr int BAR_BYTES = 1024;
 
-__host__ __device__ constexpr int stage_bytes(int block_n) { return A_STAGE_BYTES + block_n * BLOCK_K * 2; }
-__host__ __device__ constexpr int num_stages(int block_n) {
-    int s = (SMEM_LIMIT - 1024 /*alignment slack*/ - EPI_BYTES - BAR_BYTES) / stage_bytes(block_n);
+// mt = number of 128-row sub-tiles of A per CTA tile (1 or 2): with 2 the tile is 256 x 256, both sub-tiles
+// share one B tile, and a k-block costs 64 KB for 1024 cycles of tensor time instead of 48 KB for 512.
+__host__ __device__ constexpr int stage_bytes(int block_n, int mt) { return mt * A_STAGE_BYTES + block_n * BLOCK_K * 2; }
+__host__ __device__ constexpr int num_stages(int block_n, int mt) {
+    int s = (SMEM_LIMIT - 1024 /*alignment slack*/ - EPI_BYTES - BAR_BYTES) / stage_bytes(block_n, mt);
     return s > 10 ? 10 : s;
 }
-__host__ __device__ constexpr int smem_bytes(int block_n) {
-    return 1024 + num_stages(block_n) * stage_bytes(block_n) + EPI_BYTES + BAR_BYTES;
+__host__ __device__ constexpr int smem_bytes(int block_n, int mt) {
+    return 1024 + num_stages(block_n, mt) * stage_bytes(block_n, mt) + EPI_BYTES + BAR_BYTES;
 }
 
 using namespace tc;
 
-template <int BLOCK_N, bool B_MN_MAJOR>
+template <int BLOCK_N, bool B_MN_MAJOR, int MT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_c, int M, int N, int K, int tiles_m, int num_tiles,
                md_epilogue ep, md_push push, md_devflags* flags) {
-    constexpr int STAGES = num_stages(BLOCK_N);
+    constexpr int STAGES = num_stages(BLOCK_N, MT);
+    constexpr int A_TILE_BYTES = MT * A_STAGE_BYTES;   // MT sub-tiles of 128 rows, one after the other
     constexpr int B_STAGE_BYTES = BLOCK_N * BLOCK_K * 2;
-    constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    constexpr int STAGE_BYTES = A_TILE_BYTES + B_STAGE_BYTES;
+    // accumulators: MT == 1: two buffers of BLOCK_N columns (the epilogue of tile i overlaps the main loop of
+    // tile i+1); MT == 2: the two sub-tiles fill all 512 columns, one buffer
+    constexpr int NBUF = MT == 1 ? 2 : 1;
     constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // 128, 256 or 512: a power of two >= 32
+    constexpr int TILE_M = MT * BLOCK_M, CHUNKS_N = BLOCK_N / 64, CHUNKS = MT * CHUNKS_N;
     static_assert(BLOCK_N == 64 || BLOCK_N == 128 || BLOCK_N == 256, "BLOCK_N");
+    static_assert(MT == 1 || (MT == 2 && BLOCK_N == 256), "two sub-tiles only with 256-wide tiles");
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - raw);
     const uint32_t smem_a = base;
-    const uint32_t smem_b = base + STAGES * A_STAGE_BYTES;
+    const uint32_t smem_b = base + STAGES * A_TILE_BYTES;
     const uint32_t smem_epi = base + STAGES * STAGE_BYTES;
     uint8_t* epi_ptr = base_ptr + STAGES * STAGE_BYTES;
     const uint32_t bars = smem_epi + EPI_BYTES;
@@ -109,12 +121,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             int stage = 0;
             uint32_t phase = 0;
             for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-                const int m0 = (tile % tiles_m) * BLOCK_M, n0 = (tile / tiles_m) * BLOCK_N;
+                const int m0 = (tile % tiles_m) * TILE_M, n0 = (tile / tiles_m) * BLOCK_N;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, flags, 1);
                     const uint32_t full = bar_full + 8 * stage;
                     mbar_expect_tx(full, STAGE_BYTES);
-                    tma_load_2d(smem_a + stage * A_STAGE_BYTES, &tm_a, full, kb * BLOCK_K, m0);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+                        tma_load_2d(smem_a + stage * A_TILE_BYTES + mt * A_STAGE_BYTES, &tm_a, full, kb * BLOCK_K,
+                                    m0 + mt * BLOCK_M);
                     if (B_MN_MAJOR) {
 #pragma unroll
                         for (int j = 0; j < BLOCK_N / 64; ++j)
@@ -147,21 +162,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             uint32_t phase = 0;
             int local = 0;
             for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
-                const int buf = local & 1;
-                const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+                const int buf = local % NBUF;
+                const uint32_t acc_phase = (uint32_t)(local / NBUF) & 1u;
                 mbar_wait(bar_tempty + 8 * buf, acc_phase ^ 1u, abort_flag, flags, 2);
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BLOCK_N);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     mbar_wait(bar_full + 8 * stage, phase, abort_flag, flags, 3);
                     tc_fence_after();
-                    const uint32_t a_lo = a_lo0 + (uint32_t)stage * (A_STAGE_BYTES >> 4);
+                    const uint32_t a_lo = a_lo0 + (uint32_t)stage * (A_TILE_BYTES >> 4);
                     const uint32_t b_lo = b_lo0 + (uint32_t)stage * (B_STAGE_BYTES >> 4);
-                    if (kb == 0) tc_mma_f16_parts<false>(tmem_d, a_lo, a_hi, b_lo, b_hi, idesc);
-                    else tc_mma_f16_parts<true>(tmem_d, a_lo, a_hi, b_lo, b_hi, idesc);
 #pragma unroll
-                    for (int k = 1; k < BLOCK_K / UMMA_K; ++k)
-                        tc_mma_f16_parts<true>(tmem_d, a_lo + k * A_KSTEP, a_hi, b_lo + k * B_KSTEP, b_hi, idesc);
+                    for (int mt = 0; mt < MT; ++mt) {
+                        // sub-tile mt: rows mt*128.. of the A tile, accumulator columns mt*256..
+                        const uint32_t d = tmem_d + (uint32_t)(mt * 256), am = a_lo + (uint32_t)(mt * (A_STAGE_BYTES >> 4));
+                        if (kb == 0) tc_mma_f16_parts<false>(d, am, a_hi, b_lo, b_hi, idesc);
+                        else tc_mma_f16_parts<true>(d, am, a_hi, b_lo, b_hi, idesc);
+                    }
+#pragma unroll
+                    for (int k = 1; k < BLOCK_K / UMMA_K; ++k) {
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt)
+                            tc_mma_f16_parts<true>(tmem_d + (uint32_t)(mt * 256),
+                                                   a_lo + (uint32_t)(mt * (A_STAGE_BYTES >> 4)) + k * A_KSTEP, a_hi,
+                                                   b_lo + k * B_KSTEP, b_hi, idesc);
+                    }
                     tc_commit(bar_empty + 8 * stage);  // frees the smem stage once these MMAs retire
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -178,15 +203,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const bool any_glue = ep.bias || ep.residual || ep.residual2 || ep.gelu;
         int local = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
-            const int m0 = (tile % tiles_m) * BLOCK_M, n0 = (tile / tiles_m) * BLOCK_N;
-            const int buf = local & 1;
-            const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+            const int m0 = (tile % tiles_m) * TILE_M, n0 = (tile / tiles_m) * BLOCK_N;
+            const int buf = local % NBUF;
+            const uint32_t acc_phase = (uint32_t)(local / NBUF) & 1u;
             mbar_wait(bar_tfull + 8 * buf, acc_phase, abort_flag, flags, 4);
             tc_fence_after();
-            const int row = m0 + quad * 32 + lane;
-            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BLOCK_N);
 #pragma unroll 1
-            for (int c = half; c < BLOCK_N / 64; c += 2) {
+            for (int cc = half; cc < CHUNKS; cc += 2) {
+                // chunk cc = 64 columns c of sub-tile mt
+                const int mt = cc / CHUNKS_N, c = cc % CHUNKS_N;
+                const int mrow0 = m0 + mt * BLOCK_M + quad * 32, row = mrow0 + lane;
+                const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BLOCK_N + mt * 256);
                 // the staging buffer must have been read by this warp's previous TMA store
                 if (lane == 0) tma_store_wait_read<0>();
                 __syncwarp();
@@ -242,7 +269,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         *reinterpret_cast<uint4*>(out_row + chunk * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                     }
                 }
-                if (c + 2 >= BLOCK_N / 64) {
+                if (cc + 2 >= CHUNKS) {
                     // all of this warp's TMEM reads of the tile are done: hand the buffer back
                     tc_fence_before();
                     __syncwarp();
@@ -251,7 +278,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    tma_store_2d(&tm_c, my_epi, n0 + c * 64, m0 + quad * 32);
+                    tma_store_2d(&tm_c, my_epi, n0 + c * 64, mrow0);
                     tma_store_commit();
                 }
                 if (push.n > 0) {
@@ -261,7 +288,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     for (int it = 0; it < 8; ++it) {
                         const int r = it * 4 + (lane >> 3), ch = lane & 7;
                         const uint4 val = *reinterpret_cast<const uint4*>(my_epi_ptr + r * 128 + ((ch ^ (r & 7)) * 16));
-                        const int gm = m0 + quad * 32 + r, gc = n0 + c * 64 + ch * 8;
+                        const int gm = mrow0 + r, gc = n0 + c * 64 + ch * 8;
                         if (gm < M && gc < N) {
                             for (int pi = 0; pi < push.n; ++pi)
                                 *reinterpret_cast<uint4*>(push.base[pi] + (long long)gm * push.ld + gc) = val;
@@ -269,7 +296,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                 }
             }
-            if (half >= BLOCK_N / 64) {
+            if (half >= CHUNKS) {
                 // a warp without a chunk (tile narrower than its share) still releases the accumulator
                 tc_fence_before();
                 __syncwarp();
@@ -320,7 +347,7 @@ int make_map_2d(md_ctx* ctx, CUtensorMap* map, const void* ptr, uint64_t inner, 
     return MD_OK;
 }
 
-template <int BLOCK_N, bool B_MN_MAJOR>
+template <int BLOCK_N, bool B_MN_MAJOR, int MT = 1>
 int launch(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
            const md_epilogue& ep, size_t ldc, const md_push& push) {
     CUtensorMap tm_a, tm_b, tm_c;
@@ -328,12 +355,13 @@ int launch(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, s
     if (B_MN_MAJOR) MD_TRY(make_map_2d(ctx, &tm_b, b, N, K, 64, BLOCK_K));
     else MD_TRY(make_map_2d(ctx, &tm_b, b, K, N, BLOCK_K, BLOCK_N));
     MD_TRY(make_map_2d(ctx, &tm_c, c, N, M, 64, 32, ldc));
-    const int tiles_m = (int)((M + BLOCK_M - 1) / BLOCK_M), tiles_n = (int)((N + BLOCK_N - 1) / BLOCK_N);
+    const int tiles_m = (int)((M + MT * BLOCK_M - 1) / (MT * BLOCK_M)), tiles_n = (int)((N + BLOCK_N - 1) / BLOCK_N);
     const int num_tiles = tiles_m * tiles_n;
     const int grid = num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count;
-    auto kern = gemm_tc_kernel<BLOCK_N, B_MN_MAJOR>;
-    constexpr int smem = smem_bytes(BLOCK_N);
-    const uint32_t cfg_bit = 1u << ((BLOCK_N == 256 ? 0 : BLOCK_N == 128 ? 1 : 2) + (B_MN_MAJOR ? 3 : 0));
+    auto kern = gemm_tc_kernel<BLOCK_N, B_MN_MAJOR, MT>;
+    constexpr int smem = smem_bytes(BLOCK_N, MT);
+    const uint32_t cfg_bit = MT == 2 ? (1u << (B_MN_MAJOR ? 12 : 11))
+                                     : 1u << ((BLOCK_N == 256 ? 0 : BLOCK_N == 128 ? 1 : 2) + (B_MN_MAJOR ? 3 : 0));
     if (!(ctx->tc_configured & cfg_bit)) {
         MD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         ctx->tc_configured |= cfg_bit;
@@ -368,32 +396,37 @@ int md_launch_gemm_tc_ex(md_ctx* ctx, const __half* a, const __half* b, __half* 
         return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 GEMM: residuals are not supported with a strided output");
     if (!md_gemm_tc_supported(a, b, c, M, N, K, b_layout))
         return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 GEMM needs K %% 8 == 0, N %% 8 == 0 and 16-byte aligned operands");
-    // Tile width: the widest tile that still gives every SM work; narrow tiles for skinny
-    // problems, which are bandwidth-bound and want many CTAs streaming B.
-    const size_t tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
-    auto tiles = [&](size_t bn) { return tiles_m * ((N + bn - 1) / bn); };
-    // Cost model: (waves over the SMs) x (time of one tile); a tile's time grows with its width,
-    // narrower tiles run the tensor pipe less efficiently (smem bandwidth per MMA).  Skinny
-    // problems (M <= 64) are bandwidth-bound and take the narrowest tile to get many CTAs.
-    int bn = 64;
+    // Tile shape.  The kernel is bound by the bytes an SM pulls from L2 per k-block, (rows + columns) x 128,
+    // so a tile's time is proportional to its rows + columns: 128 x 64, 128 x 128, 128 x 256, or 256 x 256 (two
+    // 128-row sub-tiles sharing one B tile).  Cost = (waves over the SMs) x (rows + columns).  Skinny problems
+    // (M <= 64) are HBM-bound and take the narrowest tile to get many CTAs streaming B.
+    int bn = 64, mt = 1;
     if (M > 64) {
-        const int cand[3] = {256, 128, 64};
-        const double eff[3] = {1.0, 0.78, 0.65};
+        const int cand_n[4] = {256, 256, 128, 64}, cand_mt[4] = {2, 1, 1, 1};
         double best = 0;
-        for (int i = 0; i < 3; ++i) {
-            const size_t t = tiles(cand[i]);
+        for (int i = 0; i < 4; ++i) {
+            if (cand_mt[i] == 2 && push.n > 0) continue;  // the peer-push epilogue is written for 128-row tiles
+            const size_t rows = (size_t)cand_mt[i] * BLOCK_M;
+            const size_t t = ((M + rows - 1) / rows) * ((N + cand_n[i] - 1) / cand_n[i]);
             const size_t waves = (t + ctx->sm_count - 1) / ctx->sm_count;
-            const double cost = (double)waves * cand[i] / eff[i];
-            if (i == 0 || cost < best) { best = cost; bn = cand[i]; }
+            // measured: the 256 x 256 tile moves ~42 B per cycle against ~55 for the 128-row tiles (three ring
+            // stages, epilogue not overlapped), hence the factor 1.3 on its bytes
+            const double cost = (double)waves * (double)(rows + cand_n[i]) * (cand_mt[i] == 2 ? 1.3 : 1.0);
+            if (i == 0 || cost < best) { best = cost; bn = cand_n[i]; mt = cand_mt[i]; }
         }
     }
-    if (ctx->tc_block_n) bn = ctx->tc_block_n;
+    if (ctx->tc_block_n) {  // forced: 512 = the 256 x 256 tile
+        bn = ctx->tc_block_n == 512 ? 256 : ctx->tc_block_n;
+        mt = ctx->tc_block_n == 512 ? 2 : 1;
+    }
     const bool mn = (b_layout == 0);
     if (mn) {
+        if (mt == 2) return launch<256, true, 2>(ctx, a, b, c, M, N, K, ep, ldc, push);
         if (bn == 256) return launch<256, true>(ctx, a, b, c, M, N, K, ep, ldc, push);
         if (bn == 128) return launch<128, true>(ctx, a, b, c, M, N, K, ep, ldc, push);
         return launch<64, true>(ctx, a, b, c, M, N, K, ep, ldc, push);
     }
+    if (mt == 2) return launch<256, false, 2>(ctx, a, b, c, M, N, K, ep, ldc, push);
     if (bn == 256) return launch<256, false>(ctx, a, b, c, M, N, K, ep, ldc, push);
     if (bn == 128) return launch<128, false>(ctx, a, b, c, M, N, K, ep, ldc, push);
     return launch<64, false>(ctx, a, b, c, M, N, K, ep, ldc, push);

@@ -320,7 +320,8 @@ int md_set_option(md_ctx* ctx, const char* key, long value) {
     if (!strcmp(key, "persistent_decode")) { ctx->persistent_decode = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "attn_tc")) { ctx->attn_tc = value < 0 ? -1 : value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "tc_block_n")) {
-        MD_NEED(ctx, value == 0 || value == 64 || value == 128 || value == 256, "tc_block_n must be 0, 64, 128 or 256");
+        MD_NEED(ctx, value == 0 || value == 64 || value == 128 || value == 256 || value == 512,
+                "tc_block_n must be 0, 64, 128, 256 or 512 (512 = the 256 x 256 tile)");
         ctx->tc_block_n = (int)value;
         return MD_OK;
     }

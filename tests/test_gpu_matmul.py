@@ -170,6 +170,38 @@ def test_fused_epilogue_keeps_reference_rounding(ctx, oracle, m, k, n, layout):
         b.free()
 
 
+@pytest.mark.parametrize("layout", [0, 1])
+@pytest.mark.parametrize("m,k,n", [(300, 256, 512), (513, 384, 776), (1000, 1152, 4304), (256, 64, 256), (129, 8, 8)])
+def test_tile_256x256(ctx, oracle, m, k, n, layout):
+    """The 256 x 256 tile (two 128-row sub-tiles sharing one B tile, option tc_block_n = 512), forced on shapes
+    with ragged M, N and K, with the fused bias / GELU / residual epilogue, against the oracle and against the
+    128 x 256 tile."""
+    rng = np.random.default_rng(m + n + k)
+    a = f16_normal(rng, (m, k))
+    w_kn = f16_normal(rng, (k, n), 0.05)
+    bias, res = f16_normal(rng, (n,), 0.5), f16_normal(rng, (m, n))
+    w = w_kn if layout == 0 else np.ascontiguousarray(w_kn.T)
+    ref = oracle.hgemm_nn(a, w_kn) if layout == 0 else oracle.hgemm_nt(a, w)
+    ref = oracle.add(oracle.gelu(oracle.bias_add(ref, bias)), res)
+    da, dw, db, dr = ctx.upload(a), ctx.upload(w), ctx.upload(bias), ctx.upload(res)
+    outs = {}
+    for bn in (512, 256):
+        ctx.set_option("tc_block_n", bn)
+        try:
+            out = ctx.alloc((m, n))
+            for _ in range(3):      # consecutive launches: the single accumulator buffer is handed back every tile
+                ctx.hgemm_fused(da, dw, out, m, n, k, layout, bias=db, gelu=True, residual=dr)
+            ctx.sync()
+            outs[bn] = out.numpy()
+            out.free()
+        finally:
+            ctx.set_option("tc_block_n", 0)
+    assert_close_ref(outs[512], ref, "256 x 256 tile")
+    np.testing.assert_array_equal(outs[512], outs[256])   # same k order, same roundings: identical bits
+    for b in (da, dw, db, dr):
+        b.free()
+
+
 def test_linearity_at_full_size(ctx):
     """Size-independent property at the lm_head size: (a1 + a2) W == a1 W + a2 W up to rounding,
     and a one-hot activation selects a weight column exactly."""
