@@ -409,9 +409,14 @@ int md_launch_gemm_tc_ex(md_ctx* ctx, const __half* a, const __half* b, __half* 
             const size_t rows = (size_t)cand_mt[i] * BLOCK_M;
             const size_t t = ((M + rows - 1) / rows) * ((N + cand_n[i] - 1) / cand_n[i]);
             const size_t waves = (t + ctx->sm_count - 1) / ctx->sm_count;
-            // measured: the 256 x 256 tile moves ~42 B per cycle against ~55 for the 128-row tiles (three ring
-            // stages, epilogue not overlapped), hence the factor 1.3 on its bytes
-            const double cost = (double)waves * (double)(rows + cand_n[i]) * (cand_mt[i] == 2 ? 1.3 : 1.0);
+            // per tile: (rows + columns) per k-block; measured, the 256 x 256 tile moves ~42 B per cycle against
+            // ~55 for the 128-row tiles (three ring stages), hence the factor 1.3, and its epilogue is not hidden
+            // behind the next tile's main loop (one accumulator buffer): a fixed cost per tile, larger with glue
+            const double kblocks = (double)((K + BLOCK_K - 1) / BLOCK_K);
+            const bool glue = ep.bias || ep.gelu || ep.residual || ep.residual2;
+            const double tile = (double)(rows + cand_n[i]) * kblocks * (cand_mt[i] == 2 ? 1.3 : 1.0) +
+                                (cand_mt[i] == 2 ? (glue ? 7000.0 : 2500.0) : 0.0);
+            const double cost = (double)waves * tile;
             if (i == 0 || cost < best) { best = cost; bn = cand_n[i]; mt = cand_mt[i]; }
         }
     }
