@@ -87,7 +87,8 @@ int md_set_gemm_mode(md_ctx* ctx, int mode);
 
 /* Tuning knobs for tests and profiling; unknown keys return MD_ERR_INVALID_ARG.
  *   "gemv_variant"  0 = automatic, 1..6 = a fixed (warps, unroll) configuration of the GEMV kernel
- *   "tc_block_n"    0 = automatic, 64 / 128 / 256 = fixed tile width of the tcgen05 GEMM
+ *   "tc_block_n"    0 = automatic, 64 / 128 / 256 = fixed tile width of the tcgen05 GEMM (128-row tiles),
+ *                   512 = the 256 x 256 tile
  *   "pdl"           1 = launch the GEMV kernels with programmatic dependent launch: a kernel starts
  *                   streaming its weights while its predecessor on the stream drains.  Only for streams
  *                   on which no earlier kernel writes the weight matrices (registered weights).
