@@ -97,6 +97,7 @@ int md_set_gemm_mode(md_ctx* ctx, int mode);
  *   "decode_cluster" 0 = merge the decode attention splits through global scratch instead of a CTA cluster
  *   "attn_tc"       -1 (default) = tcgen05 attention when the operands allow it and q_len > 64,
  *                   0 = mma.sync attention only, 1 = tcgen05 only (MD_ERR_UNSUPPORTED otherwise)
+ *   "prefill_fork"  1 (default) = a prefill layer runs fc1 -> fc2 as a second kernel chain beside the attention
  *   "decode_fork"   1 (default) = the fused decode layer runs as two concurrent kernel chains (q/k/v projection ->
  *                   attention -> out-projection | fc1 -> fc2) joined by events, 0 = three kernels in a row
  *   "persistent_decode" 1 = a decode step runs as one cooperative persistent kernel (default 0: measured

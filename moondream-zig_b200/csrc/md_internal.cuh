@@ -74,6 +74,7 @@ struct md_ctx {
     int dualk_variant = 0;   // md_set_option("dualk_variant"): (warps, unroll) of gemv_dual_k_kernel
     int fused_decode = 1;    // md_set_option("fused_decode"): decode layers as 3 fused kernels
     int pdl = 0;             // md_set_option("pdl"): programmatic dependent launch for the GEMV kernels
+    int prefill_fork = 1;       // md_set_option("prefill_fork"): prefill layers run the MLP beside the attention
     int decode_fork = 1;        // md_set_option("decode_fork"): a decode layer runs as two concurrent kernel chains
     cudaStream_t side_stream = nullptr;  // second chain of the forked decode layer
     cudaEvent_t ev_fork = nullptr, ev_side = nullptr;

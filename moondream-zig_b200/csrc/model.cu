@@ -247,6 +247,32 @@ int text_layer(md_text_model* m, size_t layer, const LayerIO& io, size_t rows, b
                                      H(m->bfc2[layer]), F, io.hidden, D, rows);
     }
     MD_TRY(md_launch_layernorm(ctx, io.hidden, H(m->ln_w[layer]), H(m->ln_b[layer]), io.ln, rows, D, eps_of(w.eps_f16)));
+    // Prefill: the MLP of a Phi layer reads the same LayerNorm output as the attention, so fc1 -> fc2 run as a
+    // second kernel chain beside qkv -> rope -> attention; the GEMMs of one chain that cover only part of the SMs
+    // (96 tiles for the 2048-wide outputs at 761 rows) leave the rest to the other chain.  The chains meet in the
+    // out-projection's epilogue (same roundings as the sequential form, text_model.zig:162-171).
+    const bool fork_prefill = !decode && ctx->prefill_fork && rows > 8;
+    if (fork_prefill) {
+        if (!ctx->side_stream) {
+            MD_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking));
+            MD_CUDA(ctx, cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming));
+            MD_CUDA(ctx, cudaEventCreateWithFlags(&ctx->ev_side, cudaEventDisableTiming));
+        }
+        cudaStream_t main_stream = ctx->stream;
+        MD_CUDA(ctx, cudaEventRecord(ctx->ev_fork, main_stream));  // LayerNorm output ready
+        MD_CUDA(ctx, cudaStreamWaitEvent(ctx->side_stream, ctx->ev_fork, 0));
+        ctx->stream = ctx->side_stream;
+        md_epilogue e_fc1, e_fc2;
+        e_fc1.bias = H(m->bfc1[layer]);
+        e_fc1.gelu = 1;
+        e_fc2.bias = H(m->bfc2[layer]);
+        int st = md_gemm_dispatch(ctx, io.ln, H(m->wfc1[layer]), io.fc1, rows, F, D, 1, e_fc1);
+        if (st == MD_OK) st = md_gemm_dispatch(ctx, io.fc1, H(m->wfc2[layer]), io.attn_out, rows, D, F, 1, e_fc2);
+        if (st == MD_OK && cudaEventRecord(ctx->ev_side, ctx->side_stream) != cudaSuccess)
+            st = md_fail(ctx, MD_ERR_CUDA, "cudaEventRecord on the side stream failed");
+        ctx->stream = main_stream;
+        MD_TRY(st);
+    }
     md_epilogue e_qkv;
     e_qkv.bias = H(m->bqkv[layer]);
     MD_TRY(md_gemm_dispatch(ctx, io.ln, H(m->wqkv[layer]), io.qkv, rows, 3 * D, D, 1, e_qkv));
@@ -269,6 +295,13 @@ int text_layer(md_text_model* m, size_t layer, const LayerIO& io, size_t rows, b
     }
     md_epilogue e_out;
     e_out.bias = H(m->bout[layer]);
+    if (fork_prefill) {
+        // join the MLP chain: attn_out = f16(f16(acc) + b); attn_out += mlp_out; hidden += attn_out
+        MD_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_side, 0));
+        e_out.residual = io.attn_out;  // mlp_out, written by the side chain
+        e_out.residual2 = io.hidden;   // updated in place
+        return md_gemm_dispatch(ctx, io.attn, H(m->wout[layer]), io.hidden, rows, D, D, 1, e_out);
+    }
     MD_TRY(md_gemm_dispatch(ctx, io.attn, H(m->wout[layer]), io.attn_out, rows, D, D, 1, e_out));
     md_epilogue e_fc1;
     e_fc1.bias = H(m->bfc1[layer]);

@@ -109,6 +109,34 @@ def test_text_fused_decode_layer_matches_unfused_kernels(ctx, models_mod):
     gpu.close()
 
 
+def test_text_forked_prefill_equals_the_sequential_prefill(ctx, models_mod):
+    """Option prefill_fork (default on): fc1 -> fc2 as a second kernel chain beside qkv -> rope -> attention, joined
+    in the out-projection's epilogue.  Same kernels on the same operands with the same roundings: hidden states and
+    logits are bit-identical to the sequential form, for a fresh prompt and for a chunk appended at an offset."""
+    w = text_weights(4009, n_layers=3, hidden=8192, vocab=4096)
+    gpu = models_mod.TextModel(ctx, w)
+    rng = np.random.default_rng(9)
+    chunks = [w["wte"][rng.integers(0, 4096, n)] for n in (150, 37)]
+    res = {}
+    for fork in (1, 0):
+        ctx.set_option("prefill_fork", fork)
+        try:
+            req = gpu.request()
+            outs = []
+            for c in chunks:
+                h, lg, tok = gpu.forward(req, c, want_hidden=True, want_logits=True)
+                outs.append((np.array(h), np.array(lg), int(tok)))
+            res[fork] = outs
+            req.close()
+        finally:
+            ctx.set_option("prefill_fork", 1)
+    for (h1, l1, t1), (h0, l0, t0) in zip(res[1], res[0]):
+        np.testing.assert_array_equal(h1, h0)
+        np.testing.assert_array_equal(l1, l0)
+        assert t1 == t0
+    gpu.close()
+
+
 def test_text_forked_decode_layer_matches_the_three_kernel_layer(ctx, models_mod):
     """Option decode_fork (default on): attention chain and MLP chain of a layer as concurrent kernel chains.
     Same rounding points as the three-kernel layer; single request and a batch."""
