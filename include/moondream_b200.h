@@ -45,7 +45,9 @@ typedef enum md_status {
     MD_ERR_OOM = 7,              /* error.OutOfMemory */
     MD_ERR_CUDA = 8,
     MD_ERR_TIMEOUT = 9,          /* a bounded device-side wait gave up; results are invalid */
-    MD_ERR_NO_DEVICE = 10
+    MD_ERR_NO_DEVICE = 10,
+    MD_ERR_IO = 11,              /* a file could not be opened, mapped or read to its stated length (error.InvalidRead) */
+    MD_ERR_FORMAT = 12           /* a weight file that is not what weights.zig accepts; md_last_error names the Zig error */
 } md_status;
 
 typedef struct md_ctx md_ctx;

@@ -114,6 +114,54 @@ int md_vision_model_destroy(md_vision_model* model);
 int md_vision_encode(md_vision_model* model, const uint8_t* crops_u8, size_t crops, size_t crop_a, size_t crop_b,
                      uint16_t* features_out, uint16_t* out);
 
+/* ---- moondream.bin weight file (read: weights.zig:61-207; written by weights.py:82-246) --------------
+ *
+ * Layout, little-endian: u32 magic 0x4D4F4F4E ("MOON"), u32 version 2, then records until end of file:
+ *   u32 name_length (<= 256), u32 shape_length (<= 4), u32 data_length (element count; written, never read),
+ *   name bytes, shape_length x u64 dims, prod(dims) x f16.
+ * The 36 tensor names and their expected shapes follow from the model configuration (weights.zig:439-478);
+ * per-layer tensors are stacked on a leading n_layers axis.
+ *
+ * md_weight_file_open parses and validates on the host only (no device, no context): the file is mapped
+ * read-only and every record is checked in the reference's order.  Failures and the Zig error each stands for
+ * (the name is the first word of md_last_error(NULL)):
+ *   MD_ERR_IO      FileNotFound (open / map failed), InvalidRead (file ends inside a field)
+ *   MD_ERR_FORMAT  InvalidMagicNumber, InvalidVersion, InvalidHeader (1..11 trailing bytes), InvalidNameLength,
+ *                  InvalidShapeLength, UnknownTensorName, ShapeMismatch
+ * A name that occurs twice keeps its last occurrence, as the reference does.  Unlike the reference, which leaves
+ * the field undefined, a tensor that never occurs is reported (MissingTensor, MD_ERR_FORMAT) by
+ * md_weight_file_text / md_weight_file_vision. */
+
+typedef struct md_model_config {     /* config.zig:3-27, 86-112 */
+    size_t vocab, dim, hidden_dim, n_layers, n_heads, head_dim, seq_len;
+    float rope_theta, partial_rotary_factor;
+    size_t img_channels, img_dim, patch_size, num_patches, vit_dim, n_vit_layers, n_vit_heads, vit_head_dim,
+        hidden_features;
+} md_model_config;
+/* MODEL_CONFIG of config.zig:3-27. */
+int md_model_config_default(md_model_config* cfg);
+
+typedef struct md_weight_file md_weight_file;
+
+/* cfg NULL = md_model_config_default. */
+int md_weight_file_open(const char* path, const md_model_config* cfg, md_weight_file** out);
+int md_weight_file_close(md_weight_file* wf);   /* also frees what md_weight_file_upload allocated */
+/* The records in file order.  name is NUL-terminated and lives as long as the file object; host_data points into
+ * the read-only mapping; shape receives `rank` dims (at most 4). */
+int md_weight_file_count(const md_weight_file* wf, size_t* n_out);
+int md_weight_file_tensor(const md_weight_file* wf, size_t index, const char** name, size_t* rank, size_t shape[4],
+                          const uint16_t** host_data);
+/* Copy every tensor to the context's device, byte for byte, through a double-buffered pinned staging area; one
+ * device allocation per tensor, so the layers of a stacked tensor are contiguous.  Returns when the copies are done. */
+int md_weight_file_upload(md_weight_file* wf, md_ctx* ctx);
+/* Fill the weight tables of the two models from an uploaded file.  The per-layer pointer arrays belong to the
+ * file object; the models keep the device pointers, so close the file after the models are destroyed.
+ * rot_dim = head_dim * partial_rotary_factor, max_seq = seq_len, eps = f16(1e-5) (text_model.zig:28,
+ * vision_model.zig:35).  The projection's input width is checked as vit_head_dim * n_heads, the expression of
+ * weights.zig:470 (2304 = 2 * vit_dim for the shipped configuration). */
+int md_weight_file_text(md_weight_file* wf, md_text_weights* out);
+int md_weight_file_vision(md_weight_file* wf, md_vision_weights* out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -25,7 +25,7 @@ MD_OK = 0
 STATUS_NAMES = {
     0: "MD_OK", 1: "MD_ERR_INVALID_ARG", 2: "MD_ERR_INVALID_DIMENSION", 3: "MD_ERR_SHAPE",
     4: "MD_ERR_SEQUENCE_TOO_LONG", 5: "MD_ERR_INVALID_ROT_DIM", 6: "MD_ERR_UNSUPPORTED", 7: "MD_ERR_OOM",
-    8: "MD_ERR_CUDA", 9: "MD_ERR_TIMEOUT", 10: "MD_ERR_NO_DEVICE",
+    8: "MD_ERR_CUDA", 9: "MD_ERR_TIMEOUT", 10: "MD_ERR_NO_DEVICE", 11: "MD_ERR_IO", 12: "MD_ERR_FORMAT",
 }
 # the Zig error each status maps back to in the shim
 ZIG_ERRORS = {
@@ -39,6 +39,8 @@ class MdError(RuntimeError):
         super().__init__(f"{STATUS_NAMES.get(status, status)}: {message}")
         self.status = status
         self.zig_error = ZIG_ERRORS.get(status)
+        if status in (11, 12) and ":" in message:  # the weight-file reader puts the Zig error name first
+            self.zig_error = "error." + message.split(":", 1)[0]
 
 
 def build(force: bool = False) -> str:

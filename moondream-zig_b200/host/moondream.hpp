@@ -14,6 +14,7 @@
 //   attention::singleMaskedSDPA   attention.zig:759
 //   rope::precomputeFreqsCis      rope.zig:32
 //   rope::applyRotEmb             rope.zig:130
+//   Weights                       weights.zig:61-207 (init from a moondream.bin), 324-369 (deinit)
 //
 // The allocator parameter of the Zig functions has no counterpart: results are returned by value.
 #pragma once
@@ -25,6 +26,7 @@
 #include <vector>
 
 #include "../../include/moondream_b200.h"
+#include "../../include/moondream_b200_model.h"
 
 namespace moondream {
 
@@ -161,5 +163,44 @@ inline Tensor<f16> applyRotEmb(const Tensor<f16>& x, size_t n_heads, size_t head
     return out;
 }
 }  // namespace rope
+
+// Weights.init(config, filename, allocator): parse and validate the file, then make it resident on the
+// backend's device.  The Zig error of a rejected file (InvalidMagicNumber, ShapeMismatch, ...) is the name of
+// the exception.  text() / vision() give the device-pointer tables the model runners take.
+class Weights {
+public:
+    explicit Weights(const std::string& filename, const md_model_config* config = nullptr) {
+        fail_if(md_weight_file_open(filename.c_str(), config, &file_), nullptr);
+        const int st = md_weight_file_upload(file_, Backend::ctx());
+        if (st != MD_OK) {
+            md_weight_file_close(file_);
+            file_ = nullptr;
+            Backend::check(st);
+        }
+    }
+    ~Weights() { md_weight_file_close(file_); }
+    Weights(const Weights&) = delete;
+    Weights& operator=(const Weights&) = delete;
+
+    md_text_weights text() {
+        md_text_weights w;
+        fail_if(md_weight_file_text(file_, &w), Backend::ctx());
+        return w;
+    }
+    md_vision_weights vision() {
+        md_vision_weights w;
+        fail_if(md_weight_file_vision(file_, &w), Backend::ctx());
+        return w;
+    }
+
+private:
+    md_weight_file* file_ = nullptr;
+    static void fail_if(int status, const md_ctx* ctx) {
+        if (status == MD_OK) return;
+        const std::string msg = md_last_error(ctx);
+        if (status == MD_ERR_IO || status == MD_ERR_FORMAT) throw ZigError(msg.substr(0, msg.find(':')), msg);
+        Backend::check(status);
+    }
+};
 
 }  // namespace moondream

@@ -96,11 +96,22 @@ class TextModel:
             b = _dev(ctx, weights[name])
             self.dev[name] = b
             setattr(s, name, b.ptr)
+        self._create(s)
+
+    def _create(self, s: _TextW):
         self.s = s
-        self.dim, self.vocab, self.n_layers = dim, int(s.vocab), L
+        self.dim, self.vocab, self.n_layers = int(s.dim), int(s.vocab), int(s.n_layers)
         h = C.c_void_p()
-        ctx._check(self.lib.md_text_model_create(ctx.h, C.byref(s), C.byref(h)))
+        self.ctx._check(self.lib.md_text_model_create(self.ctx.h, C.byref(s), C.byref(h)))
         self.h = h
+
+    @classmethod
+    def from_table(cls, ctx, table: _TextW, owner=None) -> "TextModel":
+        """A model over weights that are already resident (e.g. a weight file's table); `owner` is kept alive."""
+        self = cls.__new__(cls)
+        self.ctx, self.lib, self.dev, self._keep = ctx, ctx.lib, {}, [owner]
+        self._create(table)
+        return self
 
     def request(self) -> TextRequest:
         return TextRequest(self)
@@ -175,11 +186,21 @@ class VisionModel:
             b = _dev(ctx, weights[name])
             self.dev[name] = b
             setattr(s, name, b.ptr)
+        self._create(s, max_crops)
+
+    def _create(self, s: _VisW, max_crops: int):
         self.s = s
-        self.tokens, self.dim, self.proj_out, self.img = int(s.tokens), int(s.dim), int(s.proj_out), img
+        self.tokens, self.dim, self.proj_out, self.img = int(s.tokens), int(s.dim), int(s.proj_out), int(s.img)
         h = C.c_void_p()
-        ctx._check(self.lib.md_vision_model_create(ctx.h, C.byref(s), _sz(max_crops), C.byref(h)))
+        self.ctx._check(self.lib.md_vision_model_create(self.ctx.h, C.byref(s), _sz(max_crops), C.byref(h)))
         self.h = h
+
+    @classmethod
+    def from_table(cls, ctx, table: _VisW, max_crops: int = 2, owner=None) -> "VisionModel":
+        self = cls.__new__(cls)
+        self.ctx, self.lib, self.dev, self._keep = ctx, ctx.lib, {}, [owner]
+        self._create(table, max_crops)
+        return self
 
     def encode(self, crops_u8: np.ndarray, crop_a: int = 0, crop_b: int | None = None, want_features: bool = False):
         """vision_model.zig:160-202 without the file decode. crops uint8 [c, img, img, 3]."""
