@@ -96,7 +96,10 @@ int md_set_gemm_mode(md_ctx* ctx, int mode);
  *                   on which no earlier kernel writes the weight matrices (registered weights).
  *   "fused_decode"  1 (default) = a decode layer runs as three fused kernels, 0 = one kernel per reference op
  *   "dualk_variant" 0..4 = (warps, unroll) of the out-proj + fc2 kernel of the fused decode layer
- *   "decode_cluster" 0 = merge the decode attention splits through global scratch instead of a CTA cluster
+ *   "decode_cluster" 1 = merge the key splits of the decode attention through the shared memory of a 16-CTA cluster;
+ *                   0 / -1 (default) = through global scratch and an arrival ticket
+ *   "decode_split_ln" n (default 5): a decode step over >= n rows runs each LayerNorm once as its own kernel followed by
+ *                   plain GEMVs with fused epilogues, instead of the kernels that recompute it in every CTA; 0 = never
  *   "attn_tc"       -1 (default) = tcgen05 attention when the operands allow it and q_len > 64,
  *                   0 = mma.sync attention only, 1 = tcgen05 only (MD_ERR_UNSUPPORTED otherwise)
  *   "prefill_fork"  1 (default) = a prefill layer runs fc1 -> fc2 as a second kernel chain beside the attention

@@ -314,6 +314,13 @@ struct DecodeParams {
     int splits;
     const float* rope_tab;  // fused: (cos, sin) table [positions][rot_dim/2][2] (rope.zig:32-128)
     const int* pos_ptr;     // fused + graph replay: position read from device memory, else null
+    // batch > 0: blockIdx.z selects one of up to 8 requests, each with its own cache and position; q and out
+    // advance by a row per request, partial and counters by one request's worth
+    int batch;
+    long long q_batch_stride, out_batch_stride;
+    __half* bk[8];
+    __half* bv[8];
+    const int* bpos[8];
 };
 
 __device__ __forceinline__ uint4 ldg_nc16(const void* p) {
@@ -358,6 +365,16 @@ sdpa_decode_kernel(DecodeParams p) {
     __shared__ int is_last;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int head = blockIdx.y, split = blockIdx.x;
+    if (p.batch > 0) {
+        const int b = blockIdx.z;
+        p.q += b * p.q_batch_stride;
+        p.out += b * p.out_batch_stride;
+        p.k = p.k_w = p.bk[b];
+        p.v = p.v_w = p.bv[b];
+        p.pos_ptr = p.bpos[b];
+        p.counters += b * p.n_heads;
+        p.partial += (long long)b * p.n_heads * p.splits * (DEC_D + 2);
+    }
     if (p.pos_ptr) {
         // Position held in device memory (graph replay): the grid is sized for the longest
         // context, CTAs beyond the splits this position needs leave at once.
@@ -739,23 +756,29 @@ int md_launch_sdpa_decode_fused(md_ctx* ctx, const __half* qkv_row, __half* kc, 
     return decode_launch(ctx, p);
 }
 
-int md_launch_sdpa_decode_fused_devpos(md_ctx* ctx, const __half* qkv_row, __half* kc, __half* vc, __half* out,
-                                       size_t n_heads, size_t d, size_t max_seq, const int* pos_dev, size_t rot_dim,
-                                       float theta) {
+// The decode attention of `batch` requests (1..8) in one launch: request b reads row b of qkv (row stride
+// qkv_stride elements), appends to and reads its own cache kc[b] / vc[b] at the position held in pos_dev[b],
+// and writes row b of out (row stride out_stride).
+int md_launch_sdpa_decode_fused_devpos_batch(md_ctx* ctx, const __half* qkv, size_t qkv_stride, __half* const* kc,
+                                             __half* const* vc, __half* out, size_t out_stride, size_t batch,
+                                             size_t n_heads, size_t d, size_t max_seq, const int* const* pos_dev,
+                                             size_t rot_dim, float theta) {
     if (d != DEC_D || n_heads > 256)
         return md_fail(ctx, MD_ERR_UNSUPPORTED, "decode attention supports head_dim 64 and <= 256 heads");
+    if (batch < 1 || batch > 8) return md_fail(ctx, MD_ERR_INVALID_ARG, "decode attention: batch must be 1..8");
     DecodeParams p{};
-    p.q = qkv_row; p.k = kc; p.v = vc; p.k_w = kc; p.v_w = vc; p.mask = nullptr; p.out = out;
+    p.q = qkv; p.k = kc[0]; p.v = vc[0]; p.k_w = kc[0]; p.v_w = vc[0]; p.mask = nullptr; p.out = out;
     p.k_head_stride = (long long)max_seq * DEC_D;
     p.n_heads = (int)n_heads; p.fused = 1; p.rot_dim = (int)rot_dim; p.theta = theta;
     MD_TRY(md_rope_cached(ctx, rot_dim, theta, max_seq, &p.rope_tab));
-    p.pos_ptr = pos_dev;
+    p.pos_ptr = pos_dev[0];
+    if (batch > 1) {
+        p.batch = (int)batch;
+        p.q_batch_stride = (long long)qkv_stride;
+        p.out_batch_stride = (long long)out_stride;
+        for (size_t b = 0; b < batch; ++b) { p.bk[b] = kc[b]; p.bv[b] = vc[b]; p.bpos[b] = pos_dev[b]; }
+    }
     const int max_splits = (int)((max_seq + DEC_KEYS - 1) / DEC_KEYS);
-    void* scratch = nullptr;
-    MD_TRY(md_scratch(ctx, (size_t)p.n_heads * max_splits * (DEC_D + 2) * sizeof(float), &scratch));
-    p.counters = ctx->counters;
-    p.partial = reinterpret_cast<float*>(scratch);
-    p.splits = max_splits;  // stride of the partial array; the kernel recomputes the live count
     if (ctx->decode_cluster_ok < 0) {
         const cudaError_t ce =
             cudaFuncSetAttribute(sdpa_decode_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
@@ -763,17 +786,27 @@ int md_launch_sdpa_decode_fused_devpos(md_ctx* ctx, const __half* qkv_row, __hal
         ctx->decode_cluster_ok = ce == cudaSuccess ? 1 : 0;
     }
     if (ctx->decode_cluster_mode >= 0) ctx->decode_cluster_ok = ctx->decode_cluster_ok && ctx->decode_cluster_mode;
+    // Two ways to merge the key splits of a head: through global scratch with an arrival ticket (the default), or,
+    // with md_set_option("decode_cluster", 1), through the shared memory of a 16-CTA thread-block cluster (one CTA
+    // per possible split; needs the non-portable cluster size and at most 16 splits).  The cluster form measured
+    // slower inside the two-chain decode layer (864 against 784 us per token at 24 layers): its CTAs past the live
+    // splits hold their slots until the cluster barrier, and 16-CTA clusters start at a limited rate.
+    const bool use_cluster = ctx->decode_cluster_ok && max_splits <= 16 && ctx->decode_cluster_mode == 1;
+    if (!use_cluster && batch * n_heads > MD_COUNTER_WORDS)
+        return md_fail(ctx, MD_ERR_UNSUPPORTED, "decode attention: batch * n_heads exceeds the arrival counters");
+    void* scratch = nullptr;
+    MD_TRY(md_scratch(ctx, batch * p.n_heads * max_splits * (DEC_D + 2) * sizeof(float), &scratch));
+    p.counters = ctx->counters;
+    p.partial = reinterpret_cast<float*>(scratch);
+    p.splits = max_splits;  // stride of the partial array; the kernel recomputes the live count
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)max_splits, (unsigned)p.n_heads);
+    cfg.gridDim = dim3((unsigned)max_splits, (unsigned)p.n_heads, (unsigned)batch);
     cfg.blockDim = dim3(DEC_WARPS * 32);
     cfg.stream = ctx->stream;
-    // A cluster of 16 CTAs (one per possible split) needs the non-portable cluster size; when the
-    // context could not enable it, or the cache is longer than 16 splits, the scratch-based merge runs.
-    const bool use_cluster = ctx->decode_cluster_ok && max_splits <= 16;
     cudaLaunchAttribute attr[2];
     int na = 0;
     if (use_cluster) {
-        cfg.gridDim = dim3(16u, (unsigned)p.n_heads);
+        cfg.gridDim = dim3(16u, (unsigned)p.n_heads, (unsigned)batch);
         attr[na].id = cudaLaunchAttributeClusterDimension;
         attr[na].val.clusterDim.x = 16;
         attr[na].val.clusterDim.y = 1;
@@ -792,6 +825,13 @@ int md_launch_sdpa_decode_fused_devpos(md_ctx* ctx, const __half* qkv_row, __hal
     if (le != cudaSuccess) return md_fail(ctx, MD_ERR_CUDA, "launch of sdpa_decode_kernel failed: %s", cudaGetErrorString(le));
     MD_LAUNCH_CHECK(ctx, "sdpa_decode_kernel");
     return MD_OK;
+}
+
+int md_launch_sdpa_decode_fused_devpos(md_ctx* ctx, const __half* qkv_row, __half* kc, __half* vc, __half* out,
+                                       size_t n_heads, size_t d, size_t max_seq, const int* pos_dev, size_t rot_dim,
+                                       float theta) {
+    return md_launch_sdpa_decode_fused_devpos_batch(ctx, qkv_row, 0, &kc, &vc, out, 0, 1, n_heads, d, max_seq, &pos_dev,
+                                                    rot_dim, theta);
 }
 
 int md_launch_rope_cache_write(md_ctx* ctx, const __half* qkv, __half* q_rot, __half* kc, __half* vc, size_t S,

@@ -211,8 +211,8 @@ int md_init(md_ctx** out, int device) {
     if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->mirror_host), sizeof(unsigned int), cudaHostAllocMapped) != cudaSuccess)
         return bail("cudaHostAlloc mirror");
     if (reset_flags(ctx) != MD_OK) return bail("flag initialisation");
-    if (cudaMalloc(&ctx->counters, 1024) != cudaSuccess) return bail("cudaMalloc counters");
-    if (cudaMemset(ctx->counters, 0, 1024) != cudaSuccess) return bail("cudaMemset counters");
+    if (cudaMalloc(&ctx->counters, MD_COUNTER_WORDS * 4) != cudaSuccess) return bail("cudaMalloc counters");
+    if (cudaMemset(ctx->counters, 0, MD_COUNTER_WORDS * 4) != cudaSuccess) return bail("cudaMemset counters");
     ctx->scratch_cap = (size_t)16 << 20;
     if (cudaMalloc(&ctx->scratch, ctx->scratch_cap) != cudaSuccess) return bail("cudaMalloc scratch");
     *out = ctx;
@@ -308,11 +308,12 @@ int md_set_option(md_ctx* ctx, const char* key, long value) {
     MD_NEED(ctx, key, "md_set_option: null key");
     if (!strcmp(key, "gemv_variant")) { ctx->gemv_variant = (int)value; return MD_OK; }
     if (!strcmp(key, "decode_cluster")) {
-        ctx->decode_cluster_mode = value ? 1 : 0;
+        ctx->decode_cluster_mode = value < 0 ? -1 : (value ? 1 : 0);
         ctx->decode_cluster_ok = -1;
         return MD_OK;
     }
     if (!strcmp(key, "dualk_variant")) { ctx->dualk_variant = (int)value; return MD_OK; }
+    if (!strcmp(key, "decode_split_ln")) { ctx->decode_split_ln = (int)value; return MD_OK; }
     if (!strcmp(key, "fused_decode")) { ctx->fused_decode = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "pdl")) { ctx->pdl = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "prefill_fork")) { ctx->prefill_fork = value ? 1 : 0; return MD_OK; }

@@ -40,6 +40,8 @@ struct md_graph {
     cudaGraphExec_t exec = nullptr;
 };
 
+constexpr size_t MD_COUNTER_WORDS = 256;
+
 struct md_ctx {
     int device = 0;
     int sm_count = 0;
@@ -57,7 +59,7 @@ struct md_ctx {
     // scratch for kernels that need global memory beyond inputs and outputs
     void* scratch = nullptr;
     size_t scratch_cap = 0;
-    // per-head arrival counters of the split-KV decode attention: zero between launches
+    // per-head arrival counters of the split-KV decode attention (MD_COUNTER_WORDS words): zero between launches
     unsigned int* counters = nullptr;
     // cuTensorMapEncodeTiled resolved through the runtime (no link against libcuda)
     void* encode_tiled = nullptr;
@@ -75,6 +77,7 @@ struct md_ctx {
     int fused_decode = 1;    // md_set_option("fused_decode"): decode layers as 3 fused kernels
     int pdl = 0;             // md_set_option("pdl"): programmatic dependent launch for the GEMV kernels
     int prefill_fork = 1;       // md_set_option("prefill_fork"): prefill layers run the MLP beside the attention
+    int decode_split_ln = 5;    // md_set_option("decode_split_ln"): from this many rows on a decode step runs the LayerNorm once
     int decode_fork = 1;        // md_set_option("decode_fork"): a decode layer runs as two concurrent kernel chains
     cudaStream_t side_stream = nullptr;  // second chain of the forked decode layer
     cudaEvent_t ev_fork = nullptr, ev_side = nullptr;

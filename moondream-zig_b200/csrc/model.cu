@@ -13,9 +13,10 @@
 
 extern "C" int md_gemm_dispatch(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
                                 int b_layout, const md_epilogue& ep);
-int md_launch_sdpa_decode_fused_devpos(md_ctx* ctx, const __half* qkv_row, __half* kc, __half* vc, __half* out,
-                                       size_t n_heads, size_t d, size_t max_seq, const int* pos_dev, size_t rot_dim,
-                                       float theta);
+int md_launch_sdpa_decode_fused_devpos_batch(md_ctx* ctx, const __half* qkv, size_t qkv_stride, __half* const* kc,
+                                             __half* const* vc, __half* out, size_t out_stride, size_t batch,
+                                             size_t n_heads, size_t d, size_t max_seq, const int* const* pos_dev,
+                                             size_t rot_dim, float theta);
 
 namespace {
 
@@ -180,12 +181,30 @@ struct LayerIO {
     __half *hidden, *ln, *qkv, *attn, *attn_out, *fc1;
 };
 
+// Attention of one decode step: every request's new token against its own cache, one launch for the batch.
+int decode_attention(md_text_model* m, size_t layer, const LayerIO& io, size_t rows, md_text_request* const* reqs) {
+    const md_text_weights& w = m->w;
+    __half *kc[8], *vc[8];
+    const int* pos[8];
+    for (size_t b = 0; b < rows; ++b) {
+        kc[b] = reqs[b]->kc[layer];
+        vc[b] = reqs[b]->vc[layer];
+        pos[b] = reqs[b]->pos_dev;
+    }
+    return md_launch_sdpa_decode_fused_devpos_batch(m->ctx, io.qkv, 3 * w.dim, kc, vc, io.attn, w.dim, rows, w.n_heads,
+                                                    w.head_dim, w.max_seq, pos, w.rot_dim, w.rope_theta);
+}
+
 int text_layer(md_text_model* m, size_t layer, const LayerIO& io, size_t rows, bool decode,
                md_text_request* const* reqs, size_t prefill_pos) {
     md_ctx* ctx = m->ctx;
     const md_text_weights& w = m->w;
     const size_t D = w.dim, F = w.hidden;
-    if (decode && ctx->fused_decode && md_gemv_ln_dual_supported(rows, D, 3 * D, F) &&
+    // The fused kernels recompute the LayerNorm of all rows in every CTA; with many rows that costs registers
+    // (one CTA per SM instead of two) and L2 reads, so from ctx->decode_split_ln rows on the LayerNorm runs once
+    // as its own kernel and plain GEMVs with fused epilogues follow (the generic path below, forked the same way).
+    const bool ln_once = ctx->decode_split_ln > 0 && rows >= (size_t)ctx->decode_split_ln;
+    if (decode && ctx->fused_decode && !ln_once && md_gemv_ln_dual_supported(rows, D, 3 * D, F) &&
         md_gemv_dual_k_supported(rows, D, D, F)) {
         if (ctx->decode_fork) {
             // Two concurrent chains per layer, so that the weight stream of the MLP fills the time the attention
@@ -220,12 +239,7 @@ int text_layer(md_text_model* m, size_t layer, const LayerIO& io, size_t rows, b
             MD_TRY(md_launch_gemv_ln_dual(ctx, io.hidden, H(m->ln_w[layer]), H(m->ln_b[layer]), eps_of(w.eps_f16),
                                           H(m->wqkv[layer]), H(m->bqkv[layer]), io.qkv, 3 * D, nullptr, nullptr, nullptr, 0,
                                           rows, D));
-            for (size_t b = 0; b < rows; ++b) {
-                md_text_request* r = reqs[b];
-                MD_TRY(md_launch_sdpa_decode_fused_devpos(ctx, io.qkv + b * 3 * D, r->kc[layer], r->vc[layer],
-                                                          io.attn + b * D, w.n_heads, w.head_dim, w.max_seq, r->pos_dev,
-                                                          w.rot_dim, w.rope_theta));
-            }
+            MD_TRY(decode_attention(m, layer, io, rows, reqs));
             MD_CUDA(ctx, cudaStreamWaitEvent(main_stream, ctx->ev_side, 0));
             md_epilogue e_out;
             e_out.bias = H(m->bout[layer]);
@@ -237,12 +251,7 @@ int text_layer(md_text_model* m, size_t layer, const LayerIO& io, size_t rows, b
         MD_TRY(md_launch_gemv_ln_dual(ctx, io.hidden, H(m->ln_w[layer]), H(m->ln_b[layer]), eps_of(w.eps_f16),
                                       H(m->wqkv[layer]), H(m->bqkv[layer]), io.qkv, 3 * D, H(m->wfc1[layer]),
                                       H(m->bfc1[layer]), io.fc1, F, rows, D));
-        for (size_t b = 0; b < rows; ++b) {
-            md_text_request* r = reqs[b];
-            MD_TRY(md_launch_sdpa_decode_fused_devpos(ctx, io.qkv + b * 3 * D, r->kc[layer], r->vc[layer], io.attn + b * D,
-                                                      w.n_heads, w.head_dim, w.max_seq, r->pos_dev, w.rot_dim,
-                                                      w.rope_theta));
-        }
+        MD_TRY(decode_attention(m, layer, io, rows, reqs));
         return md_launch_gemv_dual_k(ctx, io.attn, H(m->wout[layer]), H(m->bout[layer]), D, io.fc1, H(m->wfc2[layer]),
                                      H(m->bfc2[layer]), F, io.hidden, D, rows);
     }
@@ -251,7 +260,7 @@ int text_layer(md_text_model* m, size_t layer, const LayerIO& io, size_t rows, b
     // second kernel chain beside qkv -> rope -> attention; the GEMMs of one chain that cover only part of the SMs
     // (96 tiles for the 2048-wide outputs at 761 rows) leave the rest to the other chain.  The chains meet in the
     // out-projection's epilogue (same roundings as the sequential form, text_model.zig:162-171).
-    const bool fork_prefill = !decode && ctx->prefill_fork && rows > 8;
+    const bool fork_prefill = ctx->prefill_fork && (decode ? ctx->decode_fork != 0 : rows > 8);
     if (fork_prefill) {
         if (!ctx->side_stream) {
             MD_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking));
@@ -277,12 +286,7 @@ int text_layer(md_text_model* m, size_t layer, const LayerIO& io, size_t rows, b
     e_qkv.bias = H(m->bqkv[layer]);
     MD_TRY(md_gemm_dispatch(ctx, io.ln, H(m->wqkv[layer]), io.qkv, rows, 3 * D, D, 1, e_qkv));
     if (decode) {
-        for (size_t b = 0; b < rows; ++b) {
-            md_text_request* r = reqs[b];
-            MD_TRY(md_launch_sdpa_decode_fused_devpos(ctx, io.qkv + b * 3 * D, r->kc[layer], r->vc[layer], io.attn + b * D,
-                                                      w.n_heads, w.head_dim, w.max_seq, r->pos_dev, w.rot_dim,
-                                                      w.rope_theta));
-        }
+        MD_TRY(decode_attention(m, layer, io, rows, reqs));
     } else {
         md_text_request* r = reqs[0];
         void* q_rot = nullptr;
@@ -540,7 +544,8 @@ static int enqueue_decode_step(md_text_model* model, md_text_request* const* req
     } else {
         for (size_t l = 0; l < w.n_layers; ++l) MD_TRY(text_layer(model, l, io, batch, true, reqs, 0));
     }
-    const bool fused_head = persistent || (ctx->fused_decode && md_gemv_ln_dual_supported(batch, w.dim, w.vocab, 0));
+    const bool ln_once = ctx->decode_split_ln > 0 && batch >= (size_t)ctx->decode_split_ln;
+    const bool fused_head = persistent || (ctx->fused_decode && !ln_once && md_gemv_ln_dual_supported(batch, w.dim, w.vocab, 0));
     if (persistent) {
     } else if (fused_head) {
         // final LayerNorm + lm_head + greedy argmax in one kernel (text_model.zig:325-345, sampling.zig:257-273)

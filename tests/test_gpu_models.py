@@ -196,7 +196,10 @@ def test_text_persistent_decode_step_matches_the_three_kernel_layers(ctx, models
     gpu.close()
 
 
-def test_text_batched_decode_equals_single_requests(ctx, models_mod):
+@pytest.mark.parametrize("cluster_merge", [1, 0], ids=["cluster_merge", "scratch_merge"])
+def test_text_batched_decode_equals_single_requests(ctx, models_mod, cluster_merge):
+    """One attention launch serves the whole batch (grid z = request), each request at its own position; both ways
+    of merging the key splits (thread-block cluster, or global scratch + arrival counters) are exercised."""
     w = text_weights(4004, n_layers=2, hidden=512, vocab=2048)
     gpu = models_mod.TextModel(ctx, w)
     rng = np.random.default_rng(4)
@@ -211,7 +214,45 @@ def test_text_batched_decode_equals_single_requests(ctx, models_mod):
     reqs = [gpu.request() for _ in prompts]
     for r, p in zip(reqs, prompts):
         gpu.forward(r, p)
-    batch = gpu.generate_batch(reqs, firsts, 10)
+    ctx.set_option("decode_cluster", cluster_merge)
+    try:
+        batch = gpu.generate_batch(reqs, firsts, 10)
+        r = gpu.request()  # and one single request under the same merge
+        _, _, tok = gpu.forward(r, prompts[1])
+        again = gpu.generate(r, tok, 10)
+        r.close()
+    finally:
+        ctx.set_option("decode_cluster", -1)
+    np.testing.assert_array_equal(batch, np.stack(singles))
+    np.testing.assert_array_equal(again, singles[1])
+    for r in reqs:
+        r.close()
+    gpu.close()
+
+
+@pytest.mark.parametrize("split_ln", [0, 2])
+def test_text_batched_decode_with_one_layernorm_kernel_equals_the_fused_kernels(ctx, models_mod, split_ln):
+    """From decode_split_ln rows on the LayerNorm runs once as a kernel and plain GEMVs follow; below it every CTA of
+    the fused kernels recomputes it.  Both forms must produce the tokens of the single-request runs."""
+    w = text_weights(4014, n_layers=2, hidden=512, vocab=2048)
+    gpu = models_mod.TextModel(ctx, w)
+    rng = np.random.default_rng(14)
+    prompts = [w["wte"][rng.integers(0, 2048, n)] for n in (3, 129, 40, 7, 64, 200, 1, 90)]
+    singles, firsts = [], []
+    for p in prompts:
+        r = gpu.request()
+        _, _, tok = gpu.forward(r, p)
+        firsts.append(tok)
+        singles.append(gpu.generate(r, tok, 8))
+        r.close()
+    reqs = [gpu.request() for _ in prompts]
+    for r, p in zip(reqs, prompts):
+        gpu.forward(r, p)
+    ctx.set_option("decode_split_ln", split_ln)
+    try:
+        batch = gpu.generate_batch(reqs, firsts, 8)
+    finally:
+        ctx.set_option("decode_split_ln", 5)
     np.testing.assert_array_equal(batch, np.stack(singles))
     for r in reqs:
         r.close()
