@@ -344,11 +344,11 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// rope.zig:50-65,223-230 for one head vector held in shared memory (f32 in, f16-rounded out).
-__device__ __forceinline__ float rope_elem(const float* x, int dd, int pos, int rot_dim, const float* tab) {
+// rope.zig:50-65,223-230 for one head vector held in shared memory (f32 in, f16-rounded by the caller), with the
+// (cos, sin) pair of dim dd already in registers.
+__device__ __forceinline__ float rope_rotate(const float* x, int dd, int rot_dim, float2 cs) {
     if (dd >= rot_dim) return x[dd];
     const int half = rot_dim / 2, j = dd < half ? dd : dd - half;
-    const float2 cs = *reinterpret_cast<const float2*>(tab + ((size_t)pos * half + j) * 2);  // (cos, sin)
     const float xr = x[j], xi = x[j + half];
     return dd < half ? xr * cs.x - xi * cs.y : xr * cs.y + xi * cs.x;
 }
@@ -358,9 +358,11 @@ __device__ __forceinline__ float rope_elem(const float* x, int dd, int pos, int 
 // and an atomic ticket.
 template <bool CLUSTER>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
-sdpa_decode_kernel(DecodeParams p) {
+sdpa_decode_kernel(const __grid_constant__ DecodeParams gp) {
+    // the per-request tables are indexed in the constant bank; the working copy below is only accessed by field
+    DecodeParams p = gp;
     __shared__ float cpart[CLUSTER ? 16 : 1][DEC_D + 2];
-    __shared__ float q_s[DEC_D], knew_s[DEC_D], vnew_s[DEC_D], raw_s[DEC_D];
+    __shared__ float q_s[DEC_D], knew_s[DEC_D], vnew_s[DEC_D], raw_s[DEC_D], rawk_s[DEC_D];
     __shared__ float red_m[DEC_WARPS], red_l[DEC_WARPS], red_o[DEC_WARPS][DEC_D];
     __shared__ int is_last;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -369,9 +371,9 @@ sdpa_decode_kernel(DecodeParams p) {
         const int b = blockIdx.z;
         p.q += b * p.q_batch_stride;
         p.out += b * p.out_batch_stride;
-        p.k = p.k_w = p.bk[b];
-        p.v = p.v_w = p.bv[b];
-        p.pos_ptr = p.bpos[b];
+        p.k = p.k_w = gp.bk[b];
+        p.v = p.v_w = gp.bv[b];
+        p.pos_ptr = gp.bpos[b];
         p.counters += b * p.n_heads;
         p.partial += (long long)b * p.n_heads * p.splits * (DEC_D + 2);
     }
@@ -411,21 +413,32 @@ sdpa_decode_kernel(DecodeParams p) {
         const int key = key_lo + it * 4 + grp;
         vreg[it] = valid[it] ? ldg_nc16(vh + (long long)key * DEC_D + sub * 8) : make_uint4(0, 0, 0, 0);
     }
+    // the rope factors of this thread's dim depend on the position alone: requested before the wait as well
+    float2 cs = make_float2(1.f, 0.f);
+    if (p.fused && tid < p.rot_dim) {
+        const int half = p.rot_dim >> 1, j = tid < half ? tid : tid - half;
+        cs = __ldg(reinterpret_cast<const float2*>(p.rope_tab + ((size_t)p.pos * half + j) * 2));  // (cos, sin)
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    // ---- stage q (and, fused, the new k and v) in shared memory
+    // ---- stage q (and, fused, the new k and v) in shared memory: one round of loads, then the rotation
     if (p.fused) {
         const int hd = p.n_heads * DEC_D;
-        if (tid < DEC_D) raw_s[tid] = __half2float(__ldcg(p.q + head * DEC_D + tid));
+        __half vn = __float2half_rn(0.f);
+        if (tid < DEC_D) {
+            const __half rq = __ldcg(p.q + head * DEC_D + tid);
+            if (last_split) {
+                const __half rk = __ldcg(p.q + hd + head * DEC_D + tid);
+                vn = __ldcg(p.q + 2 * hd + head * DEC_D + tid);
+                rawk_s[tid] = __half2float(rk);
+            }
+            raw_s[tid] = __half2float(rq);
+        }
         __syncthreads();
-        if (tid < DEC_D) q_s[tid] = md_round_f16(rope_elem(raw_s, tid, p.pos, p.rot_dim, p.rope_tab));
-        __syncthreads();
-        if (last_split) {
-            if (tid < DEC_D) raw_s[tid] = __half2float(__ldcg(p.q + hd + head * DEC_D + tid));
-            __syncthreads();
-            if (tid < DEC_D) {
-                const __half kr = __float2half_rn(rope_elem(raw_s, tid, p.pos, p.rot_dim, p.rope_tab));
-                const __half vn = __ldcg(p.q + 2 * hd + head * DEC_D + tid);
+        if (tid < DEC_D) {
+            q_s[tid] = md_round_f16(rope_rotate(raw_s, tid, p.rot_dim, cs));
+            if (last_split) {
+                const __half kr = __float2half_rn(rope_rotate(rawk_s, tid, p.rot_dim, cs));
                 knew_s[tid] = __half2float(kr);
                 vnew_s[tid] = __half2float(vn);
                 p.k_w[head * p.k_head_stride + (long long)p.pos * DEC_D + tid] = kr;
@@ -563,7 +576,30 @@ sdpa_decode_kernel(DecodeParams p) {
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    if (tid < DEC_D) {
+    if (tid < DEC_D && p.splits <= 16) {
+        // every partial in one round of loads
+        const float* base = p.partial + (long long)head * p.splits * (DEC_D + 2);
+        float ms[16], ls[16], os[16];
+#pragma unroll
+        for (int s2 = 0; s2 < 16; ++s2) {
+            const bool live = s2 < p.splits;
+            ms[s2] = live ? __ldcg(base + s2 * (DEC_D + 2)) : -INFINITY;
+            ls[s2] = live ? __ldcg(base + s2 * (DEC_D + 2) + 1) : 0.f;
+            os[s2] = live ? __ldcg(base + s2 * (DEC_D + 2) + 2 + tid) : 0.f;
+        }
+        float Mg = -INFINITY;
+#pragma unroll
+        for (int s2 = 0; s2 < 16; ++s2) Mg = fmaxf(Mg, ms[s2]);
+        const float Mu = (Mg == -INFINITY) ? 0.f : Mg;
+        float Lg = 0.f, Og = 0.f;
+#pragma unroll
+        for (int s2 = 0; s2 < 16; ++s2) {
+            const float f = (ms[s2] == -INFINITY) ? 0.f : expf(ms[s2] - Mu);
+            Lg += ls[s2] * f;
+            Og += os[s2] * f;
+        }
+        p.out[head * DEC_D + tid] = __float2half_rn(Lg > 0.f ? Og / Lg : 0.f);
+    } else if (tid < DEC_D) {
         const float* base = p.partial + (long long)head * p.splits * (DEC_D + 2);
         float Mg = -INFINITY;
         for (int s2 = 0; s2 < p.splits; ++s2) Mg = fmaxf(Mg, __ldcg(base + s2 * (DEC_D + 2)));
