@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the decode GEMV hot path (BASELINE config 2) on N B200 GPUs of one node.
+"""Benchmark of the decode GEMV hot path (benchmark config 2: the decode GEMV sweep) on N B200 GPUs of one node.
 
 Workload ("step"): one pass over the decode GEMV sweep — M in {1,2,4,8} activation rows
 times the five Phi-1.5 layer shapes (K->N: 2048->6144, 2048->2048, 2048->8192, 8192->2048,
@@ -384,7 +384,7 @@ TRAFFIC_BYTES_PER_LAUNCH = int(round(1.0124 * STEP_BYTES / 20))
 
 
 def colsplit_extras(ctx, torch, dist, stream, world, rank):
-    """BASELINE config 5b: 8192^3 f16 GEMM with N split over the ranks; all-gather baseline (NCCL) against the
+    """Benchmark config 5b: 8192^3 f16 GEMM with N split over the ranks; all-gather baseline (NCCL) against the
     fused push epilogue.  Device time per call, max over ranks."""
     import importlib
     import __graft_entry__ as entry

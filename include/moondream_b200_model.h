@@ -77,7 +77,8 @@ int md_text_generate(md_text_model* model, md_text_request* req, uint32_t first,
                      uint32_t* tokens_out, const uint32_t* forced, uint16_t* logits_out);
 
 /* The same loop for up to 8 independent requests advanced together: every GEMV runs with M = batch rows
- * (BASELINE config 5a batches concurrent decode streams as M <= 8 GEMVs); attention runs per request.
+ * (concurrent decode streams batched as M <= 8 GEMVs); the attention of all requests runs in one launch, each request
+ * against its own cache.
  * All requests must hold caches of the same model; their lengths may differ.
  *   first [batch], tokens_out [batch, n_steps] (host). */
 int md_text_generate_batch(md_text_model* model, md_text_request* const* reqs, size_t batch, const uint32_t* first,

@@ -1,7 +1,7 @@
 """GPU parity of the matmul entry points against the oracle, through the C ABI.
 
 Covers the reference's own hgemm test cases (src/core/matmul_test.zig:154-367, same fill
-patterns and comparison rule), the BASELINE shapes (config 1, the decode GEMV sweep, vision
+patterns and comparison rule), the benchmark shapes (config 1, the decode GEMV sweep, vision
 and prefill GEMMs) with the north-star tolerance max|gpu - ref| <= 1e-2 * max|ref|, edge
 shapes around the tile sizes, and size-independent properties at full size."""
 import numpy as np
@@ -103,7 +103,7 @@ def test_empty_dims(ctx):
 
 
 def test_config1_prefill_fc1(ctx, oracle):
-    """BASELINE config 1: A[64,2048] ~N(0,1), W[2048,8192] ~N(0,0.02), both layouts."""
+    """benchmark config 1: A[64,2048] ~N(0,1), W[2048,8192] ~N(0,0.02), both layouts."""
     rng = np.random.default_rng(1000)
     a, w = f16_normal(rng, (64, 2048)), f16_normal(rng, (2048, 8192), 0.02)
     ref = oracle.hgemm_nn(a, w)
@@ -118,7 +118,7 @@ GEMV_SHAPES = [(2048, 6144), (2048, 2048), (2048, 8192), (8192, 2048), (2048, 51
 @pytest.mark.parametrize("k,n", GEMV_SHAPES)
 @pytest.mark.parametrize("m", [1, 2, 4, 8])
 def test_config2_decode_gemv(ctx, oracle, m, k, n):
-    """BASELINE config 2: M in {1,2,4,8} over the Phi-1.5 layer shapes, weights resident."""
+    """benchmark config 2: M in {1,2,4,8} over the Phi-1.5 layer shapes, weights resident."""
     rng = np.random.default_rng(2000 + m)
     w = f16_normal(rng, (n, k), 0.02)
     a = f16_normal(rng, (m, k))

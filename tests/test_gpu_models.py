@@ -273,7 +273,7 @@ def test_text_cache_overflow_is_an_error(ctx, pkg, models_mod):
 
 
 def test_text_full_config4(ctx, oracle, models_mod):
-    """BASELINE config 4: 24 layers, prefill of 761 rows (729 image rows + 32 tokens), 200 greedy steps."""
+    """benchmark config 4: 24 layers, prefill of 761 rows (729 image rows + 32 tokens), 200 greedy steps."""
     w = text_weights(4000)
     stats = run_text_parity(ctx, oracle, models_mod, w, prompt_rows=761, n_steps=200, seed=4)
     print("config 4 parity:", stats)
@@ -318,5 +318,5 @@ def test_vision_small_crops(ctx, oracle, models_mod, crops):
 
 
 def test_vision_full_config3_one_crop(ctx, oracle, models_mod):
-    """BASELINE config 3 at full depth (27 layers), one crop."""
+    """benchmark config 3 at full depth (27 layers), one crop."""
     run_vision(ctx, oracle, models_mod, vision_weights(3000), 1, seed=11)
