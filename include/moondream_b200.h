@@ -109,6 +109,11 @@ int md_set_gemm_mode(md_ctx* ctx, int mode);
  *                   slower than the three-kernel layers on B200, kept as an alternative)
  *   "persist_trace" 1 = md_text_generate prints the phase timings of the persistent step to stderr */
 int md_set_option(md_ctx* ctx, const char* key, long value);
+/* Read back a knob or a diagnostic (no counterpart in the reference): "gemv_variant", "tc_block_n", "pdl", and
+ *   "last_tc_tile"  the tile the last tcgen05 GEMM launch of this context used: 64 / 128 / 256 = width of a
+ *                   128-row tile, 512 = the 256 x 256 tile, 0 = none yet.  Lets a test see which tile the
+ *                   cost model picked for a shape (e.g. for the column-split GEMM with peers). */
+int md_get_option(md_ctx* ctx, const char* key, long* value_out);
 
 /* ---- CUDA graphs -------------------------------------------------------------------
  * A decode step is ~170 small kernels; replaying them as one graph removes the launch
@@ -197,8 +202,12 @@ int md_sdpa_single(md_ctx* ctx, const uint16_t* q, const uint16_t* k, const uint
  *   - kv_len > 2048 (the scratch's maximum) -> MD_ERR_SEQUENCE_TOO_LONG; a message is written to
  *     err[0..err_cap) when err is not NULL;
  *   - enqueues on cuda_stream (NULL = the default stream) and returns without waiting;
+ *   - the tensors must live on the device that is current when the call is made (a tensor on another
+ *     GPU -> MD_ERR_INVALID_ARG; managed memory is accepted);
  *   - the first call on a device looks up the scratch's device address; make that call with the
- *     device current and before any stream capture begins;
+ *     device current, before any stream capture begins, and at start-up before the host reserves the
+ *     rest of HBM (with lazy module loading the first use of the library on a device is what places
+ *     its code and the scratch array in device memory);
  *   - every call on a device shares the one scratch array: calls that overlap on the GPU race,
  *     so keep them on one stream or order them with events. */
 int md_sdpa_single_noalloc(const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint8_t* mask,

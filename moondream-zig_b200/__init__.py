@@ -144,6 +144,11 @@ class Context:
     def set_option(self, key: str, value: int):
         self._check(self.lib.md_set_option(self.h, C.c_char_p(key.encode()), C.c_long(int(value))))
 
+    def get_option(self, key: str) -> int:
+        v = C.c_long()
+        self._check(self.lib.md_get_option(self.h, C.c_char_p(key.encode()), C.byref(v)))
+        return int(v.value)
+
     def graph_begin(self):
         self._check(self.lib.md_graph_begin(self.h))
 

@@ -740,11 +740,11 @@ int md_launch_sdpa(md_ctx* ctx, const __half* q, const __half* k, const __half* 
         dim3 grid((unsigned)((q_len + BQ - 1) / BQ), (unsigned)n_heads, (unsigned)batch);
         // Q + 2 x (K, V) tiles of 64 rows; above the 48 KB default for d = 72, so opt in once
         const int smem64 = (BQ + 4 * BKV) * (64 + 8) * 2, smem72 = (BQ + 4 * BKV) * (80 + 8) * 2;
-        static bool attr_set = false;
-        if (!attr_set) {
+        // the attribute belongs to the device the context lives on: remembered per context, not per process
+        if (!ctx->sdpa_mma_configured) {
             MD_CUDA(ctx, cudaFuncSetAttribute(sdpa_mma_kernel<64, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem64));
             MD_CUDA(ctx, cudaFuncSetAttribute(sdpa_mma_kernel<72, 80>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem72));
-            attr_set = true;
+            ctx->sdpa_mma_configured = true;
         }
         if (d == 64) return md_launch_ex(ctx, sdpa_mma_kernel<64, 64>, grid, dim3(128), smem64, "sdpa_mma_kernel", p);
         return md_launch_ex(ctx, sdpa_mma_kernel<72, 80>, grid, dim3(128), smem72, "sdpa_mma_kernel", p);
@@ -905,8 +905,12 @@ int md_launch_rope_cache_write(md_ctx* ctx, const __half* qkv, __half* q_rot, __
 //   * fixed geometry of the reference's decode attention: 32 heads x 64 dims, kv_len <= 2048,
 //     hence at most 16 splits; the array is 256 B of counters + 32*16*66 floats = 135,424 bytes.
 //   * device pointers only (a host pointer cannot be staged without allocating).
+//   * the tensors must live on the current device (checked; a mismatch is MD_ERR_INVALID_ARG).
 //   * the first call on a device resolves the array's device address (cudaGetSymbolAddress with that
-//     device current).  That first call is set-up work: make it before any stream capture begins.
+//     device current).  That first call is set-up work: make it before any stream capture begins, and
+//     make it at start-up, before the host reserves the rest of HBM: when the CUDA runtime loads modules
+//     lazily, the first use of this library's kernels on a device is what places its code and this array
+//     in device memory.
 //   * all calls on a device share the one array, which keeps the previous call's contents.  The
 //     counters are cleared on the stream before every launch; the partials need no clearing (every
 //     slot that is read was written by the same launch).  Two calls that overlap on the GPU (different
@@ -948,6 +952,11 @@ extern "C" int md_sdpa_single_noalloc(const uint16_t* q, const uint16_t* k, cons
         return noalloc_fail(MD_ERR_SEQUENCE_TOO_LONG, err, err_cap,
                             "md_sdpa_single_noalloc: kv_len %zu exceeds the built-in scratch (max %zu keys)", kv_len,
                             NOALLOC_MAX_KV);
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES)
+        return noalloc_fail(MD_ERR_CUDA, err, err_cap, "md_sdpa_single_noalloc: cudaGetDevice: %s",
+                            e != cudaSuccess ? cudaGetErrorString(e) : "device index out of range");
     const void* ptrs[5] = {q, k, v, mask, out};
     for (const void* p : ptrs) {
         cudaPointerAttributes attr;
@@ -958,12 +967,14 @@ extern "C" int md_sdpa_single_noalloc(const uint16_t* q, const uint16_t* k, cons
                                 "md_sdpa_single_noalloc: every tensor must be device memory (host buffers would "
                                 "need a staging allocation)");
         }
+        // The kernel runs on the current device with that device's copy of the scratch array; a tensor that lives
+        // on another GPU would be dereferenced there without a peer mapping.  Managed memory migrates, so it passes.
+        if (attr.type == cudaMemoryTypeDevice && attr.device != dev)
+            return noalloc_fail(MD_ERR_INVALID_ARG, err, err_cap,
+                                "md_sdpa_single_noalloc: a tensor lives on device %d but device %d is current; make the "
+                                "tensors' device current before the call",
+                                attr.device, dev);
     }
-    int dev = -1;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES)
-        return noalloc_fail(MD_ERR_CUDA, err, err_cap, "md_sdpa_single_noalloc: cudaGetDevice: %s",
-                            e != cudaSuccess ? cudaGetErrorString(e) : "device index out of range");
     if (!g_noalloc_addr[dev]) {
         void* addr = nullptr;
         e = cudaGetSymbolAddress(&addr, md_noalloc_scratch);  // the current device's instance of the array

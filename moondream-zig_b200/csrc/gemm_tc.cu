@@ -15,6 +15,13 @@
 //               64 KB per 1024 tensor cycles instead of 48 KB per 512.
 //   warps 2..9  epilogue: tcgen05.ld (32 lanes x 32 columns) -> fused glue -> f16 ->
 //               swizzled smem -> TMA store (clips the M and N tails).
+//   warps 10..13 (column-split GEMM only) push: once a tile's TMA stores have completed they read the tile
+//               back from this GPU's C (L2 hits) and store it into the other GPUs' copies of C with plain
+//               16-byte peer stores.  The epilogue warps never wait for NVLink: they hand the accumulator
+//               back to the MMA issuer as before, and the push of tile i runs beside the main loop of the
+//               following tiles.
+// Tiles are walked in groups of 8 tile rows (all tile columns of a group before the next group), so that the
+// CTAs of one wave share a few A row blocks and a band of B in L2 instead of streaming all of A per wave.
 // Tails: TMA zero-fills out-of-bounds loads and clips out-of-bounds stores, so any M, N, K
 // with 16-byte-aligned row strides is accepted.
 //
@@ -31,6 +38,9 @@ constexpr int A_STAGE_BYTES = BLOCK_M * BLOCK_K * 2;     // 16 KiB
 constexpr int EPI_WARPS = 8, EPI_BUF_BYTES = 32 * 128;   // 32 rows x 64 f16 per epilogue warp
 constexpr int EPI_BYTES = EPI_WARPS * EPI_BUF_BYTES;     // 32 KiB
 constexpr int NUM_THREADS = (2 + EPI_WARPS) * 32;
+constexpr int PUSH_WARPS = 4;                            // extra warps of the column-split form
+constexpr int NUM_THREADS_PUSH = NUM_THREADS + PUSH_WARPS * 32;
+constexpr int RASTER_GROUP_M = 8;                        // tile rows per rasterisation group
 constexpr int SMEM_LIMIT = 232448;                       // 227 KiB opt-in maximum
 constexpr int BAR_BYTES = 1024;
 
@@ -47,8 +57,37 @@ __host__ __device__ constexpr int smem_bytes(int block_n, int mt) {
 
 using namespace tc;
 
+// Linear tile index -> (tile row, tile column): groups of RASTER_GROUP_M tile rows, row index fastest inside a group.
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+    const int per_group = RASTER_GROUP_M * tiles_n;
+    const int g = tile / per_group, r = tile - g * per_group;
+    const int m_first = g * RASTER_GROUP_M;
+    const int rows = min(RASTER_GROUP_M, tiles_m - m_first);
+    tm = m_first + r % rows;
+    tn = r / rows;
+}
+
+// Bounded wait of the push warps for the epilogue's count of finished tiles (a shared-memory word).
+static __device__ __noinline__ bool wait_stored(volatile unsigned* stored, unsigned target, volatile int* abort_flag,
+                                                md_devflags* flags, unsigned site) {
+    const unsigned long long t0 = global_ns();
+    for (unsigned spin = 0;; ++spin) {
+        if (*stored >= target) {
+            __threadfence_block();
+            return true;
+        }
+        if (*abort_flag) return false;
+        if ((spin & 63u) == 63u && global_ns() - t0 > WAIT_BUDGET_NS) {
+            *abort_flag = 1;
+            md_flag_timeout(flags, site);
+            return false;
+        }
+        __nanosleep(64);
+    }
+}
+
 template <int BLOCK_N, bool B_MN_MAJOR, int MT>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS_PUSH, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_c, int M, int N, int K, int tiles_m, int num_tiles,
                md_epilogue ep, md_push push, md_devflags* flags) {
@@ -79,9 +118,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const uint32_t bar_tfull = bars + 16 * STAGES, bar_tempty = bar_tfull + 16;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_ptr + 16 * STAGES + 32);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 16 * STAGES + 36);
+    // epilogue warps that have finished a tile (all of its TMA stores complete), counted over the CTA's tiles
+    volatile unsigned* stored = reinterpret_cast<volatile unsigned*>(bars_ptr + 16 * STAGES + 40);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    const int tiles_n = num_tiles / tiles_m;
 
     // programmatic dependent launch: the successor may start its own set-up now; this kernel sets up its
     // barriers and tensor memory, then waits for its predecessor before any global access
@@ -100,6 +142,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             mbar_init(bar_tempty + 8 * b, EPI_WARPS);
         }
         *abort_flag = 0;
+        *stored = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -121,7 +164,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             int stage = 0;
             uint32_t phase = 0;
             for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-                const int m0 = (tile % tiles_m) * TILE_M, n0 = (tile / tiles_m) * BLOCK_N;
+                int tm, tn;
+                tile_coords(tile, tiles_m, tiles_n, tm, tn);
+                const int m0 = tm * TILE_M, n0 = tn * BLOCK_N;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, flags, 1);
                     const uint32_t full = bar_full + 8 * stage;
@@ -193,7 +238,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 tc_commit(bar_tfull + 8 * buf);  // accumulator complete
             }
         }
-    } else {
+    } else if (warp < 2 + EPI_WARPS) {
         // ------------------------------------------------------------ epilogue (warps 2..9)
         // Two warps per TMEM lane quadrant; they take alternate 64-column chunks of the tile.
         const int quad = warp & 3;  // TMEM lane quadrant this warp may read
@@ -203,7 +248,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const bool any_glue = ep.bias || ep.residual || ep.residual2 || ep.gelu;
         int local = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
-            const int m0 = (tile % tiles_m) * TILE_M, n0 = (tile / tiles_m) * BLOCK_N;
+            int tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const int m0 = tm * TILE_M, n0 = tn * BLOCK_N;
             const int buf = local % NBUF;
             const uint32_t acc_phase = (uint32_t)(local / NBUF) & 1u;
             mbar_wait(bar_tfull + 8 * buf, acc_phase, abort_flag, flags, 4);
@@ -281,20 +328,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     tma_store_2d(&tm_c, my_epi, n0 + c * 64, mrow0);
                     tma_store_commit();
                 }
-                if (push.n > 0) {
-                    // Column-split GEMM: the same chunk goes to the other GPUs' copies of C with plain
-                    // peer stores, 128 contiguous bytes per row per instruction (8 lanes x 16 B).
-#pragma unroll
-                    for (int it = 0; it < 8; ++it) {
-                        const int r = it * 4 + (lane >> 3), ch = lane & 7;
-                        const uint4 val = *reinterpret_cast<const uint4*>(my_epi_ptr + r * 128 + ((ch ^ (r & 7)) * 16));
-                        const int gm = mrow0 + r, gc = n0 + c * 64 + ch * 8;
-                        if (gm < M && gc < N) {
-                            for (int pi = 0; pi < push.n; ++pi)
-                                *reinterpret_cast<uint4*>(push.base[pi] + (long long)gm * push.ld + gc) = val;
-                        }
-                    }
-                }
             }
             if (half >= CHUNKS) {
                 // a warp without a chunk (tile narrower than its share) still releases the accumulator
@@ -302,9 +335,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
             }
+            if (push.n > 0 && lane == 0) {
+                // Column-split GEMM: this warp's part of the tile is in this GPU's C once its TMA stores have
+                // completed; tell the push warps (every epilogue warp counts once per tile).  The wait costs
+                // nothing: the warp would next wait for the following tile's accumulator anyway.
+                tma_store_wait_all();
+                __threadfence_block();
+                atomicAdd(const_cast<unsigned*>(stored), 1u);
+            }
         }
         if (lane == 0) tma_store_wait_all();
-        if (push.n > 0) __threadfence_system();  // peer stores performed before the kernel ends
+    } else {
+        // ------------------------------------------------------------ push (warps 10..13, column-split GEMM)
+        // A warp instruction covers 32 / (BLOCK_N / 8) whole tile rows (BLOCK_N * 2 contiguous bytes each); four
+        // row groups are loaded before their peer stores are issued, peers interleaved.
+        constexpr int LANES_PER_ROW = BLOCK_N / 8, ROWS_PER_INSTR = 32 / LANES_PER_ROW, UNR = 4;
+        constexpr int ROW_STEP = PUSH_WARPS * ROWS_PER_INSTR;
+        const int pw = warp - (2 + EPI_WARPS);
+        const int sub = lane / LANES_PER_ROW, cl = (lane % LANES_PER_ROW) * 8;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+            int tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const int m0 = tm * TILE_M, n0 = tn * BLOCK_N;
+            if (!wait_stored(stored, (unsigned)(EPI_WARPS * (local + 1)), abort_flag, flags, 5)) break;
+            const int gc = n0 + cl;
+            if (gc >= N) continue;  // columns past this rank's block belong to a neighbour
+            for (int r = pw * ROWS_PER_INSTR + sub; r < TILE_M; r += ROW_STEP * UNR) {
+                uint4 val[UNR];
+                long long off[UNR];
+#pragma unroll
+                for (int u = 0; u < UNR; ++u) {
+                    const int gm = m0 + r + u * ROW_STEP;
+                    off[u] = (r + u * ROW_STEP < TILE_M && gm < M) ? (long long)gm * push.ld + gc : -1;
+                    if (off[u] >= 0) val[u] = __ldcg(reinterpret_cast<const uint4*>(push.self + off[u]));
+                }
+                for (int pi = 0; pi < push.n; ++pi) {
+                    // start with a different peer in every CTA so that the stores spread over the links
+                    int peer = pi + (int)blockIdx.x;
+                    peer -= (peer / push.n) * push.n;
+#pragma unroll
+                    for (int u = 0; u < UNR; ++u)
+                        if (off[u] >= 0) *reinterpret_cast<uint4*>(push.base[peer] + off[u]) = val[u];
+                }
+            }
+        }
+        __threadfence_system();  // peer stores performed before the kernel ends
     }
 
     tc_fence_before();
@@ -366,8 +442,9 @@ int launch(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, s
         MD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         ctx->tc_configured |= cfg_bit;
     }
-    return md_launch_ex(ctx, kern, dim3((unsigned)grid), dim3(NUM_THREADS), smem, "gemm_tc_kernel", tm_a, tm_b, tm_c, (int)M,
-                        (int)N, (int)K, tiles_m, num_tiles, ep, push, ctx->flags);
+    ctx->last_tc_tile = MT == 2 ? 512 : BLOCK_N;
+    return md_launch_ex(ctx, kern, dim3((unsigned)grid), dim3(push.n > 0 ? NUM_THREADS_PUSH : NUM_THREADS), smem,
+                        "gemm_tc_kernel", tm_a, tm_b, tm_c, (int)M, (int)N, (int)K, tiles_m, num_tiles, ep, push, ctx->flags);
 }
 
 }  // namespace
@@ -403,9 +480,8 @@ int md_launch_gemm_tc_ex(md_ctx* ctx, const __half* a, const __half* b, __half* 
     int bn = 64, mt = 1;
     if (M > 64) {
         const int cand_n[4] = {256, 256, 128, 64}, cand_mt[4] = {2, 1, 1, 1};
-        double best = 0;
+        double best = -1.0;
         for (int i = 0; i < 4; ++i) {
-            if (cand_mt[i] == 2 && push.n > 0) continue;  // the peer-push epilogue is written for 128-row tiles
             const size_t rows = (size_t)cand_mt[i] * BLOCK_M;
             const size_t t = ((M + rows - 1) / rows) * ((N + cand_n[i] - 1) / cand_n[i]);
             const size_t waves = (t + ctx->sm_count - 1) / ctx->sm_count;
@@ -416,8 +492,19 @@ int md_launch_gemm_tc_ex(md_ctx* ctx, const __half* a, const __half* b, __half* 
             const bool glue = ep.bias || ep.gelu || ep.residual || ep.residual2;
             const double tile = (double)(rows + cand_n[i]) * kblocks * (cand_mt[i] == 2 ? 1.3 : 1.0) +
                                 (cand_mt[i] == 2 ? (glue ? 7000.0 : 2500.0) : 0.0);
-            const double cost = (double)waves * tile;
-            if (i == 0 || cost < best) { best = cost; bn = cand_n[i]; mt = cand_mt[i]; }
+            double cost = (double)waves * tile;
+            if (push.n > 0) {
+                // Column-split GEMM: the block also has to cross NVLink to every peer (~770 GB/s per direction: in
+                // the units of `tile`, 128 bytes pulled from L2 = ~2.5 cycles, about 1000 bytes of link time).  The
+                // pushes can start when the first tile is done, and the last wave's tiles are pushed after the math.
+                const double per_byte = 1.0 / 1000.0;
+                const double total_push = (double)M * (double)N * 2.0 * push.n * per_byte;
+                const size_t last_wave = t - (waves - 1) * (size_t)ctx->sm_count;
+                const double tail_push = (double)last_wave * (double)(rows * cand_n[i]) * 2.0 * push.n * per_byte;
+                const double through = tile + total_push;
+                cost = cost + tail_push > through ? cost + tail_push : through;
+            }
+            if (best < 0.0 || cost < best) { best = cost; bn = cand_n[i]; mt = cand_mt[i]; }
         }
     }
     if (ctx->tc_block_n) {  // forced: 512 = the 256 x 256 tile

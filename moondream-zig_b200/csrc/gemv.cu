@@ -130,8 +130,9 @@ gemv_nt_mma_kernel(const __half* A, const __half* __restrict__ Bt, __half* C, in
     partial[warp][g + 8][2 * t] = acc[2];
     partial[warp][g + 8][2 * t + 1] = acc[3];
     __syncthreads();
-    if (threadIdx.x < ROWS_PER_CTA * 8) {
-        const int m = threadIdx.x >> 4, r = threadIdx.x & 15;  // consecutive threads -> consecutive n
+    // 16 rows x 8 activation rows = 128 outputs; a CTA of two warps takes two turns
+    for (int o = threadIdx.x; o < ROWS_PER_CTA * 8; o += WARPS * 32) {
+        const int m = o >> 4, r = o & 15;  // consecutive threads -> consecutive n
         const int n = row0 + r;
         if (m < M && n < N) {
             float s = 0.f;

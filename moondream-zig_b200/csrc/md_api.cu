@@ -145,6 +145,7 @@ int md_scratch(md_ctx* ctx, size_t bytes, void** out) {
         cap = (cap + 255) & ~(size_t)255;
         MD_CUDA(ctx, cudaMalloc(&ctx->scratch, cap));
         ctx->scratch_cap = cap;
+        ctx->generation++;  // graphs that hold the old address are stale
     }
     *out = ctx->scratch;
     return MD_OK;
@@ -164,6 +165,7 @@ int md_rope_cached(md_ctx* ctx, size_t rot_dim, float theta, size_t rows, const 
         ctx->rope_rows = rows;
         ctx->rope_dim = rot_dim;
         ctx->rope_theta = theta;
+        ctx->generation++;  // graphs that hold the old table are stale
         MD_TRY(md_launch_rope_table(ctx, ctx->rope_tab, rot_dim, rows, theta));
     }
     *out = ctx->rope_tab;
@@ -306,6 +308,7 @@ int md_launch_count(const md_ctx* ctx, uint64_t* count_out) {
 int md_set_option(md_ctx* ctx, const char* key, long value) {
     MD_NEED_CTX(ctx);
     MD_NEED(ctx, key, "md_set_option: null key");
+    ctx->generation++;  // options select kernels: graphs captured under the old settings are captured again
     if (!strcmp(key, "gemv_variant")) { ctx->gemv_variant = (int)value; return MD_OK; }
     if (!strcmp(key, "decode_cluster")) {
         ctx->decode_cluster_mode = value < 0 ? -1 : (value ? 1 : 0);
@@ -328,6 +331,16 @@ int md_set_option(md_ctx* ctx, const char* key, long value) {
         return MD_OK;
     }
     return md_fail(ctx, MD_ERR_INVALID_ARG, "md_set_option: unknown key '%s'", key);
+}
+
+int md_get_option(md_ctx* ctx, const char* key, long* value_out) {
+    MD_NEED_CTX(ctx);
+    MD_NEED(ctx, key && value_out, "md_get_option: null argument");
+    if (!strcmp(key, "last_tc_tile")) { *value_out = ctx->last_tc_tile; return MD_OK; }
+    if (!strcmp(key, "gemv_variant")) { *value_out = ctx->gemv_variant; return MD_OK; }
+    if (!strcmp(key, "tc_block_n")) { *value_out = ctx->tc_block_n; return MD_OK; }
+    if (!strcmp(key, "pdl")) { *value_out = ctx->pdl; return MD_OK; }
+    return md_fail(ctx, MD_ERR_INVALID_ARG, "md_get_option: unknown key '%s'", key);
 }
 
 int md_graph_begin(md_ctx* ctx) {
@@ -376,6 +389,7 @@ int md_set_gemm_mode(md_ctx* ctx, int mode) {
     MD_NEED_CTX(ctx);
     MD_NEED(ctx, mode >= 0 && mode <= 2, "md_set_gemm_mode: mode must be 0, 1 or 2");
     ctx->gemm_mode = mode;
+    ctx->generation++;
     return MD_OK;
 }
 
@@ -467,6 +481,7 @@ int md_hgemm_colsplit_push(md_ctx* ctx, const uint16_t* a, const uint16_t* b_sli
         MD_NEED(ctx, peer_c_full[i], "colsplit_push: null peer pointer");
         push.base[i] = reinterpret_cast<__half*>(peer_c_full[i]) + col_offset;
     }
+    push.self = reinterpret_cast<const __half*>(c_full) + col_offset;
     md_epilogue ep;
     return md_launch_gemm_tc_ex(ctx, (const __half*)a, (const __half*)b_slice, (__half*)c_full + col_offset, M, N_local, K,
                                 b_layout, ep, N_total, push);

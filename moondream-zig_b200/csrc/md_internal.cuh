@@ -64,13 +64,19 @@ struct md_ctx {
     // cuTensorMapEncodeTiled resolved through the runtime (no link against libcuda)
     void* encode_tiled = nullptr;
     uint32_t tc_configured = 0;  // tcgen05 kernels whose dynamic shared memory limit has been raised
+    bool sdpa_mma_configured = false;  // the same for the mma.sync attention kernels
     // (cos, sin) table shared by the fused attention calls: [rope_rows][rope_dim/2][2] f32
     float* rope_tab = nullptr;
     size_t rope_rows = 0, rope_dim = 0;
     float rope_theta = 0.f;
     bool capturing = false;  // between md_graph_begin and md_graph_end
+    // Bumped whenever something a captured graph may have baked in changes: the scratch buffer or the rope table
+    // moved (md_scratch / md_rope_cached reallocated them) or an option that selects kernels was set.  The model
+    // runners store the value with every graph they keep and capture again when it differs.
+    uint64_t generation = 0;
     int gemv_variant = 0;    // md_set_option("gemv_variant")
     int tc_block_n = 0;      // md_set_option("tc_block_n")
+    int last_tc_tile = 0;    // md_get_option("last_tc_tile"): tile of the last tcgen05 GEMM launch (64/128/256, 512 = 256 x 256)
     int decode_cluster_ok = -1;    // -1 unknown, 0/1: 16-CTA clusters usable for the decode attention merge
     int decode_cluster_mode = -1;  // md_set_option("decode_cluster"): 0 forces the scratch-based merge
     int dualk_variant = 0;   // md_set_option("dualk_variant"): (warps, unroll) of gemv_dual_k_kernel
@@ -168,6 +174,7 @@ struct md_push {
     int n = 0;                 // number of peers (0 = none)
     long long ld = 0;          // row stride of the peers' C in elements
     __half* base[7] = {};      // peer pointers to element (0, 0) of this rank's column block
+    const __half* self = nullptr;  // the same element of this rank's own C (the push warps read the tile back from it)
 };
 
 // gemv.cu: C[M,N] = A[M,K] . Bt[N,K]^T for M <= 8, K % 8 == 0.

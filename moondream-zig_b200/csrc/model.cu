@@ -123,6 +123,7 @@ struct md_text_request {
     DevPtr persist_tab, persist_scratch, persist_ctr;
     size_t persist_batch = 0;  // 0: the persistent step is not in use for the current generate call
     md_graph* graph = nullptr;
+    uint64_t graph_gen = 0, prefill_graph_gen = 0;  // md_ctx::generation the graphs were captured under
     size_t graph_steps = 0;
     bool graph_forced = false, graph_logits = false, graph_persistent = false;
     // a prefill of the same shape at the same position seen twice is captured and replayed
@@ -490,7 +491,8 @@ int md_text_forward(md_text_model* model, md_text_request* req, const uint16_t* 
         MD_LAUNCH_CHECK(ctx, "set_int_kernel");
         return MD_OK;
     };
-    if (S > 1 && req->prefill_graph && req->prefill_S == S && req->prefill_pos == pos0) {
+    if (S > 1 && req->prefill_graph && req->prefill_S == S && req->prefill_pos == pos0 &&
+        req->prefill_graph_gen == ctx->generation) {
         MD_TRY(md_graph_launch(ctx, req->prefill_graph));
     } else {
         MD_TRY(body());
@@ -503,6 +505,7 @@ int md_text_forward(md_text_model* model, md_text_request* req, const uint16_t* 
             const int st2 = md_graph_end(ctx, &g);
             if (st == MD_OK && st2 == MD_OK) {
                 req->prefill_graph = g;
+                req->prefill_graph_gen = ctx->generation;
                 req->prefill_S = S;
                 req->prefill_pos = pos0;
             } else if (g) {
@@ -653,7 +656,8 @@ static int generate_impl(md_text_model* model, md_text_request* const* reqs, siz
 
     // The graph depends on the requests' buffers and on which optional outputs exist; a single
     // request keeps its graph across calls, a batch captures one per call.
-    const bool reuse = batch == 1 && r0->graph && r0->graph_steps == n_steps && r0->graph_forced == (forced != nullptr) &&
+    const bool reuse = batch == 1 && r0->graph && r0->graph_gen == ctx->generation && r0->graph_steps == n_steps &&
+                       r0->graph_forced == (forced != nullptr) &&
                        r0->graph_persistent == (r0->persist_batch == batch) &&
                        r0->graph_logits == (logits_out != nullptr);
     md_graph* graph = reuse ? r0->graph : nullptr;
@@ -673,6 +677,7 @@ static int generate_impl(md_text_model* model, md_text_request* const* reqs, siz
             if (batch == 1) {
                 if (r0->graph) md_graph_destroy(ctx, r0->graph);
                 r0->graph = g;
+                r0->graph_gen = ctx->generation;
                 r0->graph_steps = n_steps;
                 r0->graph_forced = forced != nullptr;
                 r0->graph_persistent = r0->persist_batch == batch;
@@ -733,6 +738,7 @@ struct md_vision_model {
     size_t max_crops = 0, patch_dim = 0, patch_dim_padded = 0;
     DevPtr patch_w_padded, img, patches, x, ln, qkv, att, fc1, cat, pfc1, out;
     md_graph* graph = nullptr;  // the whole encode for (graph_crops, graph_a, graph_b), captured on its second use
+    uint64_t graph_gen = 0;     // md_ctx::generation the graph was captured under
     size_t graph_crops = 0, graph_a = 0, graph_b = 0, seen_crops = 0, seen_a = 0, seen_b = 0;
 };
 
@@ -858,7 +864,8 @@ int md_vision_encode(md_vision_model* m, const uint8_t* crops_u8, size_t crops, 
                                 w.proj_hidden, 0, e_p2));
         return MD_OK;
     };
-    if (m->graph && m->graph_crops == crops && m->graph_a == crop_a && m->graph_b == crop_b) {
+    if (m->graph && m->graph_gen == ctx->generation && m->graph_crops == crops && m->graph_a == crop_a &&
+        m->graph_b == crop_b) {
         MD_TRY(md_graph_launch(ctx, m->graph));
     } else {
         MD_TRY(body());
@@ -872,6 +879,7 @@ int md_vision_encode(md_vision_model* m, const uint8_t* crops_u8, size_t crops, 
             const int st2 = md_graph_end(ctx, &g);
             if (st == MD_OK && st2 == MD_OK) {
                 m->graph = g;
+                m->graph_gen = ctx->generation;
                 m->graph_crops = crops; m->graph_a = crop_a; m->graph_b = crop_b;
             } else if (g) {
                 md_graph_destroy(ctx, g);

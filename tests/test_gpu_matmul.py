@@ -128,6 +128,22 @@ def test_config2_decode_gemv(ctx, oracle, m, k, n):
     assert_close_ref(got, oracle.hgemm_nt(a, w), f"gemv M={m} {k}->{n}")
 
 
+@pytest.mark.parametrize("variant", [1, 2, 3, 4, 5, 6])
+@pytest.mark.parametrize("m", [1, 5, 8])
+def test_gemv_fixed_variants(ctx, oracle, variant, m):
+    """Every fixed (warps, unroll) configuration of the GEMV kernel, including the two-warp one whose 64 threads
+    take two turns over the 128 outputs of a CTA; N not a multiple of 16, K not a multiple of 32."""
+    rng = np.random.default_rng(10 * variant + m)
+    k, n = 2056, 1000
+    a, w = f16_normal(rng, (m, k)), f16_normal(rng, (n, k), 0.05)
+    ctx.set_option("gemv_variant", variant)
+    try:
+        got = ctx.hgemm_nt(a, w, m, n, k)
+    finally:
+        ctx.set_option("gemv_variant", 0)
+    assert_close_ref(got, oracle.hgemm_nt(a, w), f"gemv variant {variant} M={m}")
+
+
 @pytest.mark.parametrize("m,k,n", [(3, 2048, 100), (8, 40, 17), (1, 8, 1), (5, 8200, 33)])
 def test_gemv_edges(ctx, oracle, m, k, n):
     rng = np.random.default_rng(n)

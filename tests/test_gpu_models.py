@@ -86,6 +86,48 @@ def test_text_free_running_generation_and_graph_reuse(ctx, oracle, models_mod):
     req.close(); gpu.close()
 
 
+def test_text_graphs_are_captured_again_when_the_context_moves_its_buffers(ctx, models_mod):
+    """A request keeps the CUDA graphs of its decode step and its prefill.  They hold the addresses of the context's
+    scratch buffer and rope table; another caller on the same context can make both move (here: a prefill attention
+    over a longer cache, which needs a longer rope table and more scratch) and an option can change which kernels a
+    step uses.  The runners must notice and capture again: same tokens before and after."""
+    w = text_weights(4011, n_layers=2, hidden=512, vocab=2048)
+    gpu = models_mod.TextModel(ctx, w)
+    rng = np.random.default_rng(11)
+    embeds = w["wte"][rng.integers(0, 2048, 24)]
+    req = gpu.request()
+
+    def run():
+        req.reset()
+        _, _, tok = gpu.forward(req, embeds)
+        return tok, gpu.generate(req, tok, 12)
+
+    first = [run() for _ in range(3)][-1]          # third pass replays both captured graphs
+    # a foreign call on the same context: 4096-position cache -> the rope table is rebuilt, 9 MB of rotated q
+    S, heads, d, max_seq = 2304, 32, 64, 4096
+    qkv = ctx.upload((rng.standard_normal((S, 3 * heads * d)) * 0.5).astype(np.float16))
+    kc, vc, out = ctx.alloc((heads, max_seq, d)), ctx.alloc((heads, max_seq, d)), ctx.alloc((S, heads * d))
+    ctx.sdpa_prefill_fused(qkv, kc, vc, out, S, heads, d, max_seq, 0, 32)
+    ctx.sync()
+    for b in (qkv, kc, vc, out):
+        b.free()
+    again = run()
+    assert again[0] == first[0]
+    np.testing.assert_array_equal(again[1], first[1])
+    # an option set after the capture takes effect on the next call (and gives the same tokens here)
+    ctx.set_option("decode_fork", 0)
+    try:
+        n0 = ctx.launch_count()
+        unforked = run()
+        launched = ctx.launch_count() - n0
+    finally:
+        ctx.set_option("decode_fork", 1)
+    assert launched > 0                                # the step was enqueued again, not replayed from the stale graph
+    assert unforked[0] == first[0]
+    assert (unforked[1] == first[1]).mean() >= 0.8     # other kernels, same rounding points
+    req.close(); gpu.close()
+
+
 def test_text_fused_decode_layer_matches_unfused_kernels(ctx, models_mod):
     """The 3-kernel decode layer (LayerNorm+qkv+fc1, attention, out-proj+fc2+residuals) against the same step
     run as separate LayerNorm / GEMV kernels: same rounding points, so logits agree to the parity bar."""
@@ -312,11 +354,13 @@ def test_vision_small_two_identical_crops_match_the_reference_joint_attention(ct
     gpu.close()
 
 
-@pytest.mark.parametrize("crops", [1, 5])
+@pytest.mark.parametrize("crops", [1, 5, 13])
 def test_vision_small_crops(ctx, oracle, models_mod, crops):
     run_vision(ctx, oracle, models_mod, vision_weights(3002, n_layers=2), crops, seed=crops)
 
 
-def test_vision_full_config3_one_crop(ctx, oracle, models_mod):
-    """benchmark config 3 at full depth (27 layers), one crop."""
-    run_vision(ctx, oracle, models_mod, vision_weights(3000), 1, seed=11)
+@pytest.mark.parametrize("crops", [1, 5, 13])
+def test_vision_full_config3(ctx, oracle, models_mod, crops):
+    """benchmark config 3 at full depth (27 layers) for every crop count it names: 1, 5 and 13 crops per image
+    (vision_model.zig:204-272 run per crop; features of every crop and the projection output checked)."""
+    run_vision(ctx, oracle, models_mod, vision_weights(3000), crops, seed=10 + crops)
