@@ -1,12 +1,14 @@
 #!/usr/bin/env python
-"""Benchmark of the decode GEMV hot path (benchmark config 2: the decode GEMV sweep) on N B200 GPUs of one node.
+"""Benchmark of the decode GEMV hot path (the decode GEMV sweep) on N B200 GPUs of one node.
 
-Workload ("step"): one pass over the decode GEMV sweep — M in {1,2,4,8} activation rows
-times the five Phi-1.5 layer shapes (K->N: 2048->6144, 2048->2048, 2048->8192, 8192->2048,
-2048->51200), f16 weights ~N(0,0.02) resident in HBM, activations ~N(0,1): 20 launches of
-the GEMV kernel, replayed as one CUDA graph.  The metric is achieved HBM GB/s counted with
-the reference's own byte formula 2*(M*K + K*N + M*N) (hgemm_trans.zig:580-593).  The sweep
-touches 1.24 GB per pass, ten times the L2, so no flush is needed between iterations.
+Workload: the decode GEMV sweep — M in {1,2,4,8} activation rows times the five Phi-1.5 layer
+shapes (K->N: 2048->6144, 2048->2048, 2048->8192, 8192->2048, 2048->51200), f16 weights
+~N(0,0.02) resident in HBM, activations ~N(0,1): 20 launches of the GEMV kernel, replayed as
+one CUDA graph.  A "step" is SWEEPS_PER_STEP passes over the sweep (one pass is 0.2 ms on a
+B200; the timed region of the default run lasts more than a second, so the clock samples are
+taken under the measured load).  The metric is achieved HBM GB/s counted with the reference's
+own byte formula 2*(M*K + K*N + M*N) (hgemm_trans.zig:580-593).  A pass touches 1.24 GB of
+distinct weights, ten times the L2, so no flush is needed between iterations.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
@@ -42,7 +44,17 @@ def algo_bytes(m, k, n):
     return 2 * (m * k + k * n + m * n)
 
 
-STEP_BYTES = sum(algo_bytes(m, k, n) for m in MS for k, n in SHAPES)
+SWEEP_BYTES = sum(algo_bytes(m, k, n) for m in MS for k, n in SHAPES)
+SWEEPS_PER_STEP = 256
+STEP_BYTES = SWEEPS_PER_STEP * SWEEP_BYTES
+WORKLOAD = "decode GEMV sweep: M in {1,2,4,8} x the five Phi-1.5 layer shapes, 20 weight matrices of their own"
+
+
+def workload_config():
+    """The workload description both arms print (identical dicts)."""
+    return {"workload": WORKLOAD, "bytes_per_sweep": SWEEP_BYTES, "sweeps_per_step": SWEEPS_PER_STEP,
+            "bytes_per_step": STEP_BYTES,
+            "l2": "inputs larger than L2: 1.24 GB of distinct weights per sweep, each byte read once per sweep"}
 
 
 def measured_peaks():
@@ -62,6 +74,13 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.proc, self.lines = index, None, []
+        self.t_begin = self.t_end = None
+
+    def mark_begin(self):
+        self.t_begin = time.time()
+
+    def mark_end(self):
+        self.t_end = time.time()
 
     def start(self):
         try:
@@ -75,7 +94,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
     def stop(self):
         if not self.proc:
@@ -87,7 +106,11 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        # nvidia-smi needs most of a second to print its first line, so it is started before the warm-up; only the
+        # lines that arrived between the start and the end of the timed region are used
+        inside = [ln for (t, ln) in self.lines
+                  if self.t_begin is None or (self.t_begin <= t <= (self.t_end or t) + 0.05)]
+        for ln in inside:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 8:
                 continue
@@ -100,13 +123,16 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": "timed region only"}
 
 
 def make_inputs(seed=2000):
-    """Seeded synthetic inputs of config 2 (weights ~N(0,0.02), activations ~N(0,1))."""
+    """Seeded synthetic inputs of the sweep (weights ~N(0,0.02), activations ~N(0,1)).  Every one of the 20 problems
+    owns its weight matrix, as in the reference's benchmark (a fresh B per case): the matrix of (M, shape) is the
+    shape's base matrix rotated by M rows."""
     rng = np.random.default_rng(seed)
-    ws = [(rng.standard_normal((n, k), dtype=np.float32) * 0.02).astype(np.float16) for k, n in SHAPES]
+    base = [(rng.standard_normal((n, k), dtype=np.float32) * 0.02).astype(np.float16) for k, n in SHAPES]
+    ws = {(m, i): (base[i] if m == MS[0] else np.roll(base[i], m, axis=0)) for m in MS for i in range(len(SHAPES))}
     xs = {(m, i): rng.standard_normal((m, k), dtype=np.float32).astype(np.float16)
           for m in MS for i, (k, n) in enumerate(SHAPES)}
     return ws, xs
@@ -115,11 +141,12 @@ def make_inputs(seed=2000):
 def cpu_sweep(oracle, ws, xs):
     for m in MS:
         for i in range(len(SHAPES)):
-            oracle.hgemm_nt(xs[(m, i)], ws[i])
+            oracle.hgemm_nt(xs[(m, i)], ws[(m, i)])
 
 
 def run_reference(args, rank):
-    """The reference arm: the CPU oracle on the host cores, all threads, same sweep."""
+    """The reference arm: the CPU oracle on the host cores, all threads.  A step of this arm is a bounded sample of
+    the workload's step: one of its SWEEPS_PER_STEP sweeps (1.24 GB of weights, all 20 problems)."""
     if rank != 0:
         return
     from oracle import oracle
@@ -131,17 +158,17 @@ def run_reference(args, rank):
     for _ in range(args.steps):
         cpu_sweep(oracle, ws, xs)
     dt = (time.perf_counter() - t0) / args.steps
-    val = STEP_BYTES / dt / 1e9
+    val = SWEEP_BYTES / dt / 1e9
     cores = oracle.get_threads()
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": dt * 1e3 * SWEEPS_PER_STEP, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "decode GEMV sweep: M in {1,2,4,8} x Phi-1.5 layer shapes (BASELINE config 2)",
-                   "bytes_per_step": STEP_BYTES},
+        "config": workload_config(),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": "the full 20-GEMV sweep per step (C++ restatement of hgemm_trans.zig; the Zig "
-                                   "reference cannot be built here)"},
+                         "sample": "one sweep (all 20 problems, 1.24 GB) of the 256 sweeps of a step, per timed step; "
+                                   "ms_per_step is the sample scaled to a full step (C++ restatement of "
+                                   "hgemm_trans.zig; the Zig reference cannot be built here)"},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -151,7 +178,7 @@ def run_reference(args, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the per-shape and GEMM side measurements")
@@ -192,9 +219,7 @@ def main():
     ws_h, xs_h = make_inputs()
     # every one of the 20 problems owns its weight matrix, as in the reference's benchmark (a fresh B per case):
     # 1.24 GB of distinct weights per step, so no byte can be served twice from L2 inside a step either
-    ws0 = [torch.from_numpy(w).cuda() for w in ws_h]
-    wsm = {(m, i): (ws0[i] if m == MS[0] else torch.roll(ws0[i], shifts=m, dims=0).contiguous())
-           for m in MS for i in range(len(SHAPES))}
+    wsm = {key: torch.from_numpy(w).cuda() for key, w in ws_h.items()}
     xs = {key: torch.from_numpy(x).cuda() for key, x in xs_h.items()}
     ys = {(m, i): torch.empty((m, n), dtype=torch.float16, device="cuda") for m in MS for i, (k, n) in enumerate(SHAPES)}
 
@@ -243,43 +268,58 @@ def main():
         for ev in joins:
             stream.wait_event(ev)
 
-    n0 = ctx.launch_count()
-    ctx.graph_begin()
-    if branches > 1:
-        sweep_branched()
-    else:
-        sweep()
-    graph = ctx.graph_end()
-    launches_per_step = ctx.launch_count() - n0
+    def capture(fn):
+        n0 = ctx.launch_count()
+        ctx.graph_begin()
+        fn()
+        g = ctx.graph_end()
+        return g, ctx.launch_count() - n0
 
-    for _ in range(max(args.warmup, 3)):
+    graph, launches_per_sweep = capture(sweep_branched if branches > 1 else sweep)
+
+    def timed(g, steps, sampler=None):
+        """`steps` steps of SWEEPS_PER_STEP graph replays each, CUDA events on the launching stream, barriers and
+        synchronisation on both sides; returns the max over ranks of the mean ms per step."""
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        barrier()
+        if sampler:
+            sampler.mark_begin()
+        ev0.record(stream)
+        for _ in range(steps * SWEEPS_PER_STEP):
+            ctx.graph_launch(g)
+        ev1.record(stream)
+        torch.cuda.synchronize()
+        if sampler:
+            sampler.mark_end()
+        barrier()
+        clk = sampler.stop() if sampler else None
+        t = torch.tensor([ev0.elapsed_time(ev1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item() / steps, clk
+
+    warm = max(args.warmup, 3)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for _ in range(warm * SWEEPS_PER_STEP):
         ctx.graph_launch(graph)
     ctx.sync()
-
-    sampler = ClockSampler(local_rank)
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    barrier()
-    sampler.start()
-    # keep the sampler fed: very short runs finish before nvidia-smi prints its first line
-    ev0.record(stream)
-    for _ in range(args.steps):
-        ctx.graph_launch(graph)
-    ev1.record(stream)
-    torch.cuda.synchronize()
-    barrier()
-    ms_total = ev0.elapsed_time(ev1)
-    if ms_total < 400:  # give nvidia-smi a few samples under the same load (not timed)
-        t_end = time.time() + 0.6
-        while time.time() < t_end:
-            ctx.graph_launch(graph)
-            ctx.sync()
-    clocks = sampler.stop()
-    t = torch.tensor([ms_total], device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = t.item() / args.steps
+    # the clock samples that count are those taken during the timed region (more than a second at 20 steps)
+    ms_step, clocks = timed(graph, args.steps, sampler)
     value = world * STEP_BYTES / (ms_step * 1e-3) / 1e9
+    launches_per_step = launches_per_sweep * SWEEPS_PER_STEP
+
+    # the same 20 launches as ONE dependent chain (what a caller gets who cannot overlap independent products)
+    single = None
+    if branches > 1 and not args.no_extras:
+        g1, _ = capture(sweep)
+        for _ in range(3 * 16):
+            ctx.graph_launch(g1)
+        ms1, _ = timed(g1, max(2, args.steps // 4))
+        single = {"value": world * STEP_BYTES / (ms1 * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ms1,
+                  "note": "the 20 GEMVs of a sweep as one programmatically dependent chain instead of four"}
+        ctx.graph_destroy(g1)
 
     # ---- end to end through the C ABI with HOST buffers: H2D of the activations and D2H of the
     # result inside every call (weights registered once), as the Zig host would call it
@@ -298,11 +338,10 @@ def main():
     ctx.lib.md_hgemm_nt.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t]
     for _ in range(3):
         e2e_sweep()
-    e2e_steps = max(5, min(args.steps, 20))
     torch.cuda.synchronize()
     barrier()
     t0 = time.perf_counter()
-    for _ in range(e2e_steps):
+    for _ in range(SWEEPS_PER_STEP):     # one step
         e2e_sweep()
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
@@ -310,16 +349,17 @@ def main():
     t = torch.tensor([dt], device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_val = world * STEP_BYTES / (t.item() / e2e_steps) / 1e9
-    h2d = sum(m * k * 2 for m in MS for k, n in SHAPES)
-    d2h = sum(m * n * 2 for m in MS for k, n in SHAPES)
+    e2e_val = world * STEP_BYTES / t.item() / 1e9
+    h2d = SWEEPS_PER_STEP * sum(m * k * 2 for m in MS for k, n in SHAPES)
+    d2h = SWEEPS_PER_STEP * sum(m * n * 2 for m in MS for k, n in SHAPES)
     err = (pin_y[(8, 4)].float() - (xs[(8, 4)].float() @ wsm[(8, 4)].float().T).cpu()).abs().max().item()
     assert err < 0.2, f"e2e parity check failed: {err}"
 
-    colsplit = None
+    colsplit = box = None
     if world > 1 and not args.no_extras:
         colsplit = colsplit_extras(ctx, torch, dist, stream, world, rank)
-        decode_replicas = decode_replicas_extras(ctx, torch, dist, world)
+    if not args.no_extras:
+        box = box_requests_extras(ctx, torch, dist if world > 1 else None, world, rank)
 
     if rank != 0:
         ctx.sync()
@@ -329,28 +369,34 @@ def main():
 
     hbm_peak, tensor_peak, peak_kind = measured_peaks()
     achieved = (STEP_BYTES / launches_per_step) / (ms_step * 1e-3 / launches_per_step) / 1e9
+    config = workload_config()      # the same dict the reference arm prints
+    launch = {"launches_per_step": launches_per_step, "sweep_chains": branches, "replay": "one CUDA graph per sweep",
+              "parallelism": f"replicas x{world}"}
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
-        "config": {"workload": "decode GEMV sweep: M in {1,2,4,8} x Phi-1.5 layer shapes (BASELINE config 2)",
-                   "bytes_per_step": STEP_BYTES, "launches_per_step": launches_per_step,
-                   "l2": "inputs larger than L2: 20 distinct weight matrices, 1.24 GB per step, each read once per step",
-                   "replay": "one CUDA graph per step", "parallelism": f"replicas x{world}"},
+        "config": config, "launch": launch,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                      "traffic": TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": peak_kind, "kernel": "gemv_nt_mma_kernel",
-                     "frac_of_nominal_8tbs": achieved / 8000.0},
+                     "frac_of_nominal_8tbs": achieved / 8000.0,
+                     "note": "four concurrent chains of independent GEMVs; as one dependent chain see single_chain"},
         "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "note": "md_hgemm_nt with pinned HOST activations/outputs per call (activations copied up, results written by the kernel into the pinned host buffer), weights registered once"},
+                "note": "md_hgemm_nt with pinned HOST activations/outputs per call (activations copied up, results written by the kernel into the pinned host buffer), weights registered once; one step = 256 sweeps = 5120 synchronous calls"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
+    if single is not None:
+        single["frac"] = single["value"] / world / hbm_peak
+        line["single_chain"] = single
 
     if not args.no_extras and world == 1:
         line["extras"] = extras(ctx, torch, stream, tensor_peak, hbm_peak)
         line["extras"].update(model_extras(ctx, torch))
     if colsplit is not None:
-        line["extras"] = {"colsplit_gemm_8192": colsplit, "decode_config4_replicas": decode_replicas}
+        line.setdefault("extras", {})["colsplit_gemm_8192"] = colsplit
+    if box is not None:
+        line.setdefault("extras", {})["box_requests"] = box
 
     # ---- CPU baseline: the oracle on this box's host cores, bounded sample
     from oracle import oracle
@@ -365,9 +411,15 @@ def main():
         best = d if best is None else min(best, d)
         if time.perf_counter() - t_begin > 20:
             break
-    line["cpu_baseline"] = {"value": STEP_BYTES / best / 1e9, "unit": UNIT, "cores": oracle.get_threads(), "kind": "port",
-                            "sample": "best of up to 5 full sweeps (1.24 GB each) of the C++ restatement of "
-                                      "hgemm_trans.zig on the host cores"}
+    line["cpu_baseline"] = {"value": SWEEP_BYTES / best / 1e9, "unit": UNIT, "cores": oracle.get_threads(), "kind": "port",
+                            "sample": "best of up to 5 sweeps (1.24 GB each; a step is 256 of them) of the C++ "
+                                      "restatement of hgemm_trans.zig on the host cores"}
+    if not args.no_extras and world == 1:
+        line["extras"]["cpu"] = cpu_extras(oracle)
+        if box is not None and "cpu" in line["extras"]:
+            c = line["extras"]["cpu"]["request_extrapolated"]
+            box["cpu_requests_per_s_extrapolated"] = round(1.0 / c["seconds_per_request"], 4)
+            box["cpu_decode_tok_s"] = c["decode_tok_s"]
     print(json.dumps(line), flush=True)
     ctx.graph_destroy(graph)
     ctx.sync()
@@ -380,38 +432,61 @@ SWEEP_BRANCHES = 4  # parallel chains the sweep graph is recorded as
 # summary sits under profiles/): 280.41 MB measured over the three captured launches (fc1, fc2, lm_head at
 # M = 1) against 276.97 MB of algorithmic bytes, a factor of 1.0124; traffic grows in proportion to the weight
 # bytes, so the average launch of the sweep is scaled by the same factor.
-TRAFFIC_BYTES_PER_LAUNCH = int(round(1.0124 * STEP_BYTES / 20))
+TRAFFIC_BYTES_PER_LAUNCH = int(round(1.0124 * SWEEP_BYTES / 20))
 
 
 def colsplit_extras(ctx, torch, dist, stream, world, rank):
-    """Benchmark config 5b: 8192^3 f16 GEMM with N split over the ranks; all-gather baseline (NCCL) against the
-    fused push epilogue.  Device time per call, max over ranks."""
+    """The 8192^3 f16 GEMM with N split over the ranks: all-gather baseline (ncclAllGather inside the library)
+    against the fused push epilogue, both through the library's own communicator.  Device time per call, max over
+    ranks.  Parity is asserted on every rank: the two forms agree bit for bit, and 64 sampled rows agree with an f32
+    product of the same operands within 1e-2 * max|ref|."""
     import importlib
     import __graft_entry__ as entry
     par = importlib.import_module(entry.PKG_NAME + ".parallel")
     M = N = K = 8192
-    a = torch.randn(M, K, device="cuda").half()
-    bs = (torch.randn(N // world, K, device="cuda") * 0.02).half()   # this rank's rows of B^T ([N,K] layout)
+    g = torch.Generator(device="cuda").manual_seed(5000)          # same operands on every rank
+    a = torch.randn(M, K, device="cuda", generator=g).half()
+    b = (torch.randn(N, K, device="cuda", generator=g) * 0.02).half()     # B^T, [N,K] layout
+    bs = par.slice_b(b, 1, world, rank)
+    rows = torch.arange(0, M, M // 64, device="cuda")
+    ref = a[rows].float() @ b.float().T
+    del b
     out = {"M": M, "N": N, "K": K, "world": world}
     peaks = measured_peaks()
+    comm = par.Comm(ctx)
+    results = {}
     for mode in ("allgather", "fused"):
-        g = par.ColSplitGemm(ctx, M, N, K, 1, mode=mode)
+        gm = par.ColSplitGemm(comm, M, N, K, 1, mode=mode)
         for _ in range(3):
-            g(a, bs)
-        torch.cuda.synchronize()
+            gm(a, bs)
+        comm.barrier()
+        ctx.sync()
         dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         reps = 10
         e0.record(stream)
         for _ in range(reps):
-            g(a, bs)
+            gm(a, bs)
         e1.record(stream)
-        torch.cuda.synchronize()
+        ctx.sync()
         t = torch.tensor([e0.elapsed_time(e1) / reps], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         us = t.item() * 1e3
         out[mode] = {"us": round(us, 1), "TFLOP/s_total": round(2.0 * M * N * K / us / 1e6, 1)}
-        del g
+        comm.barrier()
+        results[mode] = torch.from_numpy(gm.result()).cuda()
+        if mode == "fused":
+            out["fused"]["tile"] = ctx.get_option("last_tc_tile")
+        dist.barrier()
+        gm.close()
+    same = bool(torch.equal(results["fused"], results["allgather"]))
+    err = (results["fused"][rows].float() - ref).abs().max().item()
+    tol = 1e-2 * ref.abs().max().item()
+    ok = torch.tensor([1 if (same and err <= tol) else 0], device="cuda")
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    assert ok.item() == 1, f"rank {rank}: column-split parity failed (forms equal: {same}, err {err} vs tol {tol})"
+    out["parity_ok"] = True
+    out["parity"] = "fused == allgather bit for bit on every rank; 64 sampled rows within 1e-2*max|ref| of an f32 product"
     # roofline of the fused kernel: the slower of the math and the bytes that must cross NVLink
     t_math = 2.0 * M * (N / world) * K / (peaks[1] * 1e12)
     t_link = M * (N / world) * 2 * (world - 1) / 770e9
@@ -428,6 +503,9 @@ def colsplit_extras(ctx, torch, dist, stream, world, rank):
     e1.record(stream)
     torch.cuda.synchronize()
     out["local_gemm_us"] = round(e0.elapsed_time(e1) / 10 * 1e3, 1)
+    comm.close()
+    del results, a, bs, y
+    torch.cuda.empty_cache()
     return out
 
 
@@ -529,21 +607,125 @@ def decode_config4(tm, embeds, sync=None):
     return t1 - t0, t2 - t1
 
 
-def decode_replicas_extras(ctx, torch, dist, world):
-    """Decode tokens/s with one request per GPU (independent requests are partitioned over the GPUs: every rank holds
-    a full replica and decodes its own request, no collective on the data path).  Aggregate = world x 200 tokens
-    over the slowest rank's decode time."""
+def build_vision_model(ctx, torch, g, n):
+    """Random-init SigLIP-style ViT + projection weights of the real shapes on the device; returns the weight dict and
+    a constructor taking the crop capacity."""
+    import importlib
+    import __graft_entry__ as entry
+    models = importlib.import_module(entry.PKG_NAME + ".models")
+    Lv, Dv, Fv = 27, 1152, 4304
+    onev, zerov = torch.ones(Dv, device="cuda").half(), torch.zeros(Dv, device="cuda").half()
+    vw = {"ln1_w": [onev] * Lv, "ln1_b": [zerov] * Lv, "ln2_w": [onev] * Lv, "ln2_b": [zerov] * Lv,
+          "wqkv": [n(Dv, 3 * Dv) for _ in range(Lv)], "bqkv": [n(3 * Dv) for _ in range(Lv)],
+          "wout": [n(Dv, Dv) for _ in range(Lv)], "bout": [n(Dv) for _ in range(Lv)],
+          "wfc1": [n(Dv, Fv) for _ in range(Lv)], "bfc1": [n(Fv) for _ in range(Lv)],
+          "wfc2": [n(Fv, Dv) for _ in range(Lv)], "bfc2": [n(Dv) for _ in range(Lv)],
+          "patch_w": n(588, Dv), "patch_b": n(Dv), "pos_emb": n(729, Dv), "norm_w": onev, "norm_b": zerov,
+          "proj_fc1_w": n(2 * Dv, 8192), "proj_fc1_b": n(8192), "proj_fc2_w": n(8192, 2048), "proj_fc2_b": n(2048)}
+    return vw, (lambda crops: models.VisionModel(ctx, vw, max_crops=crops))
+
+
+def box_requests_extras(ctx, torch, dist, world, rank):
+    """The box-scale request workload: 64 independent requests (a random 378x378 image = one crop, 32 random prompt
+    tokens, 200 greedy decode steps), request i on GPU i mod world, up to 8 requests of a GPU decoding together.
+    Every rank holds a full replica (random-init weights of the real shapes); no collective on the data path, the
+    token ids are gathered on the host at the end.  Host wall clock around the whole job, max over ranks."""
+    import importlib
+    import __graft_entry__ as entry
+    par = importlib.import_module(entry.PKG_NAME + ".parallel")
     g = torch.Generator(device="cuda").manual_seed(4000)
-    _, _, w, tm, embeds = build_text_model(ctx, torch, g)
-    _, dec = decode_config4(tm, embeds, sync=dist.barrier)
-    t = torch.tensor([dec], device="cuda", dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    models, n, w, tm, _ = build_text_model(ctx, torch, g)
+    vw, make_vm = build_vision_model(ctx, torch, g, n)
+    vm = make_vm(1)
+    n_req, n_steps = 64, 200
+    rng = np.random.default_rng(5100)
+    requests = [par.Request(rng.integers(0, 256, (1, 378, 378, 3), dtype=np.uint8), rng.integers(0, 51200, 32))
+                for _ in range(n_req)]
+    state = {}
+    par.serve_requests(ctx, vm, tm, requests[:2 * world * 8], world, rank, 8, state=state)      # warm-up: graphs, buffers
+    if dist is not None:
+        dist.barrier()
+    t0 = time.perf_counter()
+    mine = par.serve_requests(ctx, vm, tm, requests, world, rank, n_steps, state=state)
+    dt = time.perf_counter() - t0
+    if dist is not None:
+        t = torch.tensor([dt], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = t.item()
+    everything = par.gather_tokens(mine, n_req)
+    assert len(everything) == n_req and all(len(t) == n_steps + 1 for t in everything)
+    for r in state.get("reqs", []):
+        r.close()
     tm.close()
-    del w, tm
+    vm.close()
+    del w, vw, tm, vm, state
     torch.cuda.empty_cache()
-    return {"requests": world, "steps": 200, "prefill_rows": 761, "decode_tok_s_aggregate": round(world * 200 / t.item(), 1),
-            "decode_tok_s_per_gpu": round(200 / t.item(), 1),
-            "note": "one request per GPU, host wall clock around md_text_generate, max over ranks"}
+    return {"requests": n_req, "decode_steps": n_steps, "prefill_rows": 761, "crops_per_image": 1, "gpus": world,
+            "streams_per_gpu": 8, "seconds": round(dt, 3), "requests_per_s": round(n_req / dt, 2),
+            "decode_tok_s_aggregate": round(n_req * n_steps / dt, 1),
+            "note": "whole job: vision encode + 761-row prefill + 200 decode steps per request, images and prompts "
+                    "copied up from host memory, token ids gathered on the host; time = slowest rank"}
+
+
+def cpu_extras(oracle):
+    """The oracle (C++ restatement of the reference's AVX2 path) on this box's host cores next to the two other
+    headline quantities: the 64x2048 . 2048x8192 hgemm in TFLOP/s, and decode tokens/s.  Bounded samples."""
+    out = {"cores": oracle.get_threads(), "kind": "port"}
+    rng = np.random.default_rng(1000)
+    a = rng.standard_normal((64, 2048), dtype=np.float32).astype(np.float16)
+    wkn = (rng.standard_normal((2048, 8192), dtype=np.float32) * 0.02).astype(np.float16)
+    oracle.hgemm_nn(a, wkn)
+    best = min(_time(lambda: oracle.hgemm_nn(a, wkn)) for _ in range(5))
+    out["hgemm_64x2048x8192"] = {"us": round(best * 1e6, 1), "TFLOP/s": round(2.0 * 64 * 2048 * 8192 / best / 1e12, 4),
+                                 "sample": "best of 5 (the reference's own rule, hgemm.zig:446-542)"}
+
+    # one layer of each stage, scaled by the layer count; the decode steps run against the cache the 761-row
+    # prefill of that layer has just filled, i.e. at the request's own cache lengths 762, 763, ...
+    def n(*shape, std=0.02):
+        return (rng.standard_normal(shape, dtype=np.float32) * std).astype(np.float16)
+    D, F, V = 2048, 8192, 51200
+    one, zero = np.ones(D, np.float16), np.zeros(D, np.float16)
+    tw = {"ln_w": [one], "ln_b": [zero], "wqkv": [n(3 * D, D)], "bqkv": [n(3 * D)], "wout": [n(D, D)], "bout": [n(D)],
+          "wfc1": [n(F, D)], "bfc1": [n(F)], "wfc2": [n(D, F)], "bfc2": [n(D)], "ln_out_w": one, "ln_out_b": zero,
+          "lm_w": n(V, D), "lm_b": n(V), "wte": n(V, D)}
+    tm = oracle.TextModel(tw)
+    embeds = n(761, D, std=1.0)
+    t_prefill_layer = _time(lambda: tm.decoder(embeds))
+    steps = 3
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        h = tm.decoder(tm.embed([1]))
+    t_layer_step = (time.perf_counter() - t0) / steps
+    t_head = _time(lambda: tm.lm_head(h))
+    t_step = 24 * t_layer_step + t_head
+    Dv, Fv = 1152, 4304
+    onev, zerov = np.ones(Dv, np.float16), np.zeros(Dv, np.float16)
+    vw = {"ln1_w": [onev], "ln1_b": [zerov], "ln2_w": [onev], "ln2_b": [zerov], "wqkv": [n(Dv, 3 * Dv)],
+          "bqkv": [n(3 * Dv)], "wout": [n(Dv, Dv)], "bout": [n(Dv)], "wfc1": [n(Dv, Fv)], "bfc1": [n(Fv)],
+          "wfc2": [n(Fv, Dv)], "bfc2": [n(Dv)], "patch_w": n(588, Dv), "patch_b": n(Dv), "pos_emb": n(729, Dv),
+          "norm_w": onev, "norm_b": zerov, "proj_fc1_w": n(2 * Dv, 8192), "proj_fc1_b": n(8192),
+          "proj_fc2_w": n(8192, 2048), "proj_fc2_b": n(2048)}
+    vm = oracle.VisionModel(vw)
+    patches = n(1, 729, 588, std=1.0)
+    t_vis_layer = _time(lambda: vm.encoder(patches))
+    f = n(729, Dv, std=1.0)
+    t_proj = _time(lambda: vm.projection(f, f))
+    per_request = 27 * t_vis_layer + t_proj + 24 * t_prefill_layer + t_head + 200 * t_step
+    out["decode"] = {"tok_s": round(1.0 / t_step, 3), "ms_per_token": round(t_step * 1e3, 1),
+                     "sample": f"{steps} decode steps of one layer at cache length 762.. x 24 layers + one lm_head"}
+    out["request_extrapolated"] = {
+        "seconds_per_request": round(per_request, 1), "decode_tok_s": round(1.0 / t_step, 3),
+        "vision_s": round(27 * t_vis_layer + t_proj, 2), "prefill_s": round(24 * t_prefill_layer + t_head, 2),
+        "decode_s": round(200 * t_step, 1),
+        "sample": "one ViT layer x 27 + projection, one decoder layer over 761 rows x 24, 200 x the decode step above; "
+                  "64 requests = 64 x this on one host (extrapolated, not run)"}
+    return out
+
+
+def _time(fn):
+    t0 = time.perf_counter()
+    fn()
+    return time.perf_counter() - t0
 
 
 def model_extras(ctx, torch):
@@ -577,18 +759,10 @@ def model_extras(ctx, torch):
     del w, tm
     torch.cuda.empty_cache()
 
-    Lv, Dv, Fv = 27, 1152, 4304
-    onev, zerov = torch.ones(Dv, device="cuda").half(), torch.zeros(Dv, device="cuda").half()
-    vw = {"ln1_w": [onev] * Lv, "ln1_b": [zerov] * Lv, "ln2_w": [onev] * Lv, "ln2_b": [zerov] * Lv,
-          "wqkv": [n(Dv, 3 * Dv) for _ in range(Lv)], "bqkv": [n(3 * Dv) for _ in range(Lv)],
-          "wout": [n(Dv, Dv) for _ in range(Lv)], "bout": [n(Dv) for _ in range(Lv)],
-          "wfc1": [n(Dv, Fv) for _ in range(Lv)], "bfc1": [n(Fv) for _ in range(Lv)],
-          "wfc2": [n(Fv, Dv) for _ in range(Lv)], "bfc2": [n(Dv) for _ in range(Lv)],
-          "patch_w": n(588, Dv), "patch_b": n(Dv), "pos_emb": n(729, Dv), "norm_w": onev, "norm_b": zerov,
-          "proj_fc1_w": n(2 * Dv, 8192), "proj_fc1_b": n(8192), "proj_fc2_w": n(8192, 2048), "proj_fc2_b": n(2048)}
+    vw, make_vm = build_vision_model(ctx, torch, g, n)
     out["vision_config3"] = []
     for crops in (1, 5, 13):
-        vm = models.VisionModel(ctx, vw, max_crops=crops)
+        vm = make_vm(crops)
         img = np.random.default_rng(crops).integers(0, 256, (crops, 378, 378, 3), dtype=np.uint8)
         for _ in range(4):
             t0 = time.perf_counter()

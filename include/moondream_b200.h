@@ -47,7 +47,8 @@ typedef enum md_status {
     MD_ERR_TIMEOUT = 9,          /* a bounded device-side wait gave up; results are invalid */
     MD_ERR_NO_DEVICE = 10,
     MD_ERR_IO = 11,              /* a file could not be opened, mapped or read to its stated length (error.InvalidRead) */
-    MD_ERR_FORMAT = 12           /* a weight file that is not what weights.zig accepts; md_last_error names the Zig error */
+    MD_ERR_FORMAT = 12,          /* a weight file that is not what weights.zig accepts; md_last_error names the Zig error */
+    MD_ERR_NCCL = 13             /* NCCL is missing or one of its calls failed (column-split GEMM across GPUs only) */
 } md_status;
 
 typedef struct md_ctx md_ctx;
@@ -169,6 +170,38 @@ int md_hgemm_colsplit_push(md_ctx* ctx, const uint16_t* a, const uint16_t* b_sli
 /* The re-layout step of the all-gather baseline: gathered [world][M][N_local] (what an all-gather of the
  * ranks' contiguous blocks produces) -> c [M][world * N_local].  Device pointers. */
 int md_gather_colblocks(md_ctx* ctx, const uint16_t* gathered, uint16_t* c, size_t world, size_t M, size_t N_local);
+
+/* ---- the exchange step for hosts that run one process per GPU -----------------------------------
+ * The reference has no distributed code (hgemm.zig:396-423 spawns threads only), so nothing here replaces a
+ * reference function; the arithmetic per column block is md_hgemm_nn / md_hgemm_nt.  A communicator binds a
+ * context to `world` <= 8 ranks of one box.  NCCL is looked up at run time (libnccl.so.2): a process that
+ * already carries one shares it, a machine without it gets MD_ERR_NCCL from md_comm_unique_id / md_comm_init.
+ * Every call below except md_comm_unique_id is collective: all ranks make it, in the same order. */
+#define MD_COMM_ID_BYTES 128
+typedef struct md_comm md_comm;
+/* Rank 0 creates the id (ncclGetUniqueId) and hands the 128 bytes to the other ranks by any means. */
+int md_comm_unique_id(md_ctx* ctx, void* id_out);
+/* ncclCommInitRank on the context's device + a small peer-mapped signal pad for md_comm_barrier. */
+int md_comm_init(md_ctx* ctx, const void* unique_id, int rank, int world, md_comm** out);
+int md_comm_destroy(md_comm* comm);
+/* A zeroed device buffer of `bytes` on every rank, mapped into every other rank (CUDA IPC handles all-gathered
+ * over the communicator), so that this library's kernels can store into the peers' copies over NVLink. */
+int md_comm_symm_alloc(md_comm* comm, size_t bytes, void** local_out);
+int md_comm_symm_free(md_comm* comm, void* local);
+/* Stream-ordered barrier across the ranks' GPUs: one small kernel per rank, no host round trip.  A peer that
+ * does not arrive within two seconds makes the next md_sync return MD_ERR_TIMEOUT (site 200 + peer rank). */
+int md_comm_barrier(md_comm* comm);
+/* C[M, N_total] = A[M,K] . B with N split evenly over the ranks (N_total / world a multiple of 8); b_slice is
+ * this rank's slice, [K, N_total/world] (b_layout 0) or [N_total/world, K] (b_layout 1); every rank ends up with
+ * the whole C.  Device pointers only.
+ *   _allgather  the baseline: GEMM into a contiguous block, ncclAllGather of the blocks, one re-layout kernel.
+ *   _fused      md_hgemm_colsplit_push between two md_comm barriers: the GEMM kernel's push warps store every
+ *               finished tile into all ranks' C while the following tiles are computed; c_symm must come from
+ *               md_comm_symm_alloc (at least M * N_total * 2 bytes).  No collective and no re-layout runs. */
+int md_hgemm_colsplit_allgather(md_comm* comm, const uint16_t* a, const uint16_t* b_slice, uint16_t* c_full, size_t M,
+                                size_t N_total, size_t K, int b_layout);
+int md_hgemm_colsplit_fused(md_comm* comm, const uint16_t* a, const uint16_t* b_slice, uint16_t* c_symm, size_t M,
+                            size_t N_total, size_t K, int b_layout);
 
 /* ---- attention ----------------------------------------------------------------- */
 

@@ -83,6 +83,11 @@ int md_text_generate(md_text_model* model, md_text_request* req, uint32_t first,
  *   first [batch], tokens_out [batch, n_steps] (host). */
 int md_text_generate_batch(md_text_model* model, md_text_request* const* reqs, size_t batch, const uint32_t* first,
                            size_t n_steps, uint32_t* tokens_out);
+/* The batched loop under teacher forcing: forced host u32 [batch, n_steps], request b consumes forced[b][i-1] at
+ * step i instead of its own previous output (step 0 consumes first[b]); tokens_out still holds what every step
+ * produced.  For parity checks of batched decoding against a reference that generated the forced tokens. */
+int md_text_generate_batch_forced(md_text_model* model, md_text_request* const* reqs, size_t batch, const uint32_t* first,
+                                  size_t n_steps, uint32_t* tokens_out, const uint32_t* forced);
 
 /* ---- vision encoder (SigLIP-style ViT, vision_model.zig) --------------------------------- */
 

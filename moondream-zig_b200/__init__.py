@@ -26,6 +26,7 @@ STATUS_NAMES = {
     0: "MD_OK", 1: "MD_ERR_INVALID_ARG", 2: "MD_ERR_INVALID_DIMENSION", 3: "MD_ERR_SHAPE",
     4: "MD_ERR_SEQUENCE_TOO_LONG", 5: "MD_ERR_INVALID_ROT_DIM", 6: "MD_ERR_UNSUPPORTED", 7: "MD_ERR_OOM",
     8: "MD_ERR_CUDA", 9: "MD_ERR_TIMEOUT", 10: "MD_ERR_NO_DEVICE", 11: "MD_ERR_IO", 12: "MD_ERR_FORMAT",
+    13: "MD_ERR_NCCL",
 }
 # the Zig error each status maps back to in the shim
 ZIG_ERRORS = {

@@ -491,6 +491,8 @@ int md_gather_colblocks(md_ctx* ctx, const uint16_t* gathered, uint16_t* c, size
     MD_NEED_CTX(ctx);
     MD_NEED(ctx, gathered && c, "gather_colblocks: null pointer");
     if (!world || !M || !N_local) return MD_OK;
+    if ((N_local % 8) == 0 && ((reinterpret_cast<uintptr_t>(gathered) | reinterpret_cast<uintptr_t>(c)) & 15) == 0)
+        return md_launch_gather_colblocks(ctx, gathered, c, world, M, N_local);  // one kernel, 16 bytes per thread
     // block g is a contiguous [M, N_local] matrix: one strided 2-D copy per block
     for (size_t g = 0; g < world; ++g)
         MD_CUDA(ctx, cudaMemcpy2DAsync(c + g * N_local, world * N_local * 2, gathered + g * M * N_local, N_local * 2,

@@ -204,6 +204,9 @@ int md_launch_gemm_tc(md_ctx* ctx, const __half* a, const __half* b, __half* c, 
 int md_launch_gemm_tc_ex(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
                          int b_layout, const md_epilogue& ep, size_t ldc, const md_push& push);
 
+// comm.cu: gathered [world][M][n_local] -> c [M][world * n_local] (n_local % 8 == 0, 16-byte aligned)
+int md_launch_gather_colblocks(md_ctx* ctx, const uint16_t* gathered, uint16_t* c, size_t world, size_t M, size_t n_local);
+
 // gemm_tc.cu: a kernel whose bounded wait runs out on purpose (md_selftest_bounded_wait)
 int md_launch_selftest_wait(md_ctx* ctx, unsigned limit_ms);
 

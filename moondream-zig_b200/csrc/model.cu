@@ -727,6 +727,12 @@ int md_text_generate_batch(md_text_model* model, md_text_request* const* reqs, s
     return generate_impl(model, reqs, batch, first, n_steps, tokens_out, nullptr, nullptr);
 }
 
+int md_text_generate_batch_forced(md_text_model* model, md_text_request* const* reqs, size_t batch, const uint32_t* first,
+                                  size_t n_steps, uint32_t* tokens_out, const uint32_t* forced) {
+    if (!model || !reqs) return MD_ERR_INVALID_ARG;
+    return generate_impl(model, reqs, batch, first, n_steps, tokens_out, forced, nullptr);
+}
+
 }  // extern "C"
 
 // ------------------------------------------------------------------------------------ vision

@@ -116,23 +116,27 @@ class TextModel:
     def request(self) -> TextRequest:
         return TextRequest(self)
 
-    def text_encoder(self, ids) -> np.ndarray:
-        """text_model.zig:106-137."""
+    def text_encoder(self, ids, out_ptr: int | None = None):
+        """text_model.zig:106-137.  With out_ptr (a device address) the rows are written there and nothing is returned."""
         ids = np.ascontiguousarray(ids, np.uint32)
-        out = np.empty((ids.size, self.dim), np.float16)
+        out = np.empty((ids.size, self.dim), np.float16) if out_ptr is None else None
         self.ctx._check(self.lib.md_text_encoder(self.h, C.c_void_p(ids.ctypes.data), _sz(ids.size),
-                                                 C.c_void_p(out.ctypes.data)))
+                                                 C.c_void_p(out.ctypes.data if out_ptr is None else out_ptr)))
         return out
 
-    def forward(self, req: TextRequest, embeds: np.ndarray, want_hidden=True, want_logits=True):
-        """text_decoder + lm_head + argmax over S rows (text_model.zig:139-180,325-345)."""
-        embeds = np.ascontiguousarray(embeds, np.float16)
-        S = embeds.shape[0]
+    def forward(self, req: TextRequest, embeds, want_hidden=True, want_logits=True, rows: int | None = None):
+        """text_decoder + lm_head + argmax over S rows (text_model.zig:139-180,325-345).  embeds: a numpy array
+        [S, dim], or a device address together with rows=S."""
+        if isinstance(embeds, np.ndarray):
+            embeds = np.ascontiguousarray(embeds, np.float16)
+            S, src = embeds.shape[0], embeds.ctypes.data
+        else:
+            S, src = int(rows), int(embeds)
         hidden = np.empty((S, self.dim), np.float16) if want_hidden else None
         logits = np.empty((self.vocab,), np.float16) if want_logits else None
         tok = np.zeros(1, np.uint64)
         self.ctx._check(self.lib.md_text_forward(
-            self.h, req.h, C.c_void_p(embeds.ctypes.data), _sz(S),
+            self.h, req.h, C.c_void_p(src), _sz(S),
             C.c_void_p(hidden.ctypes.data if want_hidden else 0), C.c_void_p(logits.ctypes.data if want_logits else 0),
             C.c_void_p(tok.ctypes.data)))
         return hidden, logits, int(tok[0])
@@ -147,13 +151,21 @@ class TextModel:
             C.c_void_p(f.ctypes.data if f is not None else 0), C.c_void_p(logits.ctypes.data if want_logits else 0)))
         return (toks, logits) if want_logits else toks
 
-    def generate_batch(self, reqs, first, n_steps: int) -> np.ndarray:
+    def generate_batch(self, reqs, first, n_steps: int, forced=None) -> np.ndarray:
+        """Up to 8 requests advanced together; forced [batch, n_steps] = teacher forcing per request."""
         B = len(reqs)
         arr = (C.c_void_p * B)(*[r.h.value for r in reqs])
         f = np.ascontiguousarray(first, np.uint32)
         toks = np.zeros((B, n_steps), np.uint32)
-        self.ctx._check(self.lib.md_text_generate_batch(self.h, arr, _sz(B), C.c_void_p(f.ctypes.data), _sz(n_steps),
-                                                        C.c_void_p(toks.ctypes.data)))
+        if forced is None:
+            self.ctx._check(self.lib.md_text_generate_batch(self.h, arr, _sz(B), C.c_void_p(f.ctypes.data),
+                                                            _sz(n_steps), C.c_void_p(toks.ctypes.data)))
+        else:
+            fo = np.ascontiguousarray(forced, np.uint32)
+            assert fo.shape == (B, n_steps)
+            self.ctx._check(self.lib.md_text_generate_batch_forced(self.h, arr, _sz(B), C.c_void_p(f.ctypes.data),
+                                                                   _sz(n_steps), C.c_void_p(toks.ctypes.data),
+                                                                   C.c_void_p(fo.ctypes.data)))
         return toks
 
     def close(self):
@@ -202,16 +214,18 @@ class VisionModel:
         self._create(table, max_crops)
         return self
 
-    def encode(self, crops_u8: np.ndarray, crop_a: int = 0, crop_b: int | None = None, want_features: bool = False):
-        """vision_model.zig:160-202 without the file decode. crops uint8 [c, img, img, 3]."""
+    def encode(self, crops_u8: np.ndarray, crop_a: int = 0, crop_b: int | None = None, want_features: bool = False,
+               out_ptr: int | None = None):
+        """vision_model.zig:160-202 without the file decode. crops uint8 [c, img, img, 3].  With out_ptr (a device
+        address) the [tokens, proj_out] result stays on the device and nothing is returned."""
         crops_u8 = np.ascontiguousarray(crops_u8, np.uint8)
         c = crops_u8.shape[0]
         crop_b = min(1, c - 1) if crop_b is None else crop_b
         feats = np.empty((c * self.tokens, self.dim), np.float16) if want_features else None
-        out = np.empty((self.tokens, self.proj_out), np.float16)
+        out = np.empty((self.tokens, self.proj_out), np.float16) if out_ptr is None else None
         self.ctx._check(self.lib.md_vision_encode(self.h, C.c_void_p(crops_u8.ctypes.data), _sz(c), _sz(crop_a),
                                                   _sz(crop_b), C.c_void_p(feats.ctypes.data if want_features else 0),
-                                                  C.c_void_p(out.ctypes.data)))
+                                                  C.c_void_p(out.ctypes.data if out_ptr is None else out_ptr)))
         return (out, feats) if want_features else out
 
     def close(self):

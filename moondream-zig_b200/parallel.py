@@ -1,23 +1,29 @@
-"""Multi-GPU plumbing for the hot path: one process per GPU, torch.distributed for rendezvous.
+"""Multi-GPU plumbing for the hot path: one process per GPU, torch.distributed for rendezvous only.
 
 Two things shard (the reference has no distributed code at all, so the split is this library's):
 
 * independent requests -> replicas.  Every GPU holds the full weights; request i runs on GPU
-  i mod world.  No collective on the data path (``partition_requests``).
+  i mod world (``partition_requests``).  ``serve_requests`` runs a rank's share of a list of
+  requests — vision encode, 761-row prefill, greedy decode, the chain of moondream.zig:240-368 —
+  with up to 8 requests decoding together as M <= 8 GEMVs; ``gather_tokens`` collects the token
+  ids of all ranks on the host.  No collective on the data path.
 * the column-split large GEMM -> one exchange step.  C[M,N] = A . B with N split over the ranks:
   rank r computes columns [r*N/world, (r+1)*N/world) from the full A and its slice of B, then every
-  rank needs the whole C.
-    - ``ColSplitGemm(mode="allgather")``: tcgen05 GEMM into a contiguous [M, N/world] block,
-      NCCL all-gather of the blocks, strided re-layout into [M, N] (md_gather_colblocks).
-    - ``ColSplitGemm(mode="fused")``: the GEMM epilogue stores each finished chunk into every rank's
-      C through peer-mapped symmetric memory (md_hgemm_colsplit_push), then one cross-rank barrier;
-      the transfer overlaps the math tile by tile and no separate collective or re-layout runs.
+  rank needs the whole C.  ``Comm`` wraps the library's communicator (md_comm_*: NCCL from a unique
+  id, peer-mapped buffers, a device-side barrier); ``ColSplitGemm`` runs either form:
+    - mode="allgather": tcgen05 GEMM into a contiguous [M, N/world] block, ncclAllGather, one
+      re-layout kernel (md_hgemm_colsplit_allgather);
+    - mode="fused": the GEMM's push warps store each finished tile into every rank's C over NVLink
+      between two device-side barriers (md_hgemm_colsplit_fused); no collective, no re-layout.
 """
 from __future__ import annotations
 
 import ctypes as C
 
+import numpy as np
+
 _sz = C.c_size_t
+COMM_ID_BYTES = 128
 
 
 def partition_requests(n_requests: int, world: int, rank: int) -> list[int]:
@@ -46,10 +52,10 @@ def slice_b(b, b_layout: int, world: int, rank: int):
 
 
 def allgather_column_blocks(local_block, group=None, relayout=None):
-    """All-gather the ranks' [M, N/world] blocks and lay them out as [M, N].
+    """All-gather the ranks' [M, N/world] blocks and lay them out as [M, N] with torch.distributed.
 
-    `relayout(gathered [world, M, n]) -> [M, world*n]` defaults to a torch permute; the GPU path passes a
-    function that calls md_gather_colblocks.  Works on any backend (the CPU tests run it under gloo)."""
+    The host-side statement of what md_hgemm_colsplit_allgather does after its GEMM; works on any backend (the
+    CPU tests run it under gloo).  `relayout(gathered [world, M, n]) -> [M, world*n]` defaults to a permute."""
     import torch
     import torch.distributed as dist
     world = dist.get_world_size(group)
@@ -61,47 +67,162 @@ def allgather_column_blocks(local_block, group=None, relayout=None):
     return gathered.permute(1, 0, 2).reshape(m, world * n).contiguous()
 
 
-class ColSplitGemm:
-    """C[M,N] = A[M,K] . B (column-split over the ranks of `group`), result replicated on every rank."""
+def share_unique_id(make_id, group=None) -> bytes:
+    """Rank 0 calls make_id() (128 bytes); every rank of the torch.distributed group gets them."""
+    import torch.distributed as dist
+    box = [make_id() if dist.get_rank(group) == 0 else None]
+    dist.broadcast_object_list(box, src=0, group=group)
+    if not isinstance(box[0], (bytes, bytearray)) or len(box[0]) != COMM_ID_BYTES:
+        raise RuntimeError("the communicator id did not arrive")
+    return bytes(box[0])
 
-    def __init__(self, ctx, M: int, N: int, K: int, b_layout: int, mode: str = "fused", group=None):
-        import torch
+
+class Comm:
+    """md_comm: the library's communicator over the ranks of a torch.distributed group (used for rendezvous only:
+    rank 0's NCCL unique id is broadcast as a Python object, everything after that is the library's own)."""
+
+    def __init__(self, ctx, group=None):
         import torch.distributed as dist
-        assert mode in ("fused", "allgather")
-        self.ctx, self.M, self.N, self.K, self.b_layout, self.mode, self.group = ctx, M, N, K, b_layout, mode, group
+        self.ctx, self.lib = ctx, ctx.lib
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        self.off, self.width = column_block(N, self.world, self.rank)
+
+        def make_id():
+            buf = C.create_string_buffer(COMM_ID_BYTES)
+            ctx._check(self.lib.md_comm_unique_id(ctx.h, buf))
+            return buf.raw
+
+        uid = share_unique_id(make_id, group) if self.world > 1 else bytes(COMM_ID_BYTES)
+        h = C.c_void_p()
+        ctx._check(self.lib.md_comm_init(ctx.h, C.c_char_p(uid), C.c_int(self.rank), C.c_int(self.world), C.byref(h)))
+        self.h = h
+
+    def symm_alloc(self, nbytes: int) -> int:
+        p = C.c_void_p()
+        self.ctx._check(self.lib.md_comm_symm_alloc(self.h, _sz(nbytes), C.byref(p)))
+        return int(p.value)
+
+    def symm_free(self, ptr: int):
+        self.ctx._check(self.lib.md_comm_symm_free(self.h, C.c_void_p(ptr)))
+
+    def barrier(self):
+        self.ctx._check(self.lib.md_comm_barrier(self.h))
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.md_comm_destroy(self.h)
+            self.h = None
+
+
+class ColSplitGemm:
+    """C[M,N] = A[M,K] . B (column-split over the ranks of `comm`), result replicated on every rank."""
+
+    def __init__(self, comm: Comm, M: int, N: int, K: int, b_layout: int, mode: str = "fused"):
+        import torch
+        assert mode in ("fused", "allgather")
+        self.comm, self.ctx = comm, comm.ctx
+        self.M, self.N, self.K, self.b_layout, self.mode = M, N, K, b_layout, mode
+        self.off, self.width = column_block(N, comm.world, comm.rank)
         dev = torch.device("cuda", torch.cuda.current_device())
+        self.symm = None
         if mode == "fused":
-            import torch.distributed._symmetric_memory as symm
-            self.c = symm.empty((M, N), dtype=torch.float16, device=dev)
-            self.hdl = symm.rendezvous(self.c, group if group is not None else dist.group.WORLD)
-            peers = [int(p) for i, p in enumerate(self.hdl.buffer_ptrs) if i != self.rank]
-            self.peer_arr = (C.c_void_p * max(len(peers), 1))(*peers)
-            self.n_peers = len(peers)
+            self.symm = comm.symm_alloc(M * N * 2)
+            self.c_ptr = self.symm
         else:
             self.c = torch.empty((M, N), dtype=torch.float16, device=dev)
-            self.block = torch.empty((M, self.width), dtype=torch.float16, device=dev)
-            self.gathered = torch.empty((self.world, M, self.width), dtype=torch.float16, device=dev)
+            self.c_ptr = self.c.data_ptr()
 
-    def __call__(self, a, b_slice):
-        """a [M,K] and this rank's slice of B (see slice_b), torch f16 CUDA tensors. Returns C [M,N]
-        (valid on the current stream once the call returns)."""
-        import torch.distributed as dist
-        ctx = self.ctx
-        if self.mode == "fused":
-            self.hdl.barrier(channel=0)   # nobody still reads the previous C
-            ctx._check(ctx.lib.md_hgemm_colsplit_push(
-                ctx.h, C.c_void_p(a.data_ptr()), C.c_void_p(b_slice.data_ptr()), C.c_void_p(self.c.data_ptr()),
-                _sz(self.M), _sz(self.width), _sz(self.K), C.c_int(self.b_layout), _sz(self.N), _sz(self.off),
-                _sz(self.n_peers), self.peer_arr))
-            self.hdl.barrier(channel=1)   # every rank's pushes have landed
-            return self.c
-        call = ctx.lib.md_hgemm_nn if self.b_layout == 0 else ctx.lib.md_hgemm_nt
-        ctx._check(call(ctx.h, C.c_void_p(a.data_ptr()), C.c_void_p(b_slice.data_ptr()),
-                        C.c_void_p(self.block.data_ptr()), _sz(self.M), _sz(self.width), _sz(self.K)))
-        dist.all_gather_into_tensor(self.gathered, self.block, group=self.group)
-        ctx._check(ctx.lib.md_gather_colblocks(ctx.h, C.c_void_p(self.gathered.data_ptr()),
-                                               C.c_void_p(self.c.data_ptr()), _sz(self.world), _sz(self.M),
-                                               _sz(self.width)))
-        return self.c
+    def __call__(self, a, b_slice) -> int:
+        """a [M,K] and this rank's slice of B (see slice_b), torch f16 CUDA tensors.  Returns the device address of
+        C [M,N] (valid on the context's stream once the call returns)."""
+        fn = self.ctx.lib.md_hgemm_colsplit_fused if self.mode == "fused" else self.ctx.lib.md_hgemm_colsplit_allgather
+        self.ctx._check(fn(self.comm.h, C.c_void_p(a.data_ptr()), C.c_void_p(b_slice.data_ptr()), C.c_void_p(self.c_ptr),
+                           _sz(self.M), _sz(self.N), _sz(self.K), C.c_int(self.b_layout)))
+        return self.c_ptr
+
+    def result(self):
+        """C as a numpy array (waits for the stream)."""
+        out = np.empty((self.M, self.N), np.float16)
+        self.ctx._check(self.ctx.lib.md_memcpy_d2h(self.ctx.h, C.c_void_p(out.ctypes.data), C.c_void_p(self.c_ptr),
+                                                   _sz(out.nbytes)))
+        return out
+
+    def close(self):
+        if self.symm:
+            self.comm.symm_free(self.symm)
+            self.symm = None
+
+
+# ----------------------------------------------------------------------------- independent requests
+
+class Request:
+    """One request of the box-scale workload: the crops of an image and the prompt's token ids."""
+
+    def __init__(self, crops_u8: np.ndarray, prompt_ids):
+        self.crops = np.ascontiguousarray(crops_u8, np.uint8)
+        self.ids = np.ascontiguousarray(prompt_ids, np.uint32)
+        assert self.crops.ndim == 4 and self.ids.size >= 1
+
+
+def serve_requests(ctx, vision, text, requests: list, world: int, rank: int, n_steps: int, max_streams: int = 8,
+                   forced: dict | None = None, state: dict | None = None) -> dict:
+    """Run this rank's share of `requests` (request i -> rank i mod world) and return {index: tokens}.
+
+    Per request, the chain of moondream.zig:240-368 with everything between the image and the token ids resident on
+    the device: vision encode -> [embed(tok0), 729 image rows, embed(tok1..)] (moondream.zig:286-303) -> prefill ->
+    first token -> n_steps greedy decode steps.  Up to `max_streams` (<= 8) requests decode together as M <= 8 GEMVs
+    (md_text_generate_batch).  tokens = [first token, then the n_steps generated tokens].
+    forced: {index: uint32 [n_steps]} feeds those tokens instead of the model's own (teacher forcing, for parity
+    checks).  state: a dict reused across calls to keep the KV caches and buffers (8 x 384 MiB at full size)."""
+    assert 1 <= max_streams <= 8
+    mine = partition_requests(len(requests), world, rank)
+    state = state if state is not None else {}
+    reqs = state.setdefault("reqs", [])
+    while len(reqs) < min(max_streams, len(mine)):
+        reqs.append(text.request())
+    dim, tokens = text.dim, vision.tokens
+    assert vision.proj_out == dim
+    out: dict = {}
+    for g0 in range(0, len(mine), max_streams):
+        group = mine[g0:g0 + max_streams]
+        firsts = []
+        for slot, idx in enumerate(group):
+            rq = requests[idx]
+            rows = rq.ids.size + tokens
+            if state.get("embeds_rows", 0) < rows:
+                state["embeds"] = ctx.alloc((rows, dim))
+                state["embeds_rows"] = rows
+            base = state["embeds"].ptr
+            text.text_encoder(rq.ids[:1], out_ptr=base)
+            vision.encode(rq.crops, out_ptr=base + dim * 2)
+            if rq.ids.size > 1:
+                text.text_encoder(rq.ids[1:], out_ptr=base + (1 + tokens) * dim * 2)
+            reqs[slot].reset()
+            _, _, tok = text.forward(reqs[slot], base, want_hidden=False, want_logits=False, rows=rows)
+            firsts.append(tok)
+        f = None
+        if forced is not None:
+            f = np.stack([np.ascontiguousarray(forced[idx], np.uint32) for idx in group])
+        toks = text.generate_batch(reqs[:len(group)], firsts, n_steps, forced=f)
+        for slot, idx in enumerate(group):
+            out[idx] = np.concatenate([np.array([firsts[slot]], np.uint32), toks[slot]])
+    return out
+
+
+def gather_tokens(local: dict, n_requests: int, group=None) -> list:
+    """Every rank's {index: tokens} -> the list of all requests' tokens, on every rank (host-side gather; works on
+    any torch.distributed backend, or without one when the process is alone)."""
+    import torch.distributed as dist
+    parts = [local]
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        parts = [None] * dist.get_world_size(group)
+        dist.all_gather_object(parts, {int(k): np.asarray(v) for k, v in local.items()}, group=group)
+    merged: dict = {}
+    for p in parts:
+        for k, v in p.items():
+            if k in merged:
+                raise RuntimeError(f"request {k} was served twice")
+            merged[k] = v
+    missing = [i for i in range(n_requests) if i not in merged]
+    if missing:
+        raise RuntimeError(f"requests {missing} were not served")
+    return [merged[i] for i in range(n_requests)]

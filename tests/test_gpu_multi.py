@@ -1,4 +1,5 @@
-"""2-GPU test of the column-split GEMM + exchange (skipped on a single-GPU box)."""
+"""2-GPU test of the column-split GEMM + exchange through the library's communicator, and of requests partitioned
+over the ranks (skipped on a single-GPU box)."""
 import os
 import subprocess
 import sys

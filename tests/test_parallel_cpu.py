@@ -43,6 +43,14 @@ def test_column_block():
     assert torch.equal(p.slice_b(b.T.contiguous(), 1, 2, 1), b.T[16:, :])
 
 
+def test_gather_tokens_single_process():
+    p = par()
+    toks = p.gather_tokens({1: np.array([5, 6]), 0: np.array([7])}, 2)
+    assert [t.tolist() for t in toks] == [[7], [5, 6]]
+    with pytest.raises(RuntimeError):
+        p.gather_tokens({0: np.array([1])}, 2)
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -75,6 +83,18 @@ def _worker(rank, world, port, out_dir):
     gathered = [None] * world
     dist.all_gather_object(gathered, mine)
     assert sorted(sum(gathered, [])) == list(range(7))
+    # the host-side gather of the served requests' token ids: every rank ends up with all 7, in request order
+    local = {i: np.arange(4, dtype=np.uint32) + 10 * i for i in mine}
+    everything = p.gather_tokens(local, 7)
+    assert len(everything) == 7 and all(np.array_equal(everything[i], np.arange(4) + 10 * i) for i in range(7))
+    try:
+        p.gather_tokens(local, 8)                       # request 7 was never served
+        raise AssertionError("a missing request must be reported")
+    except RuntimeError as e:
+        assert "not served" in str(e)
+    # the communicator id travels as a Python object from rank 0
+    uid = p.share_unique_id(lambda: bytes(range(128)))
+    assert uid == bytes(range(128))
     dist.barrier()
     dist.destroy_process_group()
     open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
