@@ -323,6 +323,12 @@ int md_set_option(md_ctx* ctx, const char* key, long value) {
     if (!strcmp(key, "decode_fork")) { ctx->decode_fork = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "persist_trace")) { ctx->persist_trace = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "persistent_decode")) { ctx->persistent_decode = value ? 1 : 0; return MD_OK; }
+    if (!strcmp(key, "skinny")) { ctx->skinny = value ? 1 : 0; return MD_OK; }
+    if (!strcmp(key, "skinny_splits")) {
+        MD_NEED(ctx, value >= 0 && value <= 16, "skinny_splits must be 0 (automatic) or 1..16 (rounded down to 1, 2, 4 or 8)");
+        ctx->skinny_splits = (int)value;
+        return MD_OK;
+    }
     if (!strcmp(key, "attn_tc")) { ctx->attn_tc = value < 0 ? -1 : value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "tc_block_n")) {
         MD_NEED(ctx, value == 0 || value == 64 || value == 128 || value == 256 || value == 512,
@@ -418,6 +424,8 @@ int md_gemm_dispatch(md_ctx* ctx, const __half* a, const __half* b, __half* c, s
     const bool aligned16 = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0;
     if (ctx->gemm_mode != 1 && b_layout == 1 && M <= 8 && (K % 8) == 0 && aligned16 && ctx->gemm_mode != 2)
         return md_launch_gemv_nt(ctx, a, b, c, M, N, K, ep);
+    if (ctx->gemm_mode == 0 && ctx->skinny && md_gemm_skinny_supported(a, b, c, M, N, K))
+        return md_launch_gemm_skinny(ctx, a, b, c, M, N, K, b_layout, ep);
     const bool tc_ok = md_gemm_tc_supported(a, b, c, M, N, K, b_layout);
     if (ctx->gemm_mode == 2 && !tc_ok)
         return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 GEMM forced but the shape/alignment does not allow it");

@@ -64,6 +64,8 @@ struct md_ctx {
     // cuTensorMapEncodeTiled resolved through the runtime (no link against libcuda)
     void* encode_tiled = nullptr;
     uint32_t tc_configured = 0;  // tcgen05 kernels whose dynamic shared memory limit has been raised
+    int skinny = 1;          // md_set_option("skinny"): 8 < M <= 64 takes the swapped-operand split-K kernel
+    int skinny_splits = 0;   // md_set_option("skinny_splits"): 0 = automatic, else the number of K splits (tests)
     bool sdpa_mma_configured = false;  // the same for the mma.sync attention kernels
     // (cos, sin) table shared by the fused attention calls: [rope_rows][rope_dim/2][2] f32
     float* rope_tab = nullptr;
@@ -206,6 +208,11 @@ int md_launch_gemm_tc_ex(md_ctx* ctx, const __half* a, const __half* b, __half* 
 
 // comm.cu: gathered [world][M][n_local] -> c [M][world * n_local] (n_local % 8 == 0, 16-byte aligned)
 int md_launch_gather_colblocks(md_ctx* ctx, const uint16_t* gathered, uint16_t* c, size_t world, size_t M, size_t n_local);
+
+// gemm_skinny.cu: 8 < M <= 64, weights as the MMA's M side, split-K over a thread-block cluster
+bool md_gemm_skinny_supported(const void* a, const void* b, const void* c, size_t M, size_t N, size_t K);
+int md_launch_gemm_skinny(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
+                          int b_layout, const md_epilogue& ep);
 
 // gemm_tc.cu: a kernel whose bounded wait runs out on purpose (md_selftest_bounded_wait)
 int md_launch_selftest_wait(md_ctx* ctx, unsigned limit_ms);

@@ -218,6 +218,47 @@ def test_tile_256x256(ctx, oracle, m, k, n, layout):
         b.free()
 
 
+@pytest.mark.parametrize("layout", [0, 1])
+@pytest.mark.parametrize("splits", [0, 1, 3, 16])
+@pytest.mark.parametrize("m,k,n", [(64, 2048, 8192), (9, 520, 1000), (33, 8192, 2048), (40, 64, 136)])
+def test_skinny_gemm(ctx, oracle, m, k, n, layout, splits):
+    """8 < M <= 64 takes the swapped-operand split-K kernel: both weight layouts, ragged N and K, a K of one
+    k-block, every split count (0 = automatic; a request for more splits than k-blocks is clipped), with the fused
+    bias / GELU / residual epilogue, three launches in a row (the tile tickets must return to zero), against the
+    oracle and against the general tcgen05 kernel."""
+    rng = np.random.default_rng(m + n + k + splits)
+    a = f16_normal(rng, (m, k))
+    w_kn = f16_normal(rng, (k, n), 0.05)
+    bias, res = f16_normal(rng, (n,), 0.5), f16_normal(rng, (m, n))
+    w = w_kn if layout == 0 else np.ascontiguousarray(w_kn.T)
+    ref = oracle.hgemm_nn(a, w_kn) if layout == 0 else oracle.hgemm_nt(a, w)
+    ref = oracle.add(oracle.gelu(oracle.bias_add(ref, bias)), res)
+    da, dw, db, dr = ctx.upload(a), ctx.upload(w), ctx.upload(bias), ctx.upload(res)
+    out = ctx.alloc((m, n))
+    ctx.set_option("skinny_splits", splits)
+    try:
+        for _ in range(3):
+            ctx.hgemm_fused(da, dw, out, m, n, k, layout, bias=db, gelu=True, residual=dr)
+        ctx.sync()
+        assert ctx.get_option("last_tc_tile") >= 1000      # the skinny kernel ran (1000 + number of splits)
+        if splits == 1:
+            assert ctx.get_option("last_tc_tile") == 1001
+    finally:
+        ctx.set_option("skinny_splits", 0)
+    got = out.numpy()
+    assert_close_ref(got, ref, f"skinny {m}x{n}x{k} splits {splits}")
+    ctx.set_option("skinny", 0)
+    try:
+        ctx.hgemm_fused(da, dw, out, m, n, k, layout, bias=db, gelu=True, residual=dr)
+        ctx.sync()
+        assert ctx.get_option("last_tc_tile") < 1000
+    finally:
+        ctx.set_option("skinny", 1)
+    assert_close_ref(got, out.numpy(), "skinny vs general kernel", rel=2e-3)
+    for b in (da, dw, db, dr, out):
+        b.free()
+
+
 def test_linearity_at_full_size(ctx):
     """Size-independent property at the lm_head size: (a1 + a2) W == a1 W + a2 W up to rounding,
     and a one-hot activation selects a weight column exactly."""
