@@ -182,6 +182,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the per-shape and GEMM side measurements")
+    ap.add_argument("--only", default=None, choices=sorted(ONLY_CASES),
+                    help="run one small side workload alone (for profiling a kernel) and print its timing")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -215,6 +217,13 @@ def main():
     # the weights are registered once and never written on this stream, so consecutive GEMVs may be
     # launched programmatically dependent (a kernel streams its first weights while its predecessor drains)
     ctx.set_option("pdl", 1)
+
+    if args.only:
+        print(json.dumps({"only": args.only, **run_only(ctx, torch, stream, args.only)}), flush=True)
+        ctx.sync()
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     ws_h, xs_h = make_inputs()
     # every one of the 20 problems owns its weight matrix, as in the reference's benchmark (a fresh B per case):
@@ -565,6 +574,98 @@ def extras(ctx, torch, stream, tensor_peak, hbm_peak):
                             "frac_of_measured_tensor": round(tf / tensor_peak, 3)})
         del w
     return out
+
+
+# name -> what `--only name` runs: a few launches of one kernel family on inputs larger than L2 where the bytes
+# matter, so that a profiler capture of it stays small
+ONLY_CASES = {
+    "gemm_config1": "64x2048 . 2048x8192 (both layouts), ten weight matrices in turn",
+    "gemm_8192": "8192^3 NT, three calls",
+    "gemm_prefill": "761x2048 . 2048x8192 NT with bias + GELU, ten weight matrices in turn",
+    "gemm_vit": "9477x1152 . 1152x4304 NN (13 crops, fc1) with bias + GELU, four weight matrices in turn",
+    "prefill": "text prefill of 761 rows through all 24 layers, three passes",
+    "decode": "text decode, one request, 761-row prefill then 40 steps",
+    "decode8": "text decode, eight requests batched, 761-row prefill each then 40 steps",
+    "vision1": "vision encode + projection, one crop, three passes",
+    "vision13": "vision encode + projection, thirteen crops, three passes",
+}
+
+
+def run_only(ctx, torch, stream, case):
+    g = torch.Generator(device="cuda").manual_seed(4000)
+
+    def n(*shape, std=0.02):
+        return (torch.randn(*shape, device="cuda", generator=g) * std).half()
+
+    def timed(fn, reps):
+        fn()
+        ctx.sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            fn()
+        e1.record(stream)
+        ctx.sync()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3
+
+    if case.startswith("gemm_"):
+        m, k, nn, layout, copies, glue = {"gemm_config1": (64, 2048, 8192, "both", 10, False),
+                                          "gemm_8192": (8192, 8192, 8192, "nt", 1, False),
+                                          "gemm_prefill": (761, 2048, 8192, "nt", 10, True),
+                                          "gemm_vit": (9477, 1152, 4304, "nn", 4, True)}[case]
+        x = torch.randn(m, k, device="cuda", generator=g).half()
+        y = torch.empty(m, nn, device="cuda", dtype=torch.float16)
+        bias = n(nn)
+        out = {}
+        for lay in (("nt", "nn") if layout == "both" else (layout,)):
+            w = n(copies, nn, k) if lay == "nt" else n(copies, k, nn)
+
+            def fn():
+                for c in range(copies):
+                    if glue:
+                        ctx.hgemm_fused(x.data_ptr(), w[c].data_ptr(), y.data_ptr(), m, nn, k, 1 if lay == "nt" else 0,
+                                        bias=bias.data_ptr(), gelu=True)
+                    else:
+                        (ctx.hgemm_nt if lay == "nt" else ctx.hgemm_nn)(x.data_ptr(), w[c].data_ptr(), m, nn, k,
+                                                                        out=y.data_ptr())
+            out[lay + "_us_per_call"] = round(timed(fn, 3) / copies, 2)
+            out[lay + "_kernel"] = ctx.get_option("last_tc_tile")
+            del w
+        return out
+    if case in ("prefill", "decode", "decode8"):
+        _, _, w, tm, embeds = build_text_model(ctx, torch, g)
+        batch = 8 if case == "decode8" else 1
+        reqs = [tm.request() for _ in range(batch)]
+        out = {}
+        for rep in range(3 if case == "prefill" else 1):
+            toks = []
+            for r in reqs:
+                r.reset()
+                t0 = time.perf_counter()
+                toks.append(tm.forward(r, embeds, want_hidden=False, want_logits=False)[2])
+                out["prefill_ms"] = round((time.perf_counter() - t0) * 1e3, 3)
+        if case != "prefill":
+            t0 = time.perf_counter()
+            if batch == 1:
+                tm.generate(reqs[0], toks[0], 40)
+            else:
+                tm.generate_batch(reqs, toks, 40)
+            out["us_per_step"] = round((time.perf_counter() - t0) / 40 * 1e6, 1)
+        for r in reqs:
+            r.close()
+        tm.close()
+        return out
+    crops = 13 if case == "vision13" else 1
+    vw, make_vm = build_vision_model(ctx, torch, g, n)
+    vm = make_vm(crops)
+    img = np.random.default_rng(crops).integers(0, 256, (crops, 378, 378, 3), dtype=np.uint8)
+    for _ in range(3):
+        t0 = time.perf_counter()
+        vm.encode(img)
+        ms = (time.perf_counter() - t0) * 1e3
+    vm.close()
+    return {"crops": crops, "encode_ms": round(ms, 3)}
 
 
 def build_text_model(ctx, torch, g):

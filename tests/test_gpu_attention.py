@@ -158,7 +158,7 @@ def test_fused_decode_rejects_full_cache(ctx, pkg):
     assert e.value.zig_error == "error.SequenceTooLong"
 
 
-@pytest.mark.parametrize("crops", [1, 2, 5])
+@pytest.mark.parametrize("crops", [1, 2, 5, 13])
 def test_vit_fused_attention(ctx, oracle, crops):
     """qkv [crops*729, 3456] -> per-crop 729-token attention, output [crops*729, 1152]."""
     rng = np.random.default_rng(crops)

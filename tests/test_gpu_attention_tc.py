@@ -69,7 +69,7 @@ def test_prefill_ignores_unwritten_cache_rows(ctx, oracle, forced):
     assert_close_ref(got, ref, "prefill over a poisoned cache")
 
 
-@pytest.mark.parametrize("crops", [1, 3])
+@pytest.mark.parametrize("crops", [1, 3, 13])
 def test_vit_layout(ctx, oracle, forced, crops):
     """Heads interleaved inside the packed qkv rows (row stride 3456, head stride 72), one batch per crop."""
     rng = np.random.default_rng(crops + 40)
