@@ -109,10 +109,7 @@ int md_set_gemm_mode(md_ctx* ctx, int mode);
  *                   0 = mma.sync attention only, 1 = tcgen05 only (MD_ERR_UNSUPPORTED otherwise)
  *   "prefill_fork"  1 (default) = a prefill layer runs fc1 -> fc2 as a second kernel chain beside the attention
  *   "decode_fork"   1 (default) = the fused decode layer runs as two concurrent kernel chains (q/k/v projection ->
- *                   attention -> out-projection | fc1 -> fc2) joined by events, 0 = three kernels in a row
- *   "persistent_decode" 1 = a decode step runs as one cooperative persistent kernel (default 0: measured
- *                   slower than the three-kernel layers on B200, kept as an alternative)
- *   "persist_trace" 1 = md_text_generate prints the phase timings of the persistent step to stderr */
+ *                   attention -> out-projection | fc1 -> fc2) joined by events, 0 = three kernels in a row */
 int md_set_option(md_ctx* ctx, const char* key, long value);
 /* Read back a knob or a diagnostic (no counterpart in the reference): "gemv_variant", "tc_block_n", "pdl", and
  *   "last_tc_tile"  the tile the last tcgen05 GEMM launch of this context used: 64 / 128 / 256 = width of a

@@ -321,8 +321,6 @@ int md_set_option(md_ctx* ctx, const char* key, long value) {
     if (!strcmp(key, "pdl")) { ctx->pdl = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "prefill_fork")) { ctx->prefill_fork = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "decode_fork")) { ctx->decode_fork = value ? 1 : 0; return MD_OK; }
-    if (!strcmp(key, "persist_trace")) { ctx->persist_trace = value ? 1 : 0; return MD_OK; }
-    if (!strcmp(key, "persistent_decode")) { ctx->persistent_decode = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "skinny")) { ctx->skinny = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "skinny_splits")) {
         MD_NEED(ctx, value >= 0 && value <= 16, "skinny_splits must be 0 (automatic) or 1..16 (rounded down to 1, 2, 4 or 8)");

@@ -89,8 +89,6 @@ struct md_ctx {
     int decode_fork = 1;        // md_set_option("decode_fork"): a decode layer runs as two concurrent kernel chains
     cudaStream_t side_stream = nullptr;  // second chain of the forked decode layer
     cudaEvent_t ev_fork = nullptr, ev_side = nullptr;
-    int persist_trace = 0;      // md_set_option("persist_trace"): print phase timings of the persistent step (tuning aid)
-    int persistent_decode = 0;  // md_set_option("persistent_decode"): one persistent kernel per decode step
     int attn_tc = -1;        // md_set_option("attn_tc"): -1 auto, 0 mma.sync attention only, 1 tcgen05 attention only
 };
 

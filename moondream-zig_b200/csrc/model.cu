@@ -5,7 +5,6 @@
 // through md_gemm_dispatch (GEMV for <= 8 rows, tcgen05 GEMM otherwise) with the reference's
 // glue fused into the epilogue at the reference's rounding points.
 #include "md_internal.cuh"
-#include "decode_persistent.cuh"
 
 #include "../../include/moondream_b200_model.h"
 
@@ -36,12 +35,10 @@ __global__ void embed_kernel(const __half* __restrict__ wte, const unsigned long
 __global__ void __launch_bounds__(256)
 advance_kernel(unsigned long long* cur_tokens, unsigned long long* sampled, int keys, int batch,
                unsigned int* tokens_out, int n_steps, const unsigned int* forced, int* step, int* const* pos_ptrs,
-               const __half* __restrict__ wte, __half* __restrict__ hidden, int dim, int vocab,
-               unsigned int* grid_counter) {
+               const __half* __restrict__ wte, __half* __restrict__ hidden, int dim, int vocab) {
     __shared__ unsigned long long next_tok[8];
     const int b = threadIdx.x;
     const int s = *step;
-    if (grid_counter && b < 4) grid_counter[b] = 0u;  // the persistent step's barriers start every step at zero
     if (b < batch) {
         unsigned long long tok = sampled[b];
         if (keys) {
@@ -119,13 +116,10 @@ struct md_text_request {
     DevPtr hidden, ln, qkv, attn, attn_out, fc1, logits, ln_last;
     // device-side generation state
     DevPtr cur_token, sampled, tokens_out, forced, step, logits_all, pos_ptrs;
-    // persistent decode step: pointer table, attention scratch, attention tickets + grid-barrier counter
-    DevPtr persist_tab, persist_scratch, persist_ctr;
-    size_t persist_batch = 0;  // 0: the persistent step is not in use for the current generate call
     md_graph* graph = nullptr;
     uint64_t graph_gen = 0, prefill_graph_gen = 0;  // md_ctx::generation the graphs were captured under
     size_t graph_steps = 0;
-    bool graph_forced = false, graph_logits = false, graph_persistent = false;
+    bool graph_forced = false, graph_logits = false;
     // a prefill of the same shape at the same position seen twice is captured and replayed
     md_graph* prefill_graph = nullptr;
     size_t prefill_S = 0, prefill_pos = 0, seen_S = 0, seen_pos = ~(size_t)0;
@@ -536,35 +530,14 @@ static int enqueue_decode_step(md_text_model* model, md_text_request* const* req
     PdlScope pdl_scope(ctx);
     // hidden already holds the embeddings of the current tokens (generate_impl / the previous advance_kernel)
     const LayerIO io = io_of(r0);
-    const bool persistent = r0->persist_batch == batch;
     const bool ln_once = ctx->decode_split_ln > 0 && batch >= (size_t)ctx->decode_split_ln;
     // The automatic GEMV variant is tuned for isolated calls; inside the decode step, where two kernel chains share
     // the SMs, 8 warps with 8 loads in flight per lane measured best for every GEMV and every batch size
     // (742 -> 730 us per step at 1 row, 962 -> 942 at 4 rows, 1210 -> 1079 at 6 rows).
     GemvVariantScope gemv_scope(ctx, 3);
-    if (persistent) {
-        // the whole step (24 layers + lm_head + argmax) as one persistent kernel (decode_persistent.cu)
-        md_persist_params pp;
-        pp.tab = r0->persist_tab.as<md_persist_table>();
-        pp.hidden = io.hidden; pp.qkv = io.qkv; pp.attn = io.attn; pp.fc1 = io.fc1;
-        pp.logits = r0->logits.as<__half>();
-        pp.amax = r0->sampled.as<unsigned long long>();
-        pp.att_scratch = r0->persist_scratch.as<float>();
-        pp.att_counters = r0->persist_ctr.as<unsigned int>();
-        pp.grid_counter = r0->persist_ctr.as<unsigned int>() + 256;
-        MD_TRY(md_rope_cached(ctx, w.rot_dim, w.rope_theta, w.max_seq, &pp.rope_tab));
-        pp.M = (int)batch; pp.n_layers = (int)w.n_layers; pp.vocab = (int)w.vocab; pp.max_seq = (int)w.max_seq;
-        pp.max_splits = (int)((w.max_seq + 31) / 32);
-        pp.eps = eps_of(w.eps_f16);
-        pp.flags = ctx->flags;
-        pp.trace = ctx->persist_trace ? reinterpret_cast<unsigned long long*>(r0->persist_ctr.as<unsigned int>() + 264) : nullptr;
-        MD_TRY(md_launch_decode_persistent(ctx, pp));
-    } else {
-        for (size_t l = 0; l < w.n_layers; ++l) MD_TRY(text_layer(model, l, io, batch, true, reqs, 0));
-    }
-    const bool fused_head = persistent || (ctx->fused_decode && !ln_once && md_gemv_ln_dual_supported(batch, w.dim, w.vocab, 0));
-    if (persistent) {
-    } else if (fused_head) {
+    for (size_t l = 0; l < w.n_layers; ++l) MD_TRY(text_layer(model, l, io, batch, true, reqs, 0));
+    const bool fused_head = ctx->fused_decode && !ln_once && md_gemv_ln_dual_supported(batch, w.dim, w.vocab, 0);
+    if (fused_head) {
         // final LayerNorm + lm_head + greedy argmax in one kernel (text_model.zig:325-345, sampling.zig:257-273)
         MD_TRY(md_launch_gemv_ln_dual(ctx, r0->hidden.as<__half>(), H(w.ln_out_w), H(w.ln_out_b), eps_of(w.eps_f16),
                                       H(w.lm_w), H(w.lm_b), r0->logits.as<__half>(), w.vocab, nullptr, nullptr, nullptr,
@@ -583,8 +556,7 @@ static int enqueue_decode_step(md_text_model* model, md_text_request* const* req
                                                r0->tokens_out.as<unsigned int>(), (int)n_steps,
                                                forced ? r0->forced.as<unsigned int>() : nullptr, r0->step.as<int>(),
                                                r0->pos_ptrs.as<int*>(), H(w.wte), r0->hidden.as<__half>(), (int)w.dim,
-                                               (int)w.vocab,
-                                               persistent ? r0->persist_ctr.as<unsigned int>() + 256 : nullptr);
+                                               (int)w.vocab);
     MD_LAUNCH_CHECK(ctx, "advance_kernel");
     return MD_OK;
 }
@@ -626,39 +598,12 @@ static int generate_impl(md_text_model* model, md_text_request* const* reqs, siz
     if (forced)
         MD_CUDA(ctx, cudaMemcpyAsync(r0->forced.p, forced, batch * n_steps * sizeof(unsigned int), cudaMemcpyHostToDevice,
                                      ctx->stream));
-    // persistent decode step: every pointer of the step in one device table
-    r0->persist_batch = 0;
-    if (ctx->persistent_decode && ctx->fused_decode &&
-        md_decode_persistent_supported(w.dim, w.hidden, w.n_heads, w.head_dim, w.rot_dim, w.vocab, w.n_layers, batch)) {
-        md_persist_table tab;
-        memset(&tab, 0, sizeof(tab));
-        for (size_t l = 0; l < w.n_layers; ++l) {
-            md_persist_table::Layer& L = tab.layers[l];
-            L.ln_w = H(model->ln_w[l]); L.ln_b = H(model->ln_b[l]);
-            L.wqkv = H(model->wqkv[l]); L.bqkv = H(model->bqkv[l]);
-            L.wfc1 = H(model->wfc1[l]); L.bfc1 = H(model->bfc1[l]);
-            L.wout = H(model->wout[l]); L.bout = H(model->bout[l]);
-            L.wfc2 = H(model->wfc2[l]); L.bfc2 = H(model->bfc2[l]);
-            for (size_t b = 0; b < batch; ++b) { L.kc[b] = reqs[b]->kc[l]; L.vc[b] = reqs[b]->vc[l]; }
-        }
-        tab.ln_out_w = H(w.ln_out_w); tab.ln_out_b = H(w.ln_out_b);
-        tab.lm_w = H(w.lm_w); tab.lm_b = H(w.lm_b);
-        for (size_t b = 0; b < batch; ++b) tab.pos[b] = reqs[b]->pos_dev;
-        MD_TRY(r0->persist_tab.ensure(ctx, sizeof(tab)));
-        MD_TRY(r0->persist_scratch.ensure(ctx, md_decode_persistent_scratch_bytes(8, w.max_seq)));
-        MD_TRY(r0->persist_ctr.ensure(ctx, (264 + 1024) * sizeof(unsigned int)));
-        MD_CUDA(ctx, cudaMemcpyAsync(r0->persist_tab.p, &tab, sizeof(tab), cudaMemcpyHostToDevice, ctx->stream));
-        MD_CUDA(ctx, cudaMemsetAsync(r0->persist_ctr.p, 0, (264 + 1024) * sizeof(unsigned int), ctx->stream));
-        MD_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // tab is a stack object
-        r0->persist_batch = batch;
-    }
     MD_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // cur / pos_ptrs are stack arrays
 
     // The graph depends on the requests' buffers and on which optional outputs exist; a single
     // request keeps its graph across calls, a batch captures one per call.
     const bool reuse = batch == 1 && r0->graph && r0->graph_gen == ctx->generation && r0->graph_steps == n_steps &&
                        r0->graph_forced == (forced != nullptr) &&
-                       r0->graph_persistent == (r0->persist_batch == batch) &&
                        r0->graph_logits == (logits_out != nullptr);
     md_graph* graph = reuse ? r0->graph : nullptr;
     size_t done = 0;
@@ -680,7 +625,6 @@ static int generate_impl(md_text_model* model, md_text_request* const* reqs, siz
                 r0->graph_gen = ctx->generation;
                 r0->graph_steps = n_steps;
                 r0->graph_forced = forced != nullptr;
-                r0->graph_persistent = r0->persist_batch == batch;
                 r0->graph_logits = logits_out != nullptr;
             }
         }
@@ -693,23 +637,6 @@ static int generate_impl(md_text_model* model, md_text_request* const* reqs, siz
         MD_CUDA(ctx, cudaMemcpyAsync(logits_out, r0->logits_all.p, n_steps * w.vocab * 2, cudaMemcpyDeviceToHost,
                                      ctx->stream));
     const int st = md_check_flags(ctx);
-    if (ctx->persist_trace && r0->persist_batch == batch && st == MD_OK) {
-        // tuning aid: phase durations (us) of the last step on the first and last CTA, layers averaged
-        std::vector<unsigned long long> tr(512);
-        cudaMemcpy(tr.data(), r0->persist_ctr.as<unsigned int>() + 264, 512 * 8, cudaMemcpyDeviceToHost);
-        static const char* names[7] = {"ln", "phaseA", "wait_qkv", "attn", "wait_fc1", "phaseC", "sync_hidden"};
-        for (int which = 0; which < 2; ++which) {
-            const unsigned long long* t = tr.data() + which * 256;
-            double acc[7] = {0};
-            for (size_t l = 0; l < w.n_layers; ++l)
-                for (int k = 0; k < 7; ++k) acc[k] += (double)(t[1 + l * 7 + k] - t[l * 7 + k]);
-            fprintf(stderr, "[persist_trace] cta %s:", which ? "last" : "0");
-            for (int k = 0; k < 7; ++k) fprintf(stderr, " %s %.2f", names[k], acc[k] / w.n_layers / 1e3);
-            const size_t e = w.n_layers * 7;
-            fprintf(stderr, " | head_ln %.2f head %.2f total %.1f us\n", (t[e + 1] - t[e]) / 1e3,
-                    (t[e + 2] - t[e + 1]) / 1e3, (t[e + 2] - t[0]) / 1e3);
-        }
-    }
     if (graph && batch != 1) md_graph_destroy(ctx, graph);
     return st;
 }

@@ -208,36 +208,6 @@ def test_text_forked_decode_layer_matches_the_three_kernel_layer(ctx, models_mod
     gpu.close()
 
 
-def test_text_persistent_decode_step_matches_the_three_kernel_layers(ctx, models_mod):
-    """Option persistent_decode: the whole step as one cooperative kernel (weight ring + grid barriers). Same
-    rounding points as the 3-kernel layers, so logits agree to the parity bar; single request and a batch of 3
-    with different cache lengths (different numbers of attention splits per request)."""
-    w = text_weights(4007, n_layers=3, hidden=8192, vocab=4096)
-    gpu = models_mod.TextModel(ctx, w)
-    rng = np.random.default_rng(7)
-    prompts = [w["wte"][rng.integers(0, 4096, n)] for n in (70, 1, 33)]
-    forced = np.arange(1, 9, dtype=np.uint32) * 41 % 4096
-    res, batch_tokens = {}, {}
-    for persistent in (1, 0):
-        ctx.set_option("persistent_decode", persistent)
-        try:
-            req = gpu.request()
-            _, _, tok = gpu.forward(req, prompts[0])
-            res[persistent] = gpu.generate(req, tok, 8, forced=forced, want_logits=True)
-            req.close()
-            reqs = [gpu.request() for _ in prompts]
-            firsts = [gpu.forward(r, pr)[2] for r, pr in zip(reqs, prompts)]
-            batch_tokens[persistent] = np.asarray(gpu.generate_batch(reqs, firsts, 6))
-            for r in reqs:
-                r.close()
-        finally:
-            ctx.set_option("persistent_decode", 0)
-    for i in range(8):
-        assert_close_ref(res[1][1][i], res[0][1][i], f"persistent vs 3-kernel logits step {i}", rel=5e-3)
-    assert (batch_tokens[1] == batch_tokens[0]).mean() >= 0.8  # random weights: near-ties may flip a token
-    gpu.close()
-
-
 @pytest.mark.parametrize("cluster_merge", [1, 0], ids=["cluster_merge", "scratch_merge"])
 def test_text_batched_decode_equals_single_requests(ctx, models_mod, cluster_merge):
     """One attention launch serves the whole batch (grid z = request), each request at its own position; both ways
