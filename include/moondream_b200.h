@@ -90,6 +90,8 @@ int md_set_gemm_mode(md_ctx* ctx, int mode);
 
 /* Tuning knobs for tests and profiling; unknown keys return MD_ERR_INVALID_ARG.
  *   "gemv_variant"  0 = automatic, 1..6 = a fixed (warps, unroll) configuration of the GEMV kernel
+ *   "gemv_ksplit"   0 = automatic, 1 / 2 / 4 / 8 = number of K splits of the GEMV kernel (the CTAs of a thread-block
+ *                   cluster stream K / S each and add their sums through distributed shared memory)
  *   "tc_block_n"    0 = automatic, 64 / 128 / 256 = fixed tile width of the tcgen05 GEMM (128-row tiles),
  *                   512 = the 256 x 256 tile
  *   "skinny"        1 (default) = products with 8 < M <= 64 rows take the swapped-operand split-K kernel (weights on

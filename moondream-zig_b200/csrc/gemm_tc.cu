@@ -15,7 +15,7 @@
 //               64 KB per 1024 tensor cycles instead of 48 KB per 512.
 //   warps 2..9  epilogue: tcgen05.ld (32 lanes x 32 columns) -> fused glue -> f16 ->
 //               swizzled smem -> TMA store (clips the M and N tails).
-//   warps 10..13 (column-split GEMM only) push: once a tile's TMA stores have completed they read the tile
+//   warps 10..17 (column-split GEMM only) push: once a tile's TMA stores have completed they read the tile
 //               back from this GPU's C (L2 hits) and store it into the other GPUs' copies of C with plain
 //               16-byte peer stores.  The epilogue warps never wait for NVLink: they hand the accumulator
 //               back to the MMA issuer as before, and the push of tile i runs beside the main loop of the
@@ -38,7 +38,7 @@ constexpr int A_STAGE_BYTES = BLOCK_M * BLOCK_K * 2;     // 16 KiB
 constexpr int EPI_WARPS = 8, EPI_BUF_BYTES = 32 * 128;   // 32 rows x 64 f16 per epilogue warp
 constexpr int EPI_BYTES = EPI_WARPS * EPI_BUF_BYTES;     // 32 KiB
 constexpr int NUM_THREADS = (2 + EPI_WARPS) * 32;
-constexpr int PUSH_WARPS = 4;                            // extra warps of the column-split form
+constexpr int PUSH_WARPS = 8;                            // extra warps of the column-split form
 constexpr int NUM_THREADS_PUSH = NUM_THREADS + PUSH_WARPS * 32;
 constexpr int RASTER_GROUP_M = 8;                        // tile rows per rasterisation group
 constexpr int SMEM_LIMIT = 232448;                       // 227 KiB opt-in maximum
@@ -86,8 +86,10 @@ static __device__ __noinline__ bool wait_stored(volatile unsigned* stored, unsig
     }
 }
 
-template <int BLOCK_N, bool B_MN_MAJOR, int MT>
-__global__ void __launch_bounds__(NUM_THREADS_PUSH, 1)
+// PUSH = the column-split form with its eight extra warps (its own instantiation, so that the plain kernel keeps the
+// register budget of 320 threads)
+template <int BLOCK_N, bool B_MN_MAJOR, int MT, bool PUSH>
+__global__ void __launch_bounds__(PUSH ? NUM_THREADS_PUSH : NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_c, int M, int N, int K, int tiles_m, int num_tiles,
                md_epilogue ep, md_push push, md_devflags* flags) {
@@ -335,7 +337,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
             }
-            if (push.n > 0 && lane == 0) {
+            if (PUSH && lane == 0) {
                 // Column-split GEMM: this warp's part of the tile is in this GPU's C once its TMA stores have
                 // completed; tell the push warps (every epilogue warp counts once per tile).  The wait costs
                 // nothing: the warp would next wait for the following tile's accumulator anyway.
@@ -345,14 +347,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             }
         }
         if (lane == 0) tma_store_wait_all();
-    } else {
-        // ------------------------------------------------------------ push (warps 10..13, column-split GEMM)
+    } else if (PUSH) {
+        // ------------------------------------------------------------ push (warps 10..17, column-split GEMM)
         // A warp instruction covers 32 / (BLOCK_N / 8) whole tile rows (BLOCK_N * 2 contiguous bytes each); four
         // row groups are loaded before their peer stores are issued, peers interleaved.
-        constexpr int LANES_PER_ROW = BLOCK_N / 8, ROWS_PER_INSTR = 32 / LANES_PER_ROW, UNR = 4;
+        // While the main loop runs, the SM's return path from L2 is full of operand tiles and a load round trip of a
+        // push warp takes several microseconds: eight warps request 8 row groups each at once, so that a 128-row
+        // tile is two rounds (with four warps and four groups in flight the pushes fell behind the math: 317 us at
+        // four GPUs against 200 us for the product alone).
+        constexpr int LANES_PER_ROW = BLOCK_N / 8, ROWS_PER_INSTR = 32 / LANES_PER_ROW, UNR = 8;
         constexpr int ROW_STEP = PUSH_WARPS * ROWS_PER_INSTR;
         const int pw = warp - (2 + EPI_WARPS);
         const int sub = lane / LANES_PER_ROW, cl = (lane % LANES_PER_ROW) * 8;
+        const int ld = (int)push.ld;
         int local = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
             int tm, tn;
@@ -361,22 +368,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             if (!wait_stored(stored, (unsigned)(EPI_WARPS * (local + 1)), abort_flag, flags, 5)) break;
             const int gc = n0 + cl;
             if (gc >= N) continue;  // columns past this rank's block belong to a neighbour
+            const long long tile_off = (long long)m0 * push.ld + gc;
             for (int r = pw * ROWS_PER_INSTR + sub; r < TILE_M; r += ROW_STEP * UNR) {
                 uint4 val[UNR];
-                long long off[UNR];
 #pragma unroll
                 for (int u = 0; u < UNR; ++u) {
-                    const int gm = m0 + r + u * ROW_STEP;
-                    off[u] = (r + u * ROW_STEP < TILE_M && gm < M) ? (long long)gm * push.ld + gc : -1;
-                    if (off[u] >= 0) val[u] = __ldcg(reinterpret_cast<const uint4*>(push.self + off[u]));
+                    const int rr = r + u * ROW_STEP;
+                    if (rr < TILE_M && m0 + rr < M) val[u] = __ldcg(reinterpret_cast<const uint4*>(push.self + tile_off + rr * ld));
                 }
                 for (int pi = 0; pi < push.n; ++pi) {
                     // start with a different peer in every CTA so that the stores spread over the links
                     int peer = pi + (int)blockIdx.x;
                     peer -= (peer / push.n) * push.n;
+                    __half* dst = push.base[peer] + tile_off;
 #pragma unroll
-                    for (int u = 0; u < UNR; ++u)
-                        if (off[u] >= 0) *reinterpret_cast<uint4*>(push.base[peer] + off[u]) = val[u];
+                    for (int u = 0; u < UNR; ++u) {
+                        const int rr = r + u * ROW_STEP;
+                        if (rr < TILE_M && m0 + rr < M) *reinterpret_cast<uint4*>(dst + rr * ld) = val[u];
+                    }
                 }
             }
         }
@@ -423,8 +432,8 @@ int make_map_2d(md_ctx* ctx, CUtensorMap* map, const void* ptr, uint64_t inner, 
     return MD_OK;
 }
 
-template <int BLOCK_N, bool B_MN_MAJOR, int MT = 1>
-int launch(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
+template <int BLOCK_N, bool B_MN_MAJOR, int MT, bool PUSH>
+int launch_as(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
            const md_epilogue& ep, size_t ldc, const md_push& push) {
     CUtensorMap tm_a, tm_b, tm_c;
     MD_TRY(make_map_2d(ctx, &tm_a, a, K, M, BLOCK_K, BLOCK_M));
@@ -434,17 +443,25 @@ int launch(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, s
     const int tiles_m = (int)((M + MT * BLOCK_M - 1) / (MT * BLOCK_M)), tiles_n = (int)((N + BLOCK_N - 1) / BLOCK_N);
     const int num_tiles = tiles_m * tiles_n;
     const int grid = num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count;
-    auto kern = gemm_tc_kernel<BLOCK_N, B_MN_MAJOR, MT>;
+    auto kern = gemm_tc_kernel<BLOCK_N, B_MN_MAJOR, MT, PUSH>;
     constexpr int smem = smem_bytes(BLOCK_N, MT);
-    const uint32_t cfg_bit = MT == 2 ? (1u << (B_MN_MAJOR ? 12 : 11))
-                                     : 1u << ((BLOCK_N == 256 ? 0 : BLOCK_N == 128 ? 1 : 2) + (B_MN_MAJOR ? 3 : 0));
+    const uint32_t cfg_bit = (MT == 2 ? (1u << (B_MN_MAJOR ? 12 : 11))
+                                      : 1u << ((BLOCK_N == 256 ? 0 : BLOCK_N == 128 ? 1 : 2) + (B_MN_MAJOR ? 3 : 0)))
+                             << (PUSH ? 16 : 0);
     if (!(ctx->tc_configured & cfg_bit)) {
         MD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         ctx->tc_configured |= cfg_bit;
     }
     ctx->last_tc_tile = MT == 2 ? 512 : BLOCK_N;
-    return md_launch_ex(ctx, kern, dim3((unsigned)grid), dim3(push.n > 0 ? NUM_THREADS_PUSH : NUM_THREADS), smem,
+    return md_launch_ex(ctx, kern, dim3((unsigned)grid), dim3(PUSH ? NUM_THREADS_PUSH : NUM_THREADS), smem,
                         "gemm_tc_kernel", tm_a, tm_b, tm_c, (int)M, (int)N, (int)K, tiles_m, num_tiles, ep, push, ctx->flags);
+}
+
+template <int BLOCK_N, bool B_MN_MAJOR, int MT = 1>
+int launch(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
+           const md_epilogue& ep, size_t ldc, const md_push& push) {
+    if (push.n > 0) return launch_as<BLOCK_N, B_MN_MAJOR, MT, true>(ctx, a, b, c, M, N, K, ep, ldc, push);
+    return launch_as<BLOCK_N, B_MN_MAJOR, MT, false>(ctx, a, b, c, M, N, K, ep, ldc, push);
 }
 
 }  // namespace

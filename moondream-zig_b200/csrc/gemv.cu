@@ -18,6 +18,13 @@
 // f16->f32 convert and FMA issue pressure of a SIMT GEMV for every M up to 8,
 // accumulates in f32, and needs no shuffle reduction: the warps' partial 16x8
 // tiles are summed through shared memory.
+//
+// Split K.  A matrix with few rows (N = 2048: 128 CTAs) cannot keep enough bytes in
+// flight to reach the HBM rate, however many loads a lane issues.  Such a launch
+// splits K over the S CTAs of a thread-block cluster (grid.y = S): every CTA streams
+// K / S of its 16 rows, leaves its 16 x 8 partial sums in shared memory, and after one
+// cluster barrier the first CTA of the cluster adds the S partials through distributed
+// shared memory (fixed order), applies the glue and stores.  No global scratch.
 #include "md_internal.cuh"
 
 namespace {
@@ -58,6 +65,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 gemv_nt_mma_kernel(const __half* A, const __half* __restrict__ Bt, __half* C, int M, int N,
                    int K, md_epilogue ep) {
     __shared__ float partial[WARPS][ROWS_PER_CTA][8];
+    __shared__ float cta_sum[ROWS_PER_CTA * 8];   // this CTA's 16 x 8 sums, read by the cluster's first CTA
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int row0 = blockIdx.x * ROWS_PER_CTA;
@@ -70,9 +78,12 @@ gemv_nt_mma_kernel(const __half* A, const __half* __restrict__ Bt, __half* C, in
 
     // K is split into 32-wide chunks dealt round-robin to the warps, so that at any
     // moment the CTA reads one contiguous span of each of its 16 rows.
-    const int chunks = K / 32;
+    const int all_chunks = K / 32;
+    const int splits = gridDim.y, split = blockIdx.y;
+    const int per_split = (all_chunks + splits - 1) / splits;
+    const int chunks = min(all_chunks, (split + 1) * per_split);   // this CTA's chunks: [split * per_split, chunks)
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    int ch = warp;
+    int ch = split * per_split + warp;
     // Programmatic dependent launch: let the next kernel of the stream start its own prologue now, and
     // stream this kernel's first weights (which no earlier kernel writes) before waiting for the kernel
     // that produces the activations.  Without the launch attribute both instructions are no-ops.
@@ -111,8 +122,8 @@ gemv_nt_mma_kernel(const __half* A, const __half* __restrict__ Bt, __half* C, in
     }
     // K tail (K % 32 != 0, still a multiple of 8): 8-half pieces handled by warp 0 with
     // the lanes whose piece exists; missing pieces contribute zeros.
-    const int tail0 = chunks * 32;
-    if (warp == 0 && tail0 < K) {
+    const int tail0 = all_chunks * 32;
+    if (warp == 0 && split == 0 && tail0 < K) {
         const int k = tail0 + t * 8;
         uint4 lo = make_uint4(0, 0, 0, 0), hi = lo, xv = lo;
         if (k < K) {
@@ -130,17 +141,51 @@ gemv_nt_mma_kernel(const __half* A, const __half* __restrict__ Bt, __half* C, in
     partial[warp][g + 8][2 * t] = acc[2];
     partial[warp][g + 8][2 * t + 1] = acc[3];
     __syncthreads();
-    // 16 rows x 8 activation rows = 128 outputs; a CTA of two warps takes two turns
-    for (int o = threadIdx.x; o < ROWS_PER_CTA * 8; o += WARPS * 32) {
-        const int m = o >> 4, r = o & 15;  // consecutive threads -> consecutive n
-        const int n = row0 + r;
-        if (m < M && n < N) {
-            float s = 0.f;
+    if (splits == 1) {
+        // 16 rows x 8 activation rows = 128 outputs; a CTA of two warps takes two turns
+        for (int o = threadIdx.x; o < ROWS_PER_CTA * 8; o += WARPS * 32) {
+            const int m = o >> 4, r = o & 15;  // consecutive threads -> consecutive n
+            const int n = row0 + r;
+            if (m < M && n < N) {
+                float s = 0.f;
 #pragma unroll
-            for (int w = 0; w < WARPS; ++w) s += partial[w][r][m];
-            C[(size_t)m * N + n] = __float2half_rn(md_epilogue_value(ep, s, m, n, N));
+                for (int w = 0; w < WARPS; ++w) s += partial[w][r][m];
+                C[(size_t)m * N + n] = __float2half_rn(md_epilogue_value(ep, s, m, n, N));
+            }
+        }
+        return;
+    }
+    // split K: this CTA's sums go to cta_sum; the cluster's first CTA adds the S of them in the order 0 .. S-1
+    for (int o = threadIdx.x; o < ROWS_PER_CTA * 8; o += WARPS * 32) {
+        const int m = o >> 4, r = o & 15;
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) s += partial[w][r][m];
+        cta_sum[o] = s;
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (split == 0) {
+        for (int o = threadIdx.x; o < ROWS_PER_CTA * 8; o += WARPS * 32) {
+            const int m = o >> 4, r = o & 15;
+            const int n = row0 + r;
+            if (m < M && n < N) {
+                const uint32_t local = (uint32_t)__cvta_generic_to_shared(&cta_sum[o]);
+                float s = 0.f;
+                for (int c = 0; c < splits; ++c) {
+                    uint32_t remote;
+                    float v;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(c));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote));
+                    s += v;
+                }
+                C[(size_t)m * N + n] = __float2half_rn(md_epilogue_value(ep, s, m, n, N));
+            }
         }
     }
+    // nobody leaves while the first CTA may still read its shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 }  // namespace
@@ -165,14 +210,31 @@ int md_launch_gemv_nt(md_ctx* ctx, const __half* a, const __half* bt, __half* c,
     // With ctx->pdl the launch carries the programmatic-stream-serialization attribute: the kernel may
     // start while its predecessor drains and orders itself with griddepcontrol.wait.  Only valid when
     // the weights are not produced by an earlier kernel of the stream (true for registered weights).
+    // K splits (a cluster along y).  Clusters start more slowly than plain CTAs, so a split pays only where a
+    // matrix has at most one CTA per SM and long rows (the 8192 -> 2048 projection: 10.3 -> 8.4 us with two splits;
+    // four were slower again, and every shape with more rows lost).  md_set_option("gemv_ksplit") fixes the count.
+    int ksplit = ctx->gemv_ksplit;
+    if (ksplit <= 0) ksplit = (grid <= (unsigned)ctx->sm_count && K >= 4096) ? 2 : 1;
+    while (ksplit > 1 && (size_t)(K / 32) < (size_t)ksplit) ksplit /= 2;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
+    cfg.gridDim = dim3(grid, (unsigned)ksplit);
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (ksplit > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = (unsigned)ksplit;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (ctx->pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    cfg.numAttrs = na;
     const int Mi = (int)M, Ni = (int)N, Ki = (int)K;
     cudaError_t le = cudaSuccess;
 #define MD_GEMV_CASE(id, W, U)                                                          \

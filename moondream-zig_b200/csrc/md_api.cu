@@ -310,6 +310,11 @@ int md_set_option(md_ctx* ctx, const char* key, long value) {
     MD_NEED(ctx, key, "md_set_option: null key");
     ctx->generation++;  // options select kernels: graphs captured under the old settings are captured again
     if (!strcmp(key, "gemv_variant")) { ctx->gemv_variant = (int)value; return MD_OK; }
+    if (!strcmp(key, "gemv_ksplit")) {
+        MD_NEED(ctx, value == 0 || value == 1 || value == 2 || value == 4 || value == 8, "gemv_ksplit must be 0, 1, 2, 4 or 8");
+        ctx->gemv_ksplit = (int)value;
+        return MD_OK;
+    }
     if (!strcmp(key, "decode_cluster")) {
         ctx->decode_cluster_mode = value < 0 ? -1 : (value ? 1 : 0);
         ctx->decode_cluster_ok = -1;

@@ -77,6 +77,7 @@ struct md_ctx {
     // runners store the value with every graph they keep and capture again when it differs.
     uint64_t generation = 0;
     int gemv_variant = 0;    // md_set_option("gemv_variant")
+    int gemv_ksplit = 0;     // md_set_option("gemv_ksplit"): 0 = automatic, 1 / 2 / 4 / 8 = K splits of the GEMV kernel
     int tc_block_n = 0;      // md_set_option("tc_block_n")
     int last_tc_tile = 0;    // md_get_option("last_tc_tile"): tile of the last tcgen05 GEMM launch (64/128/256, 512 = 256 x 256)
     int decode_cluster_ok = -1;    // -1 unknown, 0/1: 16-CTA clusters usable for the decode attention merge

@@ -144,6 +144,29 @@ def test_gemv_fixed_variants(ctx, oracle, variant, m):
     assert_close_ref(got, oracle.hgemm_nt(a, w), f"gemv variant {variant} M={m}")
 
 
+@pytest.mark.parametrize("ksplit", [1, 2, 4, 8])
+@pytest.mark.parametrize("m,k,n", [(1, 8192, 2048), (8, 2048, 2048), (5, 2056, 1000), (3, 40, 17), (2, 96, 50)])
+def test_gemv_split_k(ctx, oracle, ksplit, m, k, n):
+    """K split over the CTAs of a cluster (sums added through distributed shared memory): every split count, a K tail,
+    K shorter than the split count (the count is clipped), with the fused bias + residual epilogue, twice in a row."""
+    rng = np.random.default_rng(ksplit * 100 + m + n)
+    a, w = f16_normal(rng, (m, k)), f16_normal(rng, (n, k), 0.05)
+    bias, res = f16_normal(rng, (n,), 0.5), f16_normal(rng, (m, n))
+    ref = oracle.add(oracle.bias_add(oracle.hgemm_nt(a, w), bias), res)
+    da, dw, db, dr = ctx.upload(a), ctx.upload(w), ctx.upload(bias), ctx.upload(res)
+    out = ctx.alloc((m, n))
+    ctx.set_option("gemv_ksplit", ksplit)
+    try:
+        for _ in range(2):
+            ctx.hgemm_fused(da, dw, out, m, n, k, 1, bias=db, residual=dr)
+        ctx.sync()
+    finally:
+        ctx.set_option("gemv_ksplit", 0)
+    assert_close_ref(out.numpy(), ref, f"gemv split-K {ksplit} M={m} {k}->{n}")
+    for b in (da, dw, db, dr, out):
+        b.free()
+
+
 @pytest.mark.parametrize("m,k,n", [(3, 2048, 100), (8, 40, 17), (1, 8, 1), (5, 8200, 33)])
 def test_gemv_edges(ctx, oracle, m, k, n):
     rng = np.random.default_rng(n)
