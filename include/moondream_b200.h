@@ -111,7 +111,10 @@ int md_set_gemm_mode(md_ctx* ctx, int mode);
  *                   0 = mma.sync attention only, 1 = tcgen05 only (MD_ERR_UNSUPPORTED otherwise)
  *   "prefill_fork"  1 (default) = a prefill layer runs fc1 -> fc2 as a second kernel chain beside the attention
  *   "decode_fork"   1 (default) = the fused decode layer runs as two concurrent kernel chains (q/k/v projection ->
- *                   attention -> out-projection | fc1 -> fc2) joined by events, 0 = three kernels in a row */
+ *                   attention -> out-projection | fc1 -> fc2) joined by events, 0 = three kernels in a row
+ *   "decode_mlp_split" 2 (default) or 4 = with decode_fork and a single request, the MLP chain runs as that many
+ *                   independent chains (a slice of fc1's rows, then that slice of fc2's K sum as f32 partial sums) which
+ *                   the out-projection's epilogue adds with the reference's roundings; 0 = one MLP chain */
 int md_set_option(md_ctx* ctx, const char* key, long value);
 /* Read back a knob or a diagnostic (no counterpart in the reference): "gemv_variant", "tc_block_n", "pdl", and
  *   "last_tc_tile"  the tile the last tcgen05 GEMM launch of this context used: 64 / 128 / 256 = width of a

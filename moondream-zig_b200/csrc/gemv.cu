@@ -63,7 +63,7 @@ constexpr int ROWS_PER_CTA = 16;
 template <int WARPS, int UNROLL>
 __global__ void __launch_bounds__(WARPS * 32)
 gemv_nt_mma_kernel(const __half* A, const __half* __restrict__ Bt, __half* C, int M, int N,
-                   int K, md_epilogue ep) {
+                   int K, int ldb, md_epilogue ep) {
     __shared__ float partial[WARPS][ROWS_PER_CTA][8];
     __shared__ float cta_sum[ROWS_PER_CTA * 8];   // this CTA's 16 x 8 sums, read by the cluster's first CTA
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -71,8 +71,8 @@ gemv_nt_mma_kernel(const __half* A, const __half* __restrict__ Bt, __half* C, in
     const int row0 = blockIdx.x * ROWS_PER_CTA;
     // Rows past N are clamped for the loads and dropped at the store.
     const int r_lo = min(row0 + g, N - 1), r_hi = min(row0 + g + 8, N - 1);
-    const __half* w_lo = Bt + (size_t)r_lo * K + t * 8;
-    const __half* w_hi = Bt + (size_t)r_hi * K + t * 8;
+    const __half* w_lo = Bt + (size_t)r_lo * ldb + t * 8;   // ldb >= K: the rows may be K-slices of a wider matrix
+    const __half* w_hi = Bt + (size_t)r_hi * ldb + t * 8;
     const bool has_x = g < M;
     const __half* x = A + (size_t)(has_x ? g : 0) * K + t * 8;
 
@@ -127,8 +127,8 @@ gemv_nt_mma_kernel(const __half* A, const __half* __restrict__ Bt, __half* C, in
         const int k = tail0 + t * 8;
         uint4 lo = make_uint4(0, 0, 0, 0), hi = lo, xv = lo;
         if (k < K) {
-            lo = ldg_stream(Bt + (size_t)r_lo * K + k);
-            hi = ldg_stream(Bt + (size_t)r_hi * K + k);
+            lo = ldg_stream(Bt + (size_t)r_lo * ldb + k);
+            hi = ldg_stream(Bt + (size_t)r_hi * ldb + k);
             if (has_x) xv = ld_act(A + (size_t)g * K + k);
         }
         mma_16816(acc, lo.x, hi.x, lo.y, hi.y, xv.x, xv.y);
@@ -150,7 +150,8 @@ gemv_nt_mma_kernel(const __half* A, const __half* __restrict__ Bt, __half* C, in
                 float s = 0.f;
 #pragma unroll
                 for (int w = 0; w < WARPS; ++w) s += partial[w][r][m];
-                C[(size_t)m * N + n] = __float2half_rn(md_epilogue_value(ep, s, m, n, N));
+                if (ep.out_f32) ep.out_f32[(size_t)m * N + n] = s;
+                else C[(size_t)m * N + n] = __float2half_rn(md_epilogue_value(ep, s, m, n, N));
             }
         }
         return;
@@ -179,7 +180,8 @@ gemv_nt_mma_kernel(const __half* A, const __half* __restrict__ Bt, __half* C, in
                     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote));
                     s += v;
                 }
-                C[(size_t)m * N + n] = __float2half_rn(md_epilogue_value(ep, s, m, n, N));
+                if (ep.out_f32) ep.out_f32[(size_t)m * N + n] = s;
+                else C[(size_t)m * N + n] = __float2half_rn(md_epilogue_value(ep, s, m, n, N));
             }
         }
     }
@@ -191,7 +193,9 @@ gemv_nt_mma_kernel(const __half* A, const __half* __restrict__ Bt, __half* C, in
 }  // namespace
 
 int md_launch_gemv_nt(md_ctx* ctx, const __half* a, const __half* bt, __half* c, size_t M, size_t N, size_t K,
-                      const md_epilogue& ep) {
+                      const md_epilogue& ep, size_t ldb) {
+    if (ldb == 0) ldb = K;
+    if (ldb < K || (ldb % 8) != 0) return md_fail(ctx, MD_ERR_UNSUPPORTED, "gemv_nt: the weight row stride must be >= K and a multiple of 8");
     if (M == 0 || M > 8 || (K % 8) != 0 || K == 0 || N == 0)
         return md_fail(ctx, MD_ERR_UNSUPPORTED, "gemv_nt needs 1 <= M <= 8 and K %% 8 == 0 (M=%zu K=%zu)", M, K);
     if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(bt)) & 15)
@@ -211,10 +215,10 @@ int md_launch_gemv_nt(md_ctx* ctx, const __half* a, const __half* bt, __half* c,
     // start while its predecessor drains and orders itself with griddepcontrol.wait.  Only valid when
     // the weights are not produced by an earlier kernel of the stream (true for registered weights).
     // K splits (a cluster along y).  Clusters start more slowly than plain CTAs, so a split pays only where a
-    // matrix has at most one CTA per SM and long rows (the 8192 -> 2048 projection: 10.3 -> 8.4 us with two splits;
+    // matrix has at most one CTA per SM and rows of K >= 8192 (the 8192 -> 2048 projection: 10.3 -> 8.4 us with two splits;
     // four were slower again, and every shape with more rows lost).  md_set_option("gemv_ksplit") fixes the count.
     int ksplit = ctx->gemv_ksplit;
-    if (ksplit <= 0) ksplit = (grid <= (unsigned)ctx->sm_count && K >= 4096) ? 2 : 1;
+    if (ksplit <= 0) ksplit = (grid <= (unsigned)ctx->sm_count && K >= 8192) ? 2 : 1;
     while (ksplit > 1 && (size_t)(K / 32) < (size_t)ksplit) ksplit /= 2;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, (unsigned)ksplit);
@@ -235,12 +239,12 @@ int md_launch_gemv_nt(md_ctx* ctx, const __half* a, const __half* bt, __half* c,
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    const int Mi = (int)M, Ni = (int)N, Ki = (int)K;
+    const int Mi = (int)M, Ni = (int)N, Ki = (int)K, ldbi = (int)ldb;
     cudaError_t le = cudaSuccess;
 #define MD_GEMV_CASE(id, W, U)                                                          \
     case id:                                                                            \
         cfg.blockDim = dim3(W * 32);                                                    \
-        le = cudaLaunchKernelEx(&cfg, gemv_nt_mma_kernel<W, U>, a, bt, c, Mi, Ni, Ki, ep); \
+        le = cudaLaunchKernelEx(&cfg, gemv_nt_mma_kernel<W, U>, a, bt, c, Mi, Ni, Ki, ldbi, ep); \
         break;
     switch (variant) {
         MD_GEMV_CASE(1, 4, 8)

@@ -234,6 +234,10 @@ int md_destroy(md_ctx* ctx) {
     if (ctx->flags_host) cudaFreeHost(ctx->flags_host);
     if (ctx->mirror_host) cudaFreeHost(ctx->mirror_host);
     if (ctx->side_stream) cudaStreamDestroy(ctx->side_stream);
+    for (auto st : ctx->mlp_stream)
+        if (st) cudaStreamDestroy(st);
+    for (auto ev : ctx->ev_mlp)
+        if (ev) cudaEventDestroy(ev);
     if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
     if (ctx->ev_side) cudaEventDestroy(ctx->ev_side);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
@@ -326,6 +330,11 @@ int md_set_option(md_ctx* ctx, const char* key, long value) {
     if (!strcmp(key, "pdl")) { ctx->pdl = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "prefill_fork")) { ctx->prefill_fork = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "decode_fork")) { ctx->decode_fork = value ? 1 : 0; return MD_OK; }
+    if (!strcmp(key, "decode_mlp_split")) {
+        MD_NEED(ctx, value == 0 || value == 2 || value == 4, "decode_mlp_split must be 0, 2 or 4");
+        ctx->decode_mlp_split = (int)value;
+        return MD_OK;
+    }
     if (!strcmp(key, "skinny")) { ctx->skinny = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "skinny_splits")) {
         MD_NEED(ctx, value >= 0 && value <= 16, "skinny_splits must be 0 (automatic) or 1..16 (rounded down to 1, 2, 4 or 8)");

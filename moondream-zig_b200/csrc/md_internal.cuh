@@ -88,8 +88,10 @@ struct md_ctx {
     int prefill_fork = 1;       // md_set_option("prefill_fork"): prefill layers run the MLP beside the attention
     int decode_split_ln = 5;    // md_set_option("decode_split_ln"): from this many rows on a decode step runs the LayerNorm once
     int decode_fork = 1;        // md_set_option("decode_fork"): a decode layer runs as two concurrent kernel chains
+    int decode_mlp_split = 2;   // md_set_option("decode_mlp_split"): single-request decode runs the MLP as 2 or 4 chains (0 = one)
     cudaStream_t side_stream = nullptr;  // second chain of the forked decode layer
-    cudaEvent_t ev_fork = nullptr, ev_side = nullptr;
+    cudaStream_t mlp_stream[3] = {};     // further chains when the MLP is split (its first part runs on side_stream)
+    cudaEvent_t ev_fork = nullptr, ev_side = nullptr, ev_mlp[3] = {};
     int attn_tc = -1;        // md_set_option("attn_tc"): -1 auto, 0 mma.sync attention only, 1 tcgen05 attention only
 };
 
@@ -168,6 +170,12 @@ struct md_epilogue {
     const __half* residual2 = nullptr;  // [M,N] or null, added after `residual`
     int gelu = 0;
     int residual_rows = 0;              // > 0: row m reads residual row m % residual_rows (broadcast over batches)
+    // GEMV kernels only (the decode layer whose MLP runs as two half-width chains):
+    float* out_f32 = nullptr;           // store the raw f32 sums [M,N] here instead of the f16 result (no glue)
+    const float* parts = nullptr;       // n_parts f32 partial products [M,N] (part_stride floats apart) of another
+    int n_parts = 0;                    //   projection and its bias: f16(f16(sum of the parts) + bias2) is added where
+    int part_stride = 0;                //   `residual` would be
+    const __half* bias2 = nullptr;
 };
 
 // Column-split GEMM: finished C chunks are also stored into the other GPUs' buffers.
@@ -180,7 +188,7 @@ struct md_push {
 
 // gemv.cu: C[M,N] = A[M,K] . Bt[N,K]^T for M <= 8, K % 8 == 0.
 int md_launch_gemv_nt(md_ctx* ctx, const __half* a, const __half* bt, __half* c, size_t M, size_t N, size_t K,
-                      const md_epilogue& ep);
+                      const md_epilogue& ep, size_t ldb = 0);  // ldb: row stride of Bt in elements (0 = K)
 // gemv_fused.cu: the decode layer's GEMVs fused with the glue around them (M <= 8 rows).
 //   ln_dual: y = LayerNorm(hidden); out1 = y W1^T + b1; out2 = gelu(y W2^T + b2)      (K = 2048)
 //   dual_k : hidden += (x1 W1^T + b1) + (x2 W2^T + b2), with the reference's f16 rounding points
@@ -306,6 +314,13 @@ __device__ __forceinline__ float md_epilogue_value(const md_epilogue& ep, float 
     if (ep.residual) {
         const int rm = ep.residual_rows > 0 ? m % ep.residual_rows : m;
         v = md_round_f16(v + __half2float(__ldcg(ep.residual + (size_t)rm * N + n)));
+    }
+    if (ep.parts) {
+        // the other projection arrives as parts of its K sum: one rounding of the sum, then its bias
+        float r = 0.f;
+        for (int i = 0; i < ep.n_parts; ++i) r += __ldcg(ep.parts + (size_t)i * ep.part_stride + (size_t)m * N + n);
+        r = md_round_f16(md_round_f16(r) + __half2float(ep.bias2[n]));
+        v = md_round_f16(v + r);
     }
     if (ep.residual2) v = md_round_f16(v + __half2float(__ldcg(ep.residual2 + (size_t)m * N + n)));
     return v;

@@ -114,6 +114,7 @@ struct md_text_request {
     int* pos_dev = nullptr;
     // activations of one forward over `rows` rows
     DevPtr hidden, ln, qkv, attn, attn_out, fc1, logits, ln_last;
+    DevPtr mlp_part;  // up to four f32 [8, dim] partial products of fc2 (the decode layer whose MLP runs as two half-width chains)
     // device-side generation state
     DevPtr cur_token, sampled, tokens_out, forced, step, logits_all, pos_ptrs;
     md_graph* graph = nullptr;
@@ -176,6 +177,7 @@ int ensure_rows(md_text_request* r, size_t rows) {
     MD_TRY(r->fc1.ensure(ctx, rows * w.hidden * 2));
     MD_TRY(r->logits.ensure(ctx, 8 * w.vocab * 2));
     MD_TRY(r->ln_last.ensure(ctx, 8 * w.dim * 2));
+    MD_TRY(r->mlp_part.ensure(ctx, 4 * 8 * w.dim * sizeof(float)));
     return MD_OK;
 }
 
@@ -184,6 +186,7 @@ int ensure_rows(md_text_request* r, size_t rows) {
 //   decode : rows = batch requests, one token each, positions in device memory
 struct LayerIO {
     __half *hidden, *ln, *qkv, *attn, *attn_out, *fc1;
+    float* mlp_part;
 };
 
 // Attention of one decode step: every request's new token against its own cache, one launch for the batch.
@@ -225,6 +228,51 @@ int text_layer(md_text_model* m, size_t layer, const LayerIO& io, size_t rows, b
             }
             cudaStream_t main_stream = ctx->stream;
             MD_CUDA(ctx, cudaEventRecord(ctx->ev_fork, main_stream));            // hidden of the previous layer is final
+            const int parts = ctx->decode_mlp_split;
+            if (rows == 1 && (parts == 2 || parts == 4) && io.mlp_part && (F % (32 * parts)) == 0) {
+                // Single request: the MLP chain (fc1 -> fc2, 67 MB) is the longest path of the layer, so it runs as
+                // 2 or 4 independent chains: chain h computes rows h*F/parts.. of fc1 (+ bias + GELU) and then the part
+                // of fc2's K sum over those features, as raw f32 sums; the out-projection's epilogue adds the parts,
+                // rounds once, adds fc2's bias and continues as before (mlp_out = f16(f16(acc) + b)).
+                const size_t Fh = F / parts;
+                int st = MD_OK;
+                for (int h = 0; h < parts && st == MD_OK; ++h) {
+                    if (h > 0 && !ctx->mlp_stream[h - 1]) {
+                        MD_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->mlp_stream[h - 1], cudaStreamNonBlocking));
+                        MD_CUDA(ctx, cudaEventCreateWithFlags(&ctx->ev_mlp[h - 1], cudaEventDisableTiming));
+                    }
+                    cudaStream_t ss = h ? ctx->mlp_stream[h - 1] : ctx->side_stream;
+                    if (cudaStreamWaitEvent(ss, ctx->ev_fork, 0) != cudaSuccess) st = md_fail(ctx, MD_ERR_CUDA, "cudaStreamWaitEvent failed");
+                    ctx->stream = ss;
+                    if (st == MD_OK)
+                        st = md_launch_gemv_ln_dual(ctx, io.hidden, H(m->ln_w[layer]), H(m->ln_b[layer]), eps_of(w.eps_f16),
+                                                    H(m->wfc1[layer]) + h * Fh * D, H(m->bfc1[layer]) + h * Fh, io.fc1 + h * Fh,
+                                                    Fh, nullptr, nullptr, nullptr, 0, rows, D, nullptr, true);
+                    if (st == MD_OK) {
+                        md_epilogue e_part;
+                        e_part.out_f32 = io.mlp_part + h * 8 * D;
+                        st = md_launch_gemv_nt(ctx, io.fc1 + h * Fh, H(m->wfc2[layer]) + h * Fh, io.attn_out, rows, D, Fh, e_part, F);
+                    }
+                    if (st == MD_OK && cudaEventRecord(h ? ctx->ev_mlp[h - 1] : ctx->ev_side, ss) != cudaSuccess)
+                        st = md_fail(ctx, MD_ERR_CUDA, "cudaEventRecord on a side stream failed");
+                }
+                ctx->stream = main_stream;
+                MD_TRY(st);
+                MD_TRY(md_launch_gemv_ln_dual(ctx, io.hidden, H(m->ln_w[layer]), H(m->ln_b[layer]), eps_of(w.eps_f16),
+                                              H(m->wqkv[layer]), H(m->bqkv[layer]), io.qkv, 3 * D, nullptr, nullptr, nullptr, 0,
+                                              rows, D));
+                MD_TRY(decode_attention(m, layer, io, rows, reqs));
+                MD_CUDA(ctx, cudaStreamWaitEvent(main_stream, ctx->ev_side, 0));
+                for (int h = 1; h < parts; ++h) MD_CUDA(ctx, cudaStreamWaitEvent(main_stream, ctx->ev_mlp[h - 1], 0));
+                md_epilogue e_out;
+                e_out.bias = H(m->bout[layer]);
+                e_out.parts = io.mlp_part;
+                e_out.n_parts = parts;
+                e_out.part_stride = (int)(8 * D);
+                e_out.bias2 = H(m->bfc2[layer]);
+                e_out.residual2 = io.hidden;    // updated in place: every element is read and written by one thread
+                return md_launch_gemv_nt(ctx, io.attn, H(m->wout[layer]), io.hidden, rows, D, D, e_out);
+            }
             MD_CUDA(ctx, cudaStreamWaitEvent(ctx->side_stream, ctx->ev_fork, 0));
             ctx->stream = ctx->side_stream;
             int st = md_launch_gemv_ln_dual(ctx, io.hidden, H(m->ln_w[layer]), H(m->ln_b[layer]), eps_of(w.eps_f16),
@@ -328,7 +376,7 @@ int text_layer(md_text_model* m, size_t layer, const LayerIO& io, size_t rows, b
 
 LayerIO io_of(md_text_request* r) {
     return LayerIO{r->hidden.as<__half>(), r->ln.as<__half>(), r->qkv.as<__half>(), r->attn.as<__half>(),
-                   r->attn_out.as<__half>(), r->fc1.as<__half>()};
+                   r->attn_out.as<__half>(), r->fc1.as<__half>(), r->mlp_part.as<float>()};
 }
 
 // lm_head over `rows` hidden rows (text_model.zig:325-345 takes the last row of one request; the

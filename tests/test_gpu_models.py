@@ -208,6 +208,41 @@ def test_text_forked_decode_layer_matches_the_three_kernel_layer(ctx, models_mod
     gpu.close()
 
 
+@pytest.mark.parametrize("parts", [2, 4])
+def test_text_split_mlp_decode_layer_matches_the_single_mlp_chain(ctx, oracle, models_mod, parts):
+    """Option decode_mlp_split (default 2, single request): the MLP as 2 or 4 independent chains whose f32 partial sums
+    of fc2 meet in the out-projection's epilogue (one rounding of the sum, then the bias, as the reference rounds
+    fc2's output once).  Against the single MLP chain (logits within the parity bar) and against the oracle."""
+    w = text_weights(4012, n_layers=3, hidden=8192, vocab=4096)
+    gpu = models_mod.TextModel(ctx, w)
+    ref = oracle.TextModel(w)
+    rng = np.random.default_rng(12)
+    ids = rng.integers(0, 4096, 33)
+    forced = np.arange(1, 7, dtype=np.uint32) * 59 % 4096
+    res = {}
+    for split in (parts, 0):
+        ctx.set_option("decode_mlp_split", split)
+        try:
+            req = gpu.request()
+            _, _, tok = gpu.forward(req, ref.embed(ids))
+            n0 = ctx.launch_count()
+            res[split] = gpu.generate(req, 5, 6, forced=forced, want_logits=True)
+            res[split] = res[split] + (ctx.launch_count() - n0,)
+            req.close()
+        finally:
+            ctx.set_option("decode_mlp_split", 2)
+    res[1] = res[parts]
+    assert res[1][2] > res[0][2]          # more kernels per layer than the five of one MLP chain: the split form ran
+    ref.decoder(ref.embed(ids))
+    cur = 5
+    for i in range(6):
+        l_ref = ref.lm_head(ref.decoder(ref.embed([cur])))
+        assert_close_ref(res[1][1][i], l_ref, f"split MLP vs oracle, step {i}")
+        assert_close_ref(res[1][1][i], res[0][1][i], f"split MLP vs single chain, step {i}", rel=5e-3)
+        cur = int(forced[i])
+    gpu.close()
+
+
 @pytest.mark.parametrize("cluster_merge", [1, 0], ids=["cluster_merge", "scratch_merge"])
 def test_text_batched_decode_equals_single_requests(ctx, models_mod, cluster_merge):
     """One attention launch serves the whole batch (grid z = request), each request at its own position; both ways
