@@ -94,6 +94,10 @@ int md_set_gemm_mode(md_ctx* ctx, int mode);
  *                   cluster stream K / S each and add their sums through distributed shared memory)
  *   "tc_block_n"    0 = automatic, 64 / 128 / 256 = fixed tile width of the tcgen05 GEMM (128-row tiles),
  *                   512 = the 256 x 256 tile
+ *   "tc_pair"       -1 (default) = shapes that would take the 128 x 256 tile and have more than 256 rows run
+ *                   256 x 256 tiles on CTA pairs (tcgen05 cta_group::2: each CTA of a cluster of two loads its 128 rows
+ *                   of A and half of the B tile, one thread issues the MMAs for both); 1 = every tcgen05 GEMM does;
+ *                   0 = single-CTA tiles only.  Same results bit for bit
  *   "skinny"        1 (default) = products with 8 < M <= 64 rows take the swapped-operand split-K kernel (weights on
  *                   the MMA's M side, K split over the CTAs of a thread-block cluster, ~2 CTAs per SM, partials
  *                   added through distributed shared memory)
@@ -118,7 +122,8 @@ int md_set_gemm_mode(md_ctx* ctx, int mode);
 int md_set_option(md_ctx* ctx, const char* key, long value);
 /* Read back a knob or a diagnostic (no counterpart in the reference): "gemv_variant", "tc_block_n", "pdl", and
  *   "last_tc_tile"  the tile the last tcgen05 GEMM launch of this context used: 64 / 128 / 256 = width of a
- *                   128-row tile, 512 = the 256 x 256 tile, 1000 + S = the skinny kernel with S splits of K,
+ *                   128-row tile, 512 = the 256 x 256 tile, 2256 = a 256 x 256 tile on a CTA pair, 1000 + S = the
+ *                   skinny kernel with S splits of K,
  *                   0 = none yet.  Lets a test see which tile the
  *                   cost model picked for a shape (e.g. for the column-split GEMM with peers). */
 int md_get_option(md_ctx* ctx, const char* key, long* value_out);

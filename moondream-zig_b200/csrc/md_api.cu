@@ -342,6 +342,7 @@ int md_set_option(md_ctx* ctx, const char* key, long value) {
         return MD_OK;
     }
     if (!strcmp(key, "attn_tc")) { ctx->attn_tc = value < 0 ? -1 : value ? 1 : 0; return MD_OK; }
+    if (!strcmp(key, "tc_pair")) { ctx->tc_pair = value < 0 ? -1 : (value ? 1 : 0); return MD_OK; }
     if (!strcmp(key, "tc_block_n")) {
         MD_NEED(ctx, value == 0 || value == 64 || value == 128 || value == 256 || value == 512,
                 "tc_block_n must be 0, 64, 128, 256 or 512 (512 = the 256 x 256 tile)");

@@ -79,6 +79,7 @@ struct md_ctx {
     int gemv_variant = 0;    // md_set_option("gemv_variant")
     int gemv_ksplit = 0;     // md_set_option("gemv_ksplit"): 0 = automatic, 1 / 2 / 4 / 8 = K splits of the GEMV kernel
     int tc_block_n = 0;      // md_set_option("tc_block_n")
+    int tc_pair = -1;        // md_set_option("tc_pair"): 1 = every tcgen05 GEMM runs on CTA pairs, 0 = never, -1 = by shape
     int last_tc_tile = 0;    // md_get_option("last_tc_tile"): tile of the last tcgen05 GEMM launch (64/128/256, 512 = 256 x 256)
     int decode_cluster_ok = -1;    // -1 unknown, 0/1: 16-CTA clusters usable for the decode attention merge
     int decode_cluster_mode = -1;  // md_set_option("decode_cluster"): 0 forces the scratch-based merge
@@ -221,6 +222,10 @@ bool md_gemm_skinny_supported(const void* a, const void* b, const void* c, size_
 int md_launch_gemm_skinny(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
                           int b_layout, const md_epilogue& ep);
 
+// gemm_pair.cu: 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2); same operand rules as md_launch_gemm_tc
+int md_launch_gemm_pair(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K, int b_layout,
+                        const md_epilogue& ep);
+
 // gemm_tc.cu: a kernel whose bounded wait runs out on purpose (md_selftest_bounded_wait)
 int md_launch_selftest_wait(md_ctx* ctx, unsigned limit_ms);
 
@@ -284,15 +289,17 @@ __device__ __forceinline__ float md_gelu_f32(float v) {
     return 0.5f * v * (1.0f + tanhf(inner));
 }
 
-// The same GELU with tanh(t) = 1 - 2 / (exp(2t) + 1) on the fast exp/divide units, for the GEMM
-// epilogues where tanhf would cost more than the tile's MMAs.  Absolute error < 1e-6, far below the
-// f16 rounding applied to the result.
+// The same GELU with the hardware tanh (tanh.approx.f32, one special-function op; absolute error about 5e-4 on the
+// tanh, i.e. at most 0.5 * |x| * 5e-4 on the result, a fraction of the f16 spacing at |x| and far inside the parity
+// bar), for the GEMM epilogues where tanhf, or an exp and a divide, would cost more than the tile's MMAs: with the
+// exp / divide form the bias + GELU epilogue of a 128 x 256 tile took longer than its 18 k-blocks of MMAs.
 __device__ __forceinline__ float md_gelu_fast_f32(float v) {
     const float c = 0.7978515625f, a = 0.044708251953125f;
     const float inner = c * (v + a * (v * v * v));
-    const float e = __expf(2.0f * fminf(fmaxf(inner, -15.0f), 15.0f));  // tanh(+-15) = +-1 to 2e-13
-    const float th = 1.0f - __fdividef(2.0f, e + 1.0f);
-    return 0.5f * v * (1.0f + th);
+    float th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(inner));
+    const float hv = 0.5f * v;
+    return fmaf(hv, th, hv);
 }
 
 // acc (f32 accumulator) -> f16 value after the fused glue, as f32 holding an f16-representable value.

@@ -282,6 +282,41 @@ def test_skinny_gemm(ctx, oracle, m, k, n, layout, splits):
         b.free()
 
 
+@pytest.mark.parametrize("layout", [0, 1])
+@pytest.mark.parametrize("m,k,n", [(256, 64, 256), (300, 520, 1000), (1024, 1152, 4304), (129, 8, 8), (100, 64, 264),
+                                   (2304, 2048, 2048)])
+def test_gemm_on_cta_pairs(ctx, oracle, m, k, n, layout):
+    """Option tc_pair: 256 x 256 tiles computed by two CTAs of a cluster (tcgen05 cta_group::2), each loading its own
+    rows of A and its half of the B tile.  Ragged M, N and K, a second CTA with one row (M = 129) or none (M = 100),
+    more tiles than pairs, the fused bias / GELU / residual epilogue,
+    three launches in a row; against the oracle, and bit for bit against the single-CTA kernel (same k order)."""
+    rng = np.random.default_rng(m + n + k + layout)
+    a = f16_normal(rng, (m, k))
+    w_kn = f16_normal(rng, (k, n), 0.05)
+    bias, res = f16_normal(rng, (n,), 0.5), f16_normal(rng, (m, n))
+    w = w_kn if layout == 0 else np.ascontiguousarray(w_kn.T)
+    ref = oracle.hgemm_nn(a, w_kn) if layout == 0 else oracle.hgemm_nt(a, w)
+    ref = oracle.add(oracle.gelu(oracle.bias_add(ref, bias)), res)
+    da, dw, db, dr = ctx.upload(a), ctx.upload(w), ctx.upload(bias), ctx.upload(res)
+    outs = {}
+    for pair in (1, 0):
+        ctx.set_option("tc_pair", pair)
+        try:
+            out = ctx.alloc((m, n))
+            for _ in range(3):
+                ctx.hgemm_fused(da, dw, out, m, n, k, layout, bias=db, gelu=True, residual=dr)
+            ctx.sync()
+            assert (ctx.get_option("last_tc_tile") == 2256) == (pair == 1)
+            outs[pair] = out.numpy()
+            out.free()
+        finally:
+            ctx.set_option("tc_pair", -1)
+    assert_close_ref(outs[1], ref, "CTA-pair GEMM")
+    np.testing.assert_array_equal(outs[1], outs[0])
+    for b in (da, dw, db, dr):
+        b.free()
+
+
 def test_linearity_at_full_size(ctx):
     """Size-independent property at the lm_head size: (a1 + a2) W == a1 W + a2 W up to rounding,
     and a one-hot activation selects a weight column exactly."""
