@@ -249,42 +249,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const int cq = col0 + 8 * q;
-                        float v[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[8 * q + j]);
-                        if (any_glue && row < M && cq < N) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) v[j] = md_round_f16(v[j]);
-                            if (ep.bias) {
-                                float b[8];
-                                load8(ep.bias + cq, b);
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) v[j] = md_round_f16(v[j] + b[j]);
-                            }
-                            if (ep.gelu) {
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) v[j] = md_round_f16(md_gelu_fast_f32(v[j]));
-                            }
-                            if (ep.residual) {
-                                const int rm = ep.residual_rows > 0 ? row % ep.residual_rows : row;
-                                float b[8];
-                                load8(ep.residual + (size_t)rm * N + cq, b);
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) v[j] = md_round_f16(v[j] + b[j]);
-                            }
-                            if (ep.residual2) {
-                                float b[8];
-                                load8(ep.residual2 + (size_t)row * N + cq, b);
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) v[j] = md_round_f16(v[j] + b[j]);
-                            }
-                        }
                         uint32_t pk[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            __half2 hh = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
-                            pk[j] = *reinterpret_cast<uint32_t*>(&hh);
-                        }
+                        epilogue_glue8(r + 8 * q, ep, row, cq, N, any_glue && row < M && cq < N, pk);
                         const int chunk = (h * 4 + q) ^ (lane & 7);  // 128-byte swizzle, matches the store map
                         *reinterpret_cast<uint4*>(out_row + chunk * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                     }

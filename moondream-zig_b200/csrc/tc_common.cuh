@@ -141,6 +141,48 @@ __device__ __forceinline__ void load8(const __half* p, float (&f)[8]) {
     }
 }
 
+// The fused glue of a GEMM epilogue on 8 consecutive output columns of one row: f32 accumulators in, four packed
+// half2 out.  Every step keeps the reference's rounding point (one rounding to f16 after the product, after the
+// bias, after the GELU, after each residual).  Sums of two f16 values are formed with packed f16 adds: an f16 + f16
+// sum is exact in f32, so f16(f32(a) + f32(b)) and the correctly rounded f16 add are the same number; only the GELU
+// needs f32 arithmetic.  (cq, row) is the position of the first column; N % 8 == 0 and 16-byte aligned operands.
+__device__ __forceinline__ void epilogue_glue8(const uint32_t* acc_bits, const md_epilogue& ep, int row, int cq, int N,
+                                               bool apply, uint32_t (&pk)[4]) {
+    __half2 h[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(__uint_as_float(acc_bits[2 * j]), __uint_as_float(acc_bits[2 * j + 1]));
+    if (apply) {
+        if (ep.bias) {
+            const uint4 u = *reinterpret_cast<const uint4*>(ep.bias + cq);
+            const __half2* b = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __hadd2(h[j], b[j]);
+        }
+        if (ep.gelu) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 x = __half22float2(h[j]);
+                h[j] = __floats2half2_rn(md_gelu_fast_f32(x.x), md_gelu_fast_f32(x.y));
+            }
+        }
+        if (ep.residual) {
+            const int rm = ep.residual_rows > 0 ? row % ep.residual_rows : row;
+            const uint4 u = *reinterpret_cast<const uint4*>(ep.residual + (size_t)rm * N + cq);
+            const __half2* b = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __hadd2(h[j], b[j]);
+        }
+        if (ep.residual2) {
+            const uint4 u = *reinterpret_cast<const uint4*>(ep.residual2 + (size_t)row * N + cq);
+            const __half2* b = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __hadd2(h[j], b[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) pk[j] = *reinterpret_cast<uint32_t*>(&h[j]);
+}
+
 // Shared-memory matrix descriptor (version 1, sm_100) as built by desc_lo / desc_hi:
 //   bits 0-13 address >> 4, 16-29 leading byte offset >> 4, 32-45 stride byte offset >> 4, 46 version,
 //   61-63 swizzle (2 = 128-byte, 4 = 64-byte, 6 = 32-byte, 0 = none).
