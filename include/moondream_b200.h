@@ -101,11 +101,7 @@ int md_set_gemm_mode(md_ctx* ctx, int mode);
  *   "skinny"        1 (default) = products with 8 < M <= 64 rows take the swapped-operand split-K kernel (weights on
  *                   the MMA's M side, K split over the CTAs of a thread-block cluster, ~2 CTAs per SM, partials
  *                   added through distributed shared memory)
- *   "skinny_wide"   1 (default) = products with 64 < M <= 1024 rows whose output is too narrow for ordinary tiles to
- *                   fill the machine take the same kernel with 256 activation rows per tile and K split over a
- *                   cluster of 2..8 CTAs, one CTA per SM
- *   "skinny_splits" 0 = automatic, else the number of K splits of those kernels (M <= 64: rounded down to 1, 2, 4
- *                   or 8; the wide form: any count 1..8)
+ *   "skinny_splits" 0 = automatic, else the number of K splits of that kernel (rounded down to 1, 2, 4 or 8)
  *   "pdl"           1 = launch the GEMV kernels with programmatic dependent launch: a kernel starts
  *                   streaming its weights while its predecessor on the stream drains.  Only for streams
  *                   on which no earlier kernel writes the weight matrices (registered weights).
@@ -127,7 +123,7 @@ int md_set_option(md_ctx* ctx, const char* key, long value);
 /* Read back a knob or a diagnostic (no counterpart in the reference): "gemv_variant", "tc_block_n", "pdl", and
  *   "last_tc_tile"  the tile the last tcgen05 GEMM launch of this context used: 64 / 128 / 256 = width of a
  *                   128-row tile, 512 = the 256 x 256 tile, 2256 = a 256 x 256 tile on a CTA pair, 1000 + S = the
- *                   skinny kernel with S splits of K, 3000 + S = its wide form,
+ *                   skinny kernel with S splits of K,
  *                   0 = none yet.  Lets a test see which tile the
  *                   cost model picked for a shape (e.g. for the column-split GEMM with peers). */
 int md_get_option(md_ctx* ctx, const char* key, long* value_out);

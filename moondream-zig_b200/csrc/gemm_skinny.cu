@@ -28,25 +28,21 @@ namespace {
 using namespace tc;
 
 constexpr int TILE_N = 128;          // weight rows (output columns) per CTA
+constexpr int XN = 64;               // activation rows covered by the MMA's N side (M <= 64)
 constexpr int BLOCK_K = 64, UMMA_K = 16;
 constexpr int W_STAGE_BYTES = TILE_N * BLOCK_K * 2;   // 16 KiB
+constexpr int X_STAGE_BYTES = XN * BLOCK_K * 2;       // 8 KiB
+constexpr int STAGE_BYTES = W_STAGE_BYTES + X_STAGE_BYTES;
 constexpr int STAGES = 4;
 constexpr int THREADS = 192;
+constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
+constexpr uint32_t TMEM_COLS = 64;
 constexpr int MAX_SPLITS = 8;          // portable cluster size
-// XN = activation rows covered by the MMA's N side: 64 (M <= 64, two CTAs per SM) or 256 (the wide form for a few
-// hundred rows whose output is too narrow to fill the machine with ordinary tiles, one CTA per SM)
-__host__ __device__ constexpr int x_stage_bytes(int xn) { return xn * BLOCK_K * 2; }
-__host__ __device__ constexpr int stage_bytes(int xn) { return W_STAGE_BYTES + x_stage_bytes(xn); }
-__host__ __device__ constexpr int smem_bytes(int xn) { return 1024 + STAGES * stage_bytes(xn) + 256; }
 
-template <bool W_MN_MAJOR, int XN>
-__global__ void __launch_bounds__(THREADS, XN == 64 ? 2 : 1)
+template <bool W_MN_MAJOR>
+__global__ void __launch_bounds__(THREADS, 2)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, __half* C, int M,
                    int N, int K, int kb_per_split, int splits, md_epilogue ep, md_devflags* flags) {
-    constexpr int X_STAGE_BYTES = x_stage_bytes(XN), STAGE_BYTES = stage_bytes(XN);
-    constexpr uint32_t TMEM_COLS = XN;
-    static_assert(XN == 64 || XN == 256, "XN");
-    static_assert(XN * TILE_N * 4 <= STAGES * STAGE_BYTES, "the f32 partial tile reuses the ring");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -61,8 +57,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x, split = blockIdx.y;
     const int n0 = tile * TILE_N;
-    const int m_base = blockIdx.z * XN;          // first activation row of this CTA's tile
-    const int m_tile = min(XN, M - m_base);      // its valid rows
     const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
     const int kb0 = split * kb_per_split;
     const int kbs = max(0, min(kb_per_split, num_kb - kb0));   // 0 for a split past the end of K: it contributes zeros
@@ -107,7 +101,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 }
             };
             auto load_x = [&](int stage, int kb) {
-                tma_load_2d(smem_x + stage * X_STAGE_BYTES, &tm_x, bar_full + 8 * stage, kb * BLOCK_K, m_base);
+                tma_load_2d(smem_x + stage * X_STAGE_BYTES, &tm_x, bar_full + 8 * stage, kb * BLOCK_K, 0);
             };
             // the first ring of weight tiles does not depend on the predecessor kernel (registered weights are
             // never written on the stream): request it before waiting for the activations' producer
@@ -132,7 +126,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         // ------------------------------------------------------------ MMA issuer
         md_pdl_wait();
         if (lane == 0) {
-            // D[128 weight rows, XN activation rows] (f32), A = weights (K-major, or MN-major for the [K,N] layout),
+            // D[128 weight rows, 64 activation rows] (f32), A = weights (K-major, or MN-major for the [K,N] layout),
             // B = activations (K-major)
             const uint32_t idesc = (1u << 4) | ((W_MN_MAJOR ? 1u : 0u) << 15) | ((uint32_t)(XN >> 3) << 17) |
                                    ((uint32_t)(TILE_N >> 4) << 24);
@@ -167,7 +161,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         if (kbs > 0) {
             mbar_wait(bar_done, 0, abort_flag, flags, 13);
             tc_fence_after();
-#pragma unroll 2
+#pragma unroll
             for (int h = 0; h < XN / 32; ++h) {
                 uint32_t r[32];
                 tc_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(h * 32), r);
@@ -195,9 +189,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const int et = threadIdx.x - 64;
         const int c4 = (et & 31) * 4, n = n0 + c4;
         const uint32_t tile_addr = base;   // shared-memory address of tile_f32 (same offset in every CTA of the cluster)
-        auto finish = [&](int ml, const float4& acc) {   // ml = row inside the tile
-            if (n >= N || ml >= m_tile) return;   // N % 8 == 0: a piece of four columns is inside or outside C
-            const int m = m_base + ml;
+        auto finish = [&](int m, const float4& acc) {
+            if (n >= N || m >= M) return;   // N % 8 == 0: a piece of four columns is inside or outside C
             const __half2 lo = __floats2half2_rn(md_epilogue_value(ep, acc.x, m, n, N), md_epilogue_value(ep, acc.y, m, n + 1, N));
             const __half2 hi = __floats2half2_rn(md_epilogue_value(ep, acc.z, m, n + 2, N), md_epilogue_value(ep, acc.w, m, n + 3, N));
             uint2 pk;
@@ -206,8 +199,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             *reinterpret_cast<uint2*>(C + (size_t)m * N + n) = pk;
         };
         // two turns at a time: all loads of both turns are issued before the first sum
-        for (int ma = split + splits * (et >> 5); ma < m_tile; ma += splits * 8) {
-            const int mb = ma + splits * 4;   // may be past the tile's rows (zeros or stale sums there: never stored)
+        for (int ma = split + splits * (et >> 5); ma < M; ma += splits * 8) {
+            const int mb = ma + splits * 4;   // may be >= M (rows past M hold zeros or stale sums: never stored)
             float4 pa[8], pb[8];
             const uint32_t la = tile_addr + (uint32_t)((ma * TILE_N + c4) * 4);
             const uint32_t lb = tile_addr + (uint32_t)(((mb < XN ? mb : ma) * TILE_N + c4) * 4);
@@ -254,55 +247,43 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 int md_make_map_2d(md_ctx* ctx, CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,
                    uint32_t box_outer, uint64_t ld);
 
-static bool skinny_operands_ok(const void* a, const void* b, const void* c, size_t N, size_t K) {
-    if (N == 0 || K == 0) return false;
+bool md_gemm_skinny_supported(const void* a, const void* b, const void* c, size_t M, size_t N, size_t K) {
+    if (M <= 8 || M > (size_t)XN || N == 0 || K == 0) return false;
     if ((K % 8) != 0 || (N % 8) != 0) return false;  // row strides must be multiples of 16 bytes for TMA
     if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) return false;
     if (reinterpret_cast<uintptr_t>(c) & 7) return false;  // 8-byte stores of four outputs
     return N <= (1u << 30) && K <= (1u << 30);
 }
 
-bool md_gemm_skinny_supported(const void* a, const void* b, const void* c, size_t M, size_t N, size_t K) {
-    return M > 8 && M <= 64 && skinny_operands_ok(a, b, c, N, K);
-}
-
-// The wide form (256 activation rows per tile, one CTA per SM) pays where a few hundred rows meet a narrow output:
-// ordinary tiles would leave most SMs idle (761 x 2048: 96 tiles of 128 x 128), while 128 x 256 swapped tiles with
-// K split over a cluster fill them (48 tiles x 3 splits).  Chosen when at least two K splits fit on the machine.
-int md_gemm_skinny_wide_splits(const md_ctx* ctx, const void* a, const void* b, const void* c, size_t M, size_t N, size_t K) {
-    if (M <= 64 || M > 1024 || !skinny_operands_ok(a, b, c, N, K)) return 0;
-    const size_t tiles = ((N + TILE_N - 1) / TILE_N) * ((M + 255) / 256);
-    const size_t num_kb = (K + BLOCK_K - 1) / BLOCK_K;
-    size_t splits = (size_t)ctx->sm_count / tiles;
-    if (splits > (size_t)MAX_SPLITS) splits = MAX_SPLITS;
-    if (splits > num_kb / 4) splits = num_kb / 4;   // at least four k-blocks per split
-    return splits >= 2 ? (int)splits : 0;
-}
-
-template <int XN>
-static int launch_skinny(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K, int b_layout,
-                         const md_epilogue& ep, int splits) {
+int md_launch_gemm_skinny(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
+                          int b_layout, const md_epilogue& ep) {
+    if (!md_gemm_skinny_supported(a, b, c, M, N, K))
+        return md_fail(ctx, MD_ERR_UNSUPPORTED, "skinny GEMM needs 8 < M <= 64, K %% 8 == 0, N %% 8 == 0 and 16-byte aligned operands");
     const bool mn = (b_layout == 0);
     CUtensorMap tm_w, tm_x;
     if (mn) MD_TRY(md_make_map_2d(ctx, &tm_w, b, N, K, 64, BLOCK_K, 0));
     else MD_TRY(md_make_map_2d(ctx, &tm_w, b, K, N, BLOCK_K, TILE_N, 0));
     MD_TRY(md_make_map_2d(ctx, &tm_x, a, K, M, BLOCK_K, XN, 0));
-    const int tiles = (int)((N + TILE_N - 1) / TILE_N), x_tiles = (int)((M + XN - 1) / XN);
+    const int tiles = (int)((N + TILE_N - 1) / TILE_N);
     const int num_kb = (int)((K + BLOCK_K - 1) / BLOCK_K);
+    // splits of K = CTAs per cluster: about two CTAs per SM in one wave, a power of two up to the portable cluster
+    // size of 8, at least two k-blocks per split
+    int want = ctx->skinny_splits > 0 ? ctx->skinny_splits : (2 * ctx->sm_count) / tiles;
+    if (want > num_kb / 2) want = num_kb / 2;
+    int splits = 1;
+    while (splits * 2 <= want && splits * 2 <= MAX_SPLITS) splits *= 2;
     const int kb_per_split = (num_kb + splits - 1) / splits;
-    constexpr int smem = smem_bytes(XN);
-    const uint32_t cfg_bit = 1u << ((mn ? 14 : 13) + (XN == 256 ? 12 : 0));
+    const uint32_t cfg_bit = 1u << (mn ? 14 : 13);
     if (!(ctx->tc_configured & cfg_bit)) {
-        if (mn) MD_CUDA(ctx, cudaFuncSetAttribute(gemm_skinny_kernel<true, XN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        else MD_CUDA(ctx, cudaFuncSetAttribute(gemm_skinny_kernel<false, XN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        if (mn) MD_CUDA(ctx, cudaFuncSetAttribute(gemm_skinny_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        else MD_CUDA(ctx, cudaFuncSetAttribute(gemm_skinny_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         ctx->tc_configured |= cfg_bit;
     }
-    // md_get_option("last_tc_tile"): 1000 + S = the skinny kernel with S splits, 3000 + S = its wide form
-    ctx->last_tc_tile = (XN == 256 ? 3000 : 1000) + splits;
+    ctx->last_tc_tile = 1000 + splits;   // md_get_option("last_tc_tile"): 1000 + S = the skinny kernel with S splits
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)tiles, (unsigned)splits, (unsigned)x_tiles);
+    cfg.gridDim = dim3((unsigned)tiles, (unsigned)splits);
     cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = smem;
+    cfg.dynamicSmemBytes = SMEM_BYTES;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[2];
     int na = 0;
@@ -321,31 +302,9 @@ static int launch_skinny(md_ctx* ctx, const __half* a, const __half* b, __half* 
     cfg.attrs = attr;
     cfg.numAttrs = na;
     const int Mi = (int)M, Ni = (int)N, Ki = (int)K;
-    const cudaError_t e = mn ? cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<true, XN>, tm_w, tm_x, c, Mi, Ni, Ki, kb_per_split, splits, ep, ctx->flags)
-                             : cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<false, XN>, tm_w, tm_x, c, Mi, Ni, Ki, kb_per_split, splits, ep, ctx->flags);
+    const cudaError_t e = mn ? cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<true>, tm_w, tm_x, c, Mi, Ni, Ki, kb_per_split, splits, ep, ctx->flags)
+                             : cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<false>, tm_w, tm_x, c, Mi, Ni, Ki, kb_per_split, splits, ep, ctx->flags);
     if (e != cudaSuccess) return md_fail(ctx, MD_ERR_CUDA, "launch of gemm_skinny_kernel failed: %s", cudaGetErrorString(e));
     ctx->launches++;
     return MD_OK;
-}
-
-int md_launch_gemm_skinny(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
-                          int b_layout, const md_epilogue& ep) {
-    if (!md_gemm_skinny_supported(a, b, c, M, N, K))
-        return md_fail(ctx, MD_ERR_UNSUPPORTED, "skinny GEMM needs 8 < M <= 64, K %% 8 == 0, N %% 8 == 0 and 16-byte aligned operands");
-    const int tiles = (int)((N + TILE_N - 1) / TILE_N);
-    const int num_kb = (int)((K + BLOCK_K - 1) / BLOCK_K);
-    // splits of K = CTAs per cluster: about two CTAs per SM in one wave, a power of two up to the portable cluster
-    // size of 8, at least two k-blocks per split
-    int want = ctx->skinny_splits > 0 ? ctx->skinny_splits : (2 * ctx->sm_count) / tiles;
-    if (want > num_kb / 2) want = num_kb / 2;
-    int splits = 1;
-    while (splits * 2 <= want && splits * 2 <= MAX_SPLITS) splits *= 2;
-    return launch_skinny<64>(ctx, a, b, c, M, N, K, b_layout, ep, splits);
-}
-
-int md_launch_gemm_skinny_wide(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
-                               int b_layout, const md_epilogue& ep, int splits) {
-    if (splits < 1 || splits > MAX_SPLITS || !skinny_operands_ok(a, b, c, N, K) || M == 0)
-        return md_fail(ctx, MD_ERR_UNSUPPORTED, "wide skinny GEMM: unsupported operands or split count");
-    return launch_skinny<256>(ctx, a, b, c, M, N, K, b_layout, ep, splits);
 }

@@ -336,7 +336,6 @@ int md_set_option(md_ctx* ctx, const char* key, long value) {
         return MD_OK;
     }
     if (!strcmp(key, "skinny")) { ctx->skinny = value ? 1 : 0; return MD_OK; }
-    if (!strcmp(key, "skinny_wide")) { ctx->skinny_wide = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "skinny_splits")) {
         MD_NEED(ctx, value >= 0 && value <= 16, "skinny_splits must be 0 (automatic) or 1..16 (rounded down to 1, 2, 4 or 8)");
         ctx->skinny_splits = (int)value;
@@ -440,12 +439,6 @@ int md_gemm_dispatch(md_ctx* ctx, const __half* a, const __half* b, __half* c, s
         return md_launch_gemv_nt(ctx, a, b, c, M, N, K, ep);
     if (ctx->gemm_mode == 0 && ctx->skinny && md_gemm_skinny_supported(a, b, c, M, N, K))
         return md_launch_gemm_skinny(ctx, a, b, c, M, N, K, b_layout, ep);
-    if (ctx->gemm_mode == 0 && ctx->skinny_wide) {
-        const int wide = ctx->skinny_splits > 0 && M > 64 && M <= 1024 ? ctx->skinny_splits
-                                                                       : md_gemm_skinny_wide_splits(ctx, a, b, c, M, N, K);
-        if (wide >= (ctx->skinny_splits > 0 ? 1 : 2) && md_gemm_tc_supported(a, b, c, M, N, K, b_layout))
-            return md_launch_gemm_skinny_wide(ctx, a, b, c, M, N, K, b_layout, ep, wide > 8 ? 8 : wide);
-    }
     const bool tc_ok = md_gemm_tc_supported(a, b, c, M, N, K, b_layout);
     if (ctx->gemm_mode == 2 && !tc_ok)
         return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 GEMM forced but the shape/alignment does not allow it");

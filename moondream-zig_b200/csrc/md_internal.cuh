@@ -65,7 +65,6 @@ struct md_ctx {
     void* encode_tiled = nullptr;
     uint32_t tc_configured = 0;  // tcgen05 kernels whose dynamic shared memory limit has been raised
     int skinny = 1;          // md_set_option("skinny"): 8 < M <= 64 takes the swapped-operand split-K kernel
-    int skinny_wide = 1;     // md_set_option("skinny_wide"): its wide form for a few hundred rows and a narrow output
     int skinny_splits = 0;   // md_set_option("skinny_splits"): 0 = automatic, else the number of K splits (tests)
     bool sdpa_mma_configured = false;  // the same for the mma.sync attention kernels
     // (cos, sin) table shared by the fused attention calls: [rope_rows][rope_dim/2][2] f32
@@ -222,11 +221,6 @@ int md_launch_gather_colblocks(md_ctx* ctx, const uint16_t* gathered, uint16_t* 
 bool md_gemm_skinny_supported(const void* a, const void* b, const void* c, size_t M, size_t N, size_t K);
 int md_launch_gemm_skinny(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
                           int b_layout, const md_epilogue& ep);
-// the wide form: 64 < M <= 1024 with an output too narrow for ordinary tiles; returns the number of K splits to use
-// (0 = do not take this kernel)
-int md_gemm_skinny_wide_splits(const md_ctx* ctx, const void* a, const void* b, const void* c, size_t M, size_t N, size_t K);
-int md_launch_gemm_skinny_wide(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
-                               int b_layout, const md_epilogue& ep, int splits);
 
 // gemm_pair.cu: 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2); same operand rules as md_launch_gemm_tc
 int md_launch_gemm_pair(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K, int b_layout,

@@ -283,46 +283,6 @@ def test_skinny_gemm(ctx, oracle, m, k, n, layout, splits):
 
 
 @pytest.mark.parametrize("layout", [0, 1])
-@pytest.mark.parametrize("splits", [0, 1, 3, 5, 8])
-@pytest.mark.parametrize("m,k,n", [(761, 2048, 2048), (729, 4304, 1152), (300, 520, 1000), (65, 64, 136), (1024, 256, 128)])
-def test_skinny_gemm_wide_form(ctx, oracle, m, k, n, layout, splits):
-    """The wide form of the swapped-operand split-K kernel (256 activation rows per tile, 64 < M <= 1024): ragged row
-    tiles, cluster sizes that are not powers of two, splits past the end of K (they contribute zeros), the fused
-    epilogue, three launches in a row; against the oracle and against the general tcgen05 kernel."""
-    rng = np.random.default_rng(m + n + k + splits)
-    a = f16_normal(rng, (m, k))
-    w_kn = f16_normal(rng, (k, n), 0.05)
-    bias, res = f16_normal(rng, (n,), 0.5), f16_normal(rng, (m, n))
-    w = w_kn if layout == 0 else np.ascontiguousarray(w_kn.T)
-    ref = oracle.hgemm_nn(a, w_kn) if layout == 0 else oracle.hgemm_nt(a, w)
-    ref = oracle.add(oracle.gelu(oracle.bias_add(ref, bias)), res)
-    da, dw, db, dr = ctx.upload(a), ctx.upload(w), ctx.upload(bias), ctx.upload(res)
-    out = ctx.alloc((m, n))
-    ctx.set_option("skinny_splits", splits)
-    try:
-        for _ in range(3):
-            ctx.hgemm_fused(da, dw, out, m, n, k, layout, bias=db, gelu=True, residual=dr)
-        ctx.sync()
-        tile = ctx.get_option("last_tc_tile")
-        if splits:
-            assert tile == 3000 + splits          # the wide form ran with the requested cluster size
-    finally:
-        ctx.set_option("skinny_splits", 0)
-    got = out.numpy()
-    assert_close_ref(got, ref, f"wide skinny {m}x{n}x{k} splits {splits} (kernel {tile})")
-    ctx.set_option("skinny_wide", 0)
-    try:
-        ctx.hgemm_fused(da, dw, out, m, n, k, layout, bias=db, gelu=True, residual=dr)
-        ctx.sync()
-        assert ctx.get_option("last_tc_tile") < 3000
-    finally:
-        ctx.set_option("skinny_wide", 1)
-    assert_close_ref(got, out.numpy(), "wide skinny vs general kernel", rel=2e-3)
-    for b in (da, dw, db, dr, out):
-        b.free()
-
-
-@pytest.mark.parametrize("layout", [0, 1])
 @pytest.mark.parametrize("m,k,n", [(256, 64, 256), (300, 520, 1000), (1024, 1152, 4304), (129, 8, 8), (100, 64, 264),
                                    (2304, 2048, 2048)])
 def test_gemm_on_cta_pairs(ctx, oracle, m, k, n, layout):
