@@ -120,6 +120,13 @@ int md_vision_model_destroy(md_vision_model* model);
 int md_vision_encode(md_vision_model* model, const uint8_t* crops_u8, size_t crops, size_t crop_a, size_t crop_b,
                      uint16_t* features_out, uint16_t* out);
 
+/* `n_images` (<= max_crops) independent images of one crop each in one pass: the encoder's GEMMs run over
+ * n_images * tokens rows, attention stays per image, and image i is projected from concat(features[i], features[i])
+ * — what md_vision_encode gives for the reference's two identical crops of one image (vision_model.zig:137-155) —
+ * into outs[i] ([tokens, proj_out], host or device).  images_u8 [n_images, img, img, 3], host or device.  For hosts
+ * that serve several requests at once (the reference encodes one image per process run). */
+int md_vision_encode_images(md_vision_model* model, const uint8_t* images_u8, size_t n_images, uint16_t* const* outs);
+
 /* ---- moondream.bin weight file (read: weights.zig:61-207; written by weights.py:82-246) --------------
  *
  * Layout, little-endian: u32 magic 0x4D4F4F4E ("MOON"), u32 version 2, then records until end of file:

@@ -616,6 +616,165 @@ sdpa_decode_kernel(const __grid_constant__ DecodeParams gp) {
     if (tid == 0) p.counters[head] = 0;  // ready for the next launch
 }
 
+// The same decode attention for a batched step with enough (head, request) pairs to fill the machine by themselves
+// (8 requests x 32 heads = 256 CTAs): ONE CTA per pair walks all of its keys, so nothing is merged across CTAs: no
+// partials in global memory, no fence, no ticket, no last-arriver round.  8 warps; a lane group of 8 lanes x 16 B
+// covers a key row, a warp 4 keys per load instruction, the CTA 128 keys per turn; every lane keeps the loads of
+// the NEXT turn (4 K + 4 V rows) in flight while it works on the current one (two register buffers, the loop is
+// unrolled by two).  Each lane group carries a running (max, sum, 8 output dims) over its keys; the 32 groups of the
+// CTA meet once through shared memory at the end.  Fused form only (q / new k / new v from the qkv row, rope in-kernel,
+// append to the cache, position from device memory).
+constexpr int LOOP_WARPS = 8, LOOP_ITER = 4, LOOP_KEYS = LOOP_WARPS * 4 * LOOP_ITER;   // 128 keys per turn
+
+__global__ void __launch_bounds__(LOOP_WARPS * 32, 2)
+sdpa_decode_loop_kernel(const __grid_constant__ DecodeParams gp) {
+    __shared__ float q_s[DEC_D], knew_s[DEC_D], vnew_s[DEC_D], raw_s[DEC_D], rawk_s[DEC_D];
+    __shared__ float red_m[LOOP_WARPS * 4], red_l[LOOP_WARPS * 4], red_o[LOOP_WARPS * 4][DEC_D];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int head = blockIdx.x, b = blockIdx.y;
+    const __half* qrow = gp.q + b * gp.q_batch_stride;
+    __half* out = gp.out + b * gp.out_batch_stride;
+    __half* kc = gp.bk[b];
+    __half* vc = gp.bv[b];
+    const int pos = *gp.bpos[b];          // keys 0 .. pos-1 are in the cache, the new token becomes key pos
+    const float scale = 0.125f;           // 1/sqrt(64)
+    const int sub = lane & 7, grp = lane >> 3;
+    asm volatile("griddepcontrol.launch_dependents;");
+    const __half* kh = kc + head * gp.k_head_stride + sub * 8;
+    const __half* vh = vc + head * gp.k_head_stride + sub * 8;
+    const int key_w = warp * (4 * LOOP_ITER) + grp;   // this lane group's first key of a turn (then +4 per load)
+
+    uint4 ka[LOOP_ITER], va[LOOP_ITER], kb[LOOP_ITER], vb[LOOP_ITER];
+    auto request = [&](int key0, uint4 (&kr)[LOOP_ITER], uint4 (&vr)[LOOP_ITER]) {
+#pragma unroll
+        for (int it = 0; it < LOOP_ITER; ++it) {
+            const int key = key0 + key_w + it * 4;
+            kr[it] = key < pos ? ldg_nc16(kh + (long long)key * DEC_D) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int it = 0; it < LOOP_ITER; ++it) {
+            const int key = key0 + key_w + it * 4;
+            vr[it] = key < pos ? ldg_nc16(vh + (long long)key * DEC_D) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    // the cached prefix was written by earlier steps: the first two turns are requested before the dependency wait
+    request(0, ka, va);
+    request(LOOP_KEYS, kb, vb);
+    float2 cs = make_float2(1.f, 0.f);
+    if (tid < gp.rot_dim) {
+        const int half = gp.rot_dim >> 1, j = tid < half ? tid : tid - half;
+        cs = __ldg(reinterpret_cast<const float2*>(gp.rope_tab + ((size_t)pos * half + j) * 2));  // (cos, sin)
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // q, new k, new v of this head from the qkv row; rotate q and k, append k and v to the cache
+    const int hd = gp.n_heads * DEC_D;
+    if (tid < DEC_D) {
+        raw_s[tid] = __half2float(__ldcg(qrow + head * DEC_D + tid));
+        rawk_s[tid] = __half2float(__ldcg(qrow + hd + head * DEC_D + tid));
+        vnew_s[tid] = __half2float(__ldcg(qrow + 2 * hd + head * DEC_D + tid));
+    }
+    __syncthreads();
+    if (tid < DEC_D) {
+        q_s[tid] = md_round_f16(rope_rotate(raw_s, tid, gp.rot_dim, cs));
+        const __half kr = __float2half_rn(rope_rotate(rawk_s, tid, gp.rot_dim, cs));
+        knew_s[tid] = __half2float(kr);
+        kc[head * gp.k_head_stride + (long long)pos * DEC_D + tid] = kr;
+        vc[head * gp.k_head_stride + (long long)pos * DEC_D + tid] = __float2half_rn(vnew_s[tid]);
+    }
+    __syncthreads();
+    float qv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) qv[i] = q_s[sub * 8 + i];
+
+    // running state of this lane group over its keys: exponent reference m, sum l, 8 output dims per lane
+    float m = -INFINITY, l = 0.f, acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    auto consume = [&](int key0, const uint4 (&kr)[LOOP_ITER], const uint4 (&vr)[LOOP_ITER]) {
+        float sc[LOOP_ITER], mt = -INFINITY;
+#pragma unroll
+        for (int it = 0; it < LOOP_ITER; ++it) {
+            float kf[8];
+            unpack8(kr[it], kf);
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dot = fmaf(qv[i], kf[i], dot);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+            sc[it] = (key0 + key_w + it * 4 < pos) ? dot * scale : -INFINITY;
+            mt = fmaxf(mt, sc[it]);
+        }
+        if (mt > m) {   // the reference of this group moves: rescale what it holds (uniform within the 8 lanes)
+            const float corr = (m == -INFINITY) ? 0.f : expf(m - mt);
+            l *= corr;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] *= corr;
+            m = mt;
+        }
+        const float mu = (m == -INFINITY) ? 0.f : m;
+#pragma unroll
+        for (int it = 0; it < LOOP_ITER; ++it) {
+            const float pw = expf(sc[it] - mu);   // exp(-inf) = 0 for keys past the cache
+            l += pw;
+            float vf[8];
+            unpack8(vr[it], vf);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = fmaf(pw, vf[i], acc[i]);
+        }
+    };
+    for (int key0 = 0; key0 < pos; key0 += 2 * LOOP_KEYS) {
+        consume(key0, ka, va);
+        if (key0 + 2 * LOOP_KEYS < pos) request(key0 + 2 * LOOP_KEYS, ka, va);
+        if (key0 + LOOP_KEYS < pos) {
+            consume(key0 + LOOP_KEYS, kb, vb);
+            if (key0 + 3 * LOOP_KEYS < pos) request(key0 + 3 * LOOP_KEYS, kb, vb);
+        }
+    }
+    // the appended token: lane group 0 of warp 0
+    if (warp == 0 && grp == 0) {
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dot = fmaf(qv[i], knew_s[sub * 8 + i], dot);
+        dot += __shfl_xor_sync(0x000000ffu, dot, 1);
+        dot += __shfl_xor_sync(0x000000ffu, dot, 2);
+        dot += __shfl_xor_sync(0x000000ffu, dot, 4);
+        const float s_new = dot * scale;
+        if (s_new > m) {
+            const float corr = (m == -INFINITY) ? 0.f : expf(m - s_new);
+            l *= corr;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] *= corr;
+            m = s_new;
+        }
+        const float pw = expf(s_new - m);
+        l += pw;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = fmaf(pw, vnew_s[sub * 8 + i], acc[i]);
+    }
+    // the 32 lane groups of the CTA meet: group g = warp * 4 + grp
+    const int g = warp * 4 + grp;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red_o[g][sub * 8 + i] = acc[i];
+    if (sub == 0) { red_m[g] = m; red_l[g] = l; }
+    __syncthreads();
+    if (tid < DEC_D) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < LOOP_WARPS * 4; ++w) M = fmaxf(M, red_m[w]);
+        const float Mu = (M == -INFINITY) ? 0.f : M;
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < LOOP_WARPS * 4; ++w) {
+            const float f = (red_m[w] == -INFINITY) ? 0.f : expf(red_m[w] - Mu);
+            L += red_l[w] * f;
+            O += red_o[w][tid] * f;
+        }
+        out[head * DEC_D + tid] = __float2half_rn(L > 0.f ? O / L : 0.f);
+    }
+}
+
 // qkv [S, 3*H*d] -> rotated q [S, H*d], rotated k and raw v appended to the cache at pos..pos+S-1,
 // 8 dims (16 bytes) per thread: thread -> (row s, head h, 8-dim piece c).  A rotated piece needs its
 // partner piece half a rotary width away; both are single 16-byte loads.  Needs d % 8 == 0 and rot_dim % 16 == 0.
@@ -813,6 +972,23 @@ int md_launch_sdpa_decode_fused_devpos_batch(md_ctx* ctx, const __half* qkv, siz
         p.q_batch_stride = (long long)qkv_stride;
         p.out_batch_stride = (long long)out_stride;
         for (size_t b = 0; b < batch; ++b) { p.bk[b] = kc[b]; p.bv[b] = vc[b]; p.bpos[b] = pos_dev[b]; }
+    }
+    // enough (head, request) pairs to fill the machine without splitting the keys: one CTA per pair, no merge
+    if (ctx->decode_loop != 0 && batch > 1 && batch * n_heads >= (size_t)(ctx->decode_loop > 0 ? ctx->decode_loop : 192) &&
+        rot_dim <= DEC_D) {
+        cudaLaunchConfig_t lcfg = {};
+        lcfg.gridDim = dim3((unsigned)n_heads, (unsigned)batch);
+        lcfg.blockDim = dim3(LOOP_WARPS * 32);
+        lcfg.stream = ctx->stream;
+        cudaLaunchAttribute lattr[1];
+        lattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        lattr[0].val.programmaticStreamSerializationAllowed = 1;
+        lcfg.attrs = lattr;
+        lcfg.numAttrs = ctx->pdl ? 1 : 0;
+        const cudaError_t le = cudaLaunchKernelEx(&lcfg, sdpa_decode_loop_kernel, p);
+        if (le != cudaSuccess) return md_fail(ctx, MD_ERR_CUDA, "launch of sdpa_decode_loop_kernel failed: %s", cudaGetErrorString(le));
+        MD_LAUNCH_CHECK(ctx, "sdpa_decode_loop_kernel");
+        return MD_OK;
     }
     const int max_splits = (int)((max_seq + DEC_KEYS - 1) / DEC_KEYS);
     if (ctx->decode_cluster_ok < 0) {

@@ -330,6 +330,7 @@ int md_set_option(md_ctx* ctx, const char* key, long value) {
     if (!strcmp(key, "pdl")) { ctx->pdl = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "prefill_fork")) { ctx->prefill_fork = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "decode_fork")) { ctx->decode_fork = value ? 1 : 0; return MD_OK; }
+    if (!strcmp(key, "decode_loop")) { ctx->decode_loop = (int)value; return MD_OK; }
     if (!strcmp(key, "decode_mlp_split")) {
         MD_NEED(ctx, value == 0 || value == 2 || value == 4, "decode_mlp_split must be 0, 2 or 4");
         ctx->decode_mlp_split = (int)value;

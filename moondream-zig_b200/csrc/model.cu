@@ -777,15 +777,26 @@ int md_vision_model_destroy(md_vision_model* model) {
     return MD_OK;
 }
 
-int md_vision_encode(md_vision_model* m, const uint8_t* crops_u8, size_t crops, size_t crop_a, size_t crop_b,
-                     uint16_t* features_out, uint16_t* out) {
-    if (!m) return MD_ERR_INVALID_ARG;
+}  // extern "C"
+
+// images == false: one image of `crops` crops, projection of concat(features[a], features[b]) -> outs[0].
+// images == true : `crops` independent single-crop images in one pass (the GEMMs see crops * tokens rows); image i is
+//                  projected from concat(features[i], features[i]) (the reference's two identical crops) -> outs[i].
+static int vision_encode_impl(md_vision_model* m, const uint8_t* crops_u8, size_t crops, size_t crop_a, size_t crop_b,
+                              bool images, uint16_t* features_out, uint16_t* const* outs) {
     md_ctx* ctx = m->ctx;
     const md_vision_weights& w = m->w;
-    if (!crops_u8 || !out) return md_fail(ctx, MD_ERR_INVALID_ARG, "vision_encode: null pointer");
     if (crops == 0 || crops > m->max_crops || crop_a >= crops || crop_b >= crops)
         return md_fail(ctx, MD_ERR_INVALID_ARG, "vision_encode: crops %zu (max %zu), a %zu, b %zu", crops, m->max_crops, crop_a,
                        crop_b);
+    const size_t PR = images ? crops * w.tokens : w.tokens;   // rows of the projection
+    if (m->graph && (m->cat.cap < PR * 2 * w.dim * 2 || m->pfc1.cap < PR * w.proj_hidden * 2 || m->out.cap < PR * w.proj_out * 2)) {
+        md_graph_destroy(ctx, m->graph);   // the projection's buffers are about to move: the captured encode is stale
+        m->graph = nullptr;
+    }
+    MD_TRY(m->cat.ensure(ctx, PR * 2 * w.dim * 2));
+    MD_TRY(m->pfc1.ensure(ctx, PR * w.proj_hidden * 2));
+    MD_TRY(m->out.ensure(ctx, PR * w.proj_out * 2));
     const size_t T = w.tokens, D = w.dim, F = w.hidden, R = crops * T;
     const float eps = eps_of(w.eps_f16);
     const cudaMemcpyKind in_kind = md_is_device_ptr(crops_u8) ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
@@ -829,22 +840,24 @@ int md_vision_encode(md_vision_model* m, const uint8_t* crops_u8, size_t crops, 
         return MD_OK;
     };
     auto proj = [&]() -> int {
-        // concat(features[a], features[b]) on the feature dim (vision_model.zig:189-195)
+        // concat(features[a], features[b]) on the feature dim (vision_model.zig:189-195); for independent images
+        // every image's rows are paired with themselves
         __half* cat = m->cat.as<__half>();
-        MD_CUDA(ctx, cudaMemcpy2DAsync(cat, 2 * D * 2, ln + crop_a * T * D, D * 2, D * 2, T, cudaMemcpyDeviceToDevice,
-                                       ctx->stream));
-        MD_CUDA(ctx, cudaMemcpy2DAsync(cat + D, 2 * D * 2, ln + crop_b * T * D, D * 2, D * 2, T, cudaMemcpyDeviceToDevice,
+        const size_t ra = images ? 0 : crop_a * T, rb = images ? 0 : crop_b * T;
+        MD_CUDA(ctx, cudaMemcpy2DAsync(cat, 2 * D * 2, ln + ra * D, D * 2, D * 2, PR, cudaMemcpyDeviceToDevice, ctx->stream));
+        MD_CUDA(ctx, cudaMemcpy2DAsync(cat + D, 2 * D * 2, ln + rb * D, D * 2, D * 2, PR, cudaMemcpyDeviceToDevice,
                                        ctx->stream));
         md_epilogue e_p1;
         e_p1.bias = H(w.proj_fc1_b);
         e_p1.gelu = 1;
-        MD_TRY(md_gemm_dispatch(ctx, cat, H(w.proj_fc1_w), m->pfc1.as<__half>(), T, w.proj_hidden, 2 * D, 0, e_p1));
+        MD_TRY(md_gemm_dispatch(ctx, cat, H(w.proj_fc1_w), m->pfc1.as<__half>(), PR, w.proj_hidden, 2 * D, 0, e_p1));
         md_epilogue e_p2;
         e_p2.bias = H(w.proj_fc2_b);
-        MD_TRY(md_gemm_dispatch(ctx, m->pfc1.as<__half>(), H(w.proj_fc2_w), m->out.as<__half>(), T, w.proj_out,
+        MD_TRY(md_gemm_dispatch(ctx, m->pfc1.as<__half>(), H(w.proj_fc2_w), m->out.as<__half>(), PR, w.proj_out,
                                 w.proj_hidden, 0, e_p2));
         return MD_OK;
     };
+    if (images) crop_a = crop_b = ~(size_t)0;   // the graph key of the independent-images form
     if (m->graph && m->graph_gen == ctx->generation && m->graph_crops == crops && m->graph_a == crop_a &&
         m->graph_b == crop_b) {
         MD_TRY(md_graph_launch(ctx, m->graph));
@@ -869,8 +882,27 @@ int md_vision_encode(md_vision_model* m, const uint8_t* crops_u8, size_t crops, 
         m->seen_crops = crops; m->seen_a = crop_a; m->seen_b = crop_b;
     }
     MD_TRY(copy_out(ctx, features_out, ln, R * D * 2));
-    MD_TRY(copy_out(ctx, out, m->out.p, T * w.proj_out * 2));
+    for (size_t i = 0; i < (images ? crops : 1); ++i)
+        MD_TRY(copy_out(ctx, outs[i], m->out.as<__half>() + i * T * w.proj_out, T * w.proj_out * 2));
     return md_check_flags(ctx);
+}
+
+extern "C" {
+
+int md_vision_encode(md_vision_model* m, const uint8_t* crops_u8, size_t crops, size_t crop_a, size_t crop_b,
+                     uint16_t* features_out, uint16_t* out) {
+    if (!m) return MD_ERR_INVALID_ARG;
+    if (!crops_u8 || !out) return md_fail(m->ctx, MD_ERR_INVALID_ARG, "vision_encode: null pointer");
+    uint16_t* outs[1] = {out};
+    return vision_encode_impl(m, crops_u8, crops, crop_a, crop_b, false, features_out, outs);
+}
+
+int md_vision_encode_images(md_vision_model* m, const uint8_t* images_u8, size_t n_images, uint16_t* const* outs) {
+    if (!m) return MD_ERR_INVALID_ARG;
+    if (!images_u8 || !outs) return md_fail(m->ctx, MD_ERR_INVALID_ARG, "vision_encode_images: null pointer");
+    for (size_t i = 0; i < n_images; ++i)
+        if (!outs[i]) return md_fail(m->ctx, MD_ERR_INVALID_ARG, "vision_encode_images: null output %zu", i);
+    return vision_encode_impl(m, images_u8, n_images, 0, 0, true, nullptr, outs);
 }
 
 }  // extern "C"

@@ -203,6 +203,7 @@ class VisionModel:
     def _create(self, s: _VisW, max_crops: int):
         self.s = s
         self.tokens, self.dim, self.proj_out, self.img = int(s.tokens), int(s.dim), int(s.proj_out), int(s.img)
+        self.max_crops = int(max_crops)
         h = C.c_void_p()
         self.ctx._check(self.lib.md_vision_model_create(self.ctx.h, C.byref(s), _sz(max_crops), C.byref(h)))
         self.h = h
@@ -227,6 +228,20 @@ class VisionModel:
                                                   _sz(crop_b), C.c_void_p(feats.ctypes.data if want_features else 0),
                                                   C.c_void_p(out.ctypes.data if out_ptr is None else out_ptr)))
         return (out, feats) if want_features else out
+
+    def encode_images(self, images_u8: np.ndarray, out_ptrs=None):
+        """n independent one-crop images in one pass (md_vision_encode_images).  images uint8 [n, img, img, 3].
+        out_ptrs: n device addresses of [tokens, proj_out] buffers; without them a numpy array [n, tokens, proj_out]
+        is returned."""
+        images_u8 = np.ascontiguousarray(images_u8, np.uint8)
+        n = images_u8.shape[0]
+        out = None
+        if out_ptrs is None:
+            out = np.empty((n, self.tokens, self.proj_out), np.float16)
+            out_ptrs = [out[i].ctypes.data for i in range(n)]
+        arr = (C.c_void_p * n)(*[int(p) for p in out_ptrs])
+        self.ctx._check(self.lib.md_vision_encode_images(self.h, C.c_void_p(images_u8.ctypes.data), _sz(n), arr))
+        return out
 
     def close(self):
         if getattr(self, "h", None):

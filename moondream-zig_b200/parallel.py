@@ -181,19 +181,30 @@ def serve_requests(ctx, vision, text, requests: list, world: int, rank: int, n_s
         reqs.append(text.request())
     dim, tokens = text.dim, vision.tokens
     assert vision.proj_out == dim
+    embeds = state.setdefault("embeds", {})          # slot -> (DevBuf [rows, dim], rows)
     out: dict = {}
     for g0 in range(0, len(mine), max_streams):
         group = mine[g0:g0 + max_streams]
+        bases = []
+        for slot, idx in enumerate(group):
+            rows = requests[idx].ids.size + tokens
+            if slot not in embeds or embeds[slot][1] < rows:
+                embeds[slot] = (ctx.alloc((rows, dim)), rows)
+            bases.append(embeds[slot][0].ptr)
+        # the images of a group go through the vision encoder together when each is one crop and the encoder has
+        # the capacity (its GEMMs then see len(group) * 729 rows instead of 729); otherwise one encode per request
+        together = len(group) > 1 and len(group) <= vision.max_crops and all(requests[i].crops.shape[0] == 1 for i in group)
+        if together:
+            vision.encode_images(np.concatenate([requests[i].crops for i in group]),
+                                 out_ptrs=[b + dim * 2 for b in bases])
         firsts = []
         for slot, idx in enumerate(group):
             rq = requests[idx]
             rows = rq.ids.size + tokens
-            if state.get("embeds_rows", 0) < rows:
-                state["embeds"] = ctx.alloc((rows, dim))
-                state["embeds_rows"] = rows
-            base = state["embeds"].ptr
+            base = bases[slot]
             text.text_encoder(rq.ids[:1], out_ptr=base)
-            vision.encode(rq.crops, out_ptr=base + dim * 2)
+            if not together:
+                vision.encode(rq.crops, out_ptr=base + dim * 2)
             if rq.ids.size > 1:
                 text.text_encoder(rq.ids[1:], out_ptr=base + (1 + tokens) * dim * 2)
             reqs[slot].reset()

@@ -31,13 +31,14 @@ def oracle_request(oracle, vw, tw, req, n_steps):
     return first, first_gap, np.array(toks, np.uint32), np.array(gaps)
 
 
-@pytest.mark.parametrize("max_streams", [3, 8])
-def test_requests_match_the_oracle_under_teacher_forcing(ctx, oracle, pkg, max_streams):
+@pytest.mark.parametrize("max_streams,vision_capacity", [(3, 1), (8, 1), (8, 4)])
+def test_requests_match_the_oracle_under_teacher_forcing(ctx, oracle, pkg, max_streams, vision_capacity):
     par = importlib.import_module(entry.PKG_NAME + ".parallel")
     models = importlib.import_module(entry.PKG_NAME + ".models")
     tw = text_weights(4031, n_layers=2, hidden=1024, vocab=4096)
     vw = vision_weights(3031, n_layers=2)
-    tm, vm = models.TextModel(ctx, tw), models.VisionModel(ctx, vw, max_crops=1)
+    # vision_capacity 4: the four images of the group go through the encoder in one pass (md_vision_encode_images)
+    tm, vm = models.TextModel(ctx, tw), models.VisionModel(ctx, vw, max_crops=vision_capacity)
     rng = np.random.default_rng(31)
     n_req, n_steps = 4, 10
     requests = [par.Request(rng.integers(0, 256, (1, 378, 378, 3), dtype=np.uint8), rng.integers(0, 4096, 32))
@@ -59,6 +60,28 @@ def test_requests_match_the_oracle_under_teacher_forcing(ctx, oracle, pkg, max_s
         np.testing.assert_array_equal(got[1:][pinned], toks[pinned], err_msg=f"request {i}")
     assert pinned_total >= n_steps     # the check is not vacuous
     tm.close(); vm.close()
+
+
+def test_images_encoded_together_equal_images_encoded_alone(ctx, oracle, pkg):
+    """md_vision_encode_images: n one-crop images in one pass against the oracle (features of an image paired with
+    themselves, as the reference's two identical crops) and against one md_vision_encode per image."""
+    models = importlib.import_module(entry.PKG_NAME + ".models")
+    from conftest import assert_close_ref
+    vw = vision_weights(3033, n_layers=2)
+    vm = models.VisionModel(ctx, vw, max_crops=3)
+    rng = np.random.default_rng(33)
+    imgs = rng.integers(0, 256, (3, 378, 378, 3), dtype=np.uint8)
+    ref = oracle.VisionModel(vw)
+    feats = ref.encoder(oracle.preprocess_patchify(imgs), joint_attention=False)
+    for _ in range(3):                  # the third pass replays the captured encode
+        together = vm.encode_images(imgs)
+    for i in range(3):
+        assert_close_ref(together[i], ref.projection(feats[i], feats[i]), f"image {i} vs oracle")
+        alone = vm.encode(imgs[i:i + 1])
+        assert_close_ref(together[i], alone, f"image {i}: together vs alone", rel=2e-3)
+    # a single-image encode after the batched one (another graph, the projection buffers keep their size)
+    assert_close_ref(vm.encode(imgs[:1]), ref.projection(feats[0], feats[0]), "single encode afterwards")
+    vm.close()
 
 
 def test_requests_partition_is_the_same_work(ctx, pkg):
