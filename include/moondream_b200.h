@@ -116,6 +116,8 @@ int md_set_gemm_mode(md_ctx* ctx, int mode);
  *   "prefill_fork"  1 (default) = a prefill layer runs fc1 -> fc2 as a second kernel chain beside the attention
  *   "decode_fork"   1 (default) = the fused decode layer runs as two concurrent kernel chains (q/k/v projection ->
  *                   attention -> out-projection | fc1 -> fc2) joined by events, 0 = three kernels in a row
+ *   "attn_ctas_per_sm" 2 (default), 1: the tcgen05 attention runs that many CTAs per SM, each walking several
+ *                   (query block, head, batch) items with its barriers, rings and TMEM kept; 0: one CTA per item
  *   "decode_loop"   n: the attention of a batched decode step with at least n (head, request) pairs runs one CTA per
  *                   pair that walks all of its keys (nothing to merge across CTAs); -1 (default) = 192, 0 = never
  *   "decode_mlp_split" 2 (default) or 4 = with decode_fork and a single request, the MLP chain runs as that many

@@ -632,11 +632,13 @@ sdpa_decode_loop_kernel(const __grid_constant__ DecodeParams gp) {
     __shared__ float red_m[LOOP_WARPS * 4], red_l[LOOP_WARPS * 4], red_o[LOOP_WARPS * 4][DEC_D];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int head = blockIdx.x, b = blockIdx.y;
-    const __half* qrow = gp.q + b * gp.q_batch_stride;
-    __half* out = gp.out + b * gp.out_batch_stride;
-    __half* kc = gp.bk[b];
-    __half* vc = gp.bv[b];
-    const int pos = *gp.bpos[b];          // keys 0 .. pos-1 are in the cache, the new token becomes key pos
+    const bool batched = gp.batch > 0;    // one request: cache and position in the scalar fields
+    const __half* qrow = gp.q + (batched ? b * gp.q_batch_stride : 0);
+    __half* out = gp.out + (batched ? b * gp.out_batch_stride : 0);
+    __half* kc = batched ? gp.bk[b] : gp.k_w;
+    __half* vc = batched ? gp.bv[b] : gp.v_w;
+    const int* pos_ptr = batched ? gp.bpos[b] : gp.pos_ptr;
+    const int pos = pos_ptr ? *pos_ptr : gp.pos;   // keys 0 .. pos-1 are in the cache, the new token becomes key pos
     const float scale = 0.125f;           // 1/sqrt(64)
     const int sub = lane & 7, grp = lane >> 3;
     asm volatile("griddepcontrol.launch_dependents;");
@@ -915,7 +917,33 @@ int md_launch_sdpa(md_ctx* ctx, const __half* q, const __half* k, const __half* 
     return MD_OK;
 }
 
+// One CTA per (head, request) walking all keys of its head: taken when there are enough such pairs to fill the
+// machine (option decode_loop), fused form only.
+static bool decode_loop_wanted(const md_ctx* ctx, const DecodeParams& p, size_t batch) {
+    if (ctx->decode_loop == 0 || !p.fused || p.rot_dim > DEC_D) return false;
+    if (ctx->decode_loop < 0 && batch < 2) return false;   // a single request keeps the key splits unless asked
+    return batch * (size_t)p.n_heads >= (size_t)(ctx->decode_loop > 0 ? ctx->decode_loop : 192);
+}
+
+static int decode_loop_launch(md_ctx* ctx, const DecodeParams& p, size_t batch) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)p.n_heads, (unsigned)batch);
+    cfg.blockDim = dim3(LOOP_WARPS * 32);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, sdpa_decode_loop_kernel, p);
+    if (le != cudaSuccess)
+        return md_fail(ctx, MD_ERR_CUDA, "launch of sdpa_decode_loop_kernel failed: %s", cudaGetErrorString(le));
+    MD_LAUNCH_CHECK(ctx, "sdpa_decode_loop_kernel");
+    return MD_OK;
+}
+
 static int decode_launch(md_ctx* ctx, DecodeParams& p) {
+    if (decode_loop_wanted(ctx, p, 1)) return decode_loop_launch(ctx, p, 1);
     p.splits = (p.kv_cache_len + DEC_KEYS - 1) / DEC_KEYS;
     if (p.splits < 1) p.splits = 1;
     const size_t partial_bytes = (size_t)p.n_heads * p.splits * (DEC_D + 2) * sizeof(float);
@@ -973,23 +1001,7 @@ int md_launch_sdpa_decode_fused_devpos_batch(md_ctx* ctx, const __half* qkv, siz
         p.out_batch_stride = (long long)out_stride;
         for (size_t b = 0; b < batch; ++b) { p.bk[b] = kc[b]; p.bv[b] = vc[b]; p.bpos[b] = pos_dev[b]; }
     }
-    // enough (head, request) pairs to fill the machine without splitting the keys: one CTA per pair, no merge
-    if (ctx->decode_loop != 0 && batch > 1 && batch * n_heads >= (size_t)(ctx->decode_loop > 0 ? ctx->decode_loop : 192) &&
-        rot_dim <= DEC_D) {
-        cudaLaunchConfig_t lcfg = {};
-        lcfg.gridDim = dim3((unsigned)n_heads, (unsigned)batch);
-        lcfg.blockDim = dim3(LOOP_WARPS * 32);
-        lcfg.stream = ctx->stream;
-        cudaLaunchAttribute lattr[1];
-        lattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        lattr[0].val.programmaticStreamSerializationAllowed = 1;
-        lcfg.attrs = lattr;
-        lcfg.numAttrs = ctx->pdl ? 1 : 0;
-        const cudaError_t le = cudaLaunchKernelEx(&lcfg, sdpa_decode_loop_kernel, p);
-        if (le != cudaSuccess) return md_fail(ctx, MD_ERR_CUDA, "launch of sdpa_decode_loop_kernel failed: %s", cudaGetErrorString(le));
-        MD_LAUNCH_CHECK(ctx, "sdpa_decode_loop_kernel");
-        return MD_OK;
-    }
+    if (decode_loop_wanted(ctx, p, batch)) return decode_loop_launch(ctx, p, batch);
     const int max_splits = (int)((max_seq + DEC_KEYS - 1) / DEC_KEYS);
     if (ctx->decode_cluster_ok < 0) {
         const cudaError_t ce =

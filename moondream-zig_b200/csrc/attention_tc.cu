@@ -4,8 +4,13 @@
 // attention.multiMaskedSDPA (attention.zig:416-541: decoder prefill, d = 64, causal) for the layouts
 // TMA can address; sdpa_mma_kernel (attention.cu) remains the path for everything else.
 //
-// One CTA = 128 queries of one (batch, head), 192 threads, two CTAs per SM:
-//   warp 0      TMA producer: Q once, then K and V tiles of 64 keys through their own rings of stages.
+// A work item = 128 queries of one (batch, head).  The grid is at most two CTAs per SM (192 threads each); a CTA
+// takes items blockIdx.x, blockIdx.x + gridDim.x, ... and keeps its barriers, its TMEM and its rings across them,
+// so that from the second item on nothing of a CTA's start-up (launch, barrier set-up, TMEM allocation, descriptor
+// fetch, first loads) is paid again: the producer fetches the next item's Q as soon as the last S product of the
+// current item has read it, and its K / V tiles as ring stages come free, while the softmax warps still write the
+// current item's output.
+//   warp 0      TMA producer: per item Q, then K and V tiles of 64 keys through their own rings of stages.
 //   warp 1      one lane issues tcgen05.mma: S = Q K^T (128 x 64 x d into one of two S buffers in TMEM)
 //               and O += P V (128 x d x 64, accumulated in TMEM over all key tiles);
 //               tcgen05.commit signals completion.
@@ -22,14 +27,20 @@
 // Operands are addressed through 4-D tensor maps (d, row, head, batch) whose extents are exactly the
 // valid data, so everything outside (rows past kv_len, dims past d) is zero-filled by TMA: no stale
 // cache rows or neighbouring heads ever reach the tensor cores.
-// d = 72: dims 0-63 travel as a 128B-swizzled tile, dims 64-79 (64-71 data, the rest zero fill) as a
-// second, 32B-swizzled tile of 16 dims; S takes one more k-step over the tail and the PV product one
-// more MMA with N = 16.
+// d = 72: dims 0-63 travel as a 128B-swizzled tile.  For Q and K (K-major operands of S) dims 64-79 (64-71 data, the
+// rest zero fill) follow as a second, 32B-swizzled tile of 16 dims, one more k-step of S.  For V (the MN-major B
+// operand of the PV product) the tail is a second 128B-swizzled atom (dims 64-127 of the box, all but 8 of them zero
+// fill and never read) right behind the main tile, so that one MMA with N = 80 covers both: an MMA this small costs
+// about the same 45-50 cycles whatever its N, so a separate N = 16 product for the tail would nearly double the time
+// of the PV product.
 //
 // Numerics as the reference: scores, probability sums and the output accumulate in f32, one rounding
 // to f16 at the end (attention.zig:199-202,505-508); P is rounded to f16 for the PV product.
 // Every mbarrier wait is bounded (tc_common.cuh); a wait that gives up is reported through the
 // context's error word and the kernel still runs to its end and frees its TMEM.
+#include <algorithm>
+#include <climits>
+
 #include "md_internal.cuh"
 #include "tc_common.cuh"
 
@@ -53,7 +64,25 @@ struct AttnTcParams {
     // 4-D tensor maps (dim 0 = head dimension d; dims 1..3 = row, head, batch in order of ascending stride):
     // which map dimension carries the row / head / batch index, for q and for k, v
     int q_dim_row, q_dim_head, q_dim_batch, kv_dim_row, kv_dim_head, kv_dim_batch;
+    int n_qblk, n_heads, n_batch, n_items;   // items = n_qblk * n_heads * n_batch
 };
+
+// Item w -> (query block, head, batch).  Causal: the last query blocks see the most keys, so they come first
+// (longest items first when a CTA takes several); otherwise the query blocks of one (batch, head) are neighbours,
+// so the CTAs that run together share K and V in L2.
+__device__ __forceinline__ void attn_item(const AttnTcParams& p, int w, int& qblk, int& head, int& batch) {
+    const int hb = p.n_heads * p.n_batch;
+    int r;
+    if (p.causal_pos >= 0) { qblk = p.n_qblk - 1 - w / hb; r = w % hb; }
+    else { qblk = w % p.n_qblk; r = w / p.n_qblk; }
+    head = r % p.n_heads;
+    batch = r / p.n_heads;
+}
+__device__ __forceinline__ int attn_tiles(const AttnTcParams& p, int q0) {
+    int kv_end = p.kv_len;
+    if (p.causal_pos >= 0) kv_end = min(kv_end, p.causal_pos + min(q0 + ABQ, p.q_len));
+    return (kv_end + ABKV - 1) / ABKV;
+}
 
 struct AttnTcMaps {
     CUtensorMap q, k, v;     // dims 0-63, 128B swizzle
@@ -99,9 +128,10 @@ template <int D> struct AttnCfg {
     static constexpr int Q_MAIN = ABQ * 128, Q_TAIL = TAIL ? ABQ * 32 : 0;
     static constexpr int KV_MAIN = ABKV * 128, KV_TAIL = TAIL ? ABKV * 32 : 0;
     static constexpr int Q_BYTES = Q_MAIN + Q_TAIL;
-    static constexpr int STAGE_BYTES = KV_MAIN + KV_TAIL;    // one K (or V) tile: main | tail
+    static constexpr int STAGE_BYTES = KV_MAIN + KV_TAIL;    // one K tile: main | 32B-swizzled tail
+    static constexpr int V_STAGE_BYTES = KV_MAIN + (TAIL ? KV_MAIN : 0);   // one V tile: main | second 128B atom
     static constexpr int P_BYTES = ABQ * 128;                // 128 rows x 64 keys f16, two buffers
-    static constexpr int SMEM = 1024 + Q_BYTES + 2 * STAGES * STAGE_BYTES + 2 * P_BYTES + 256;  // 97.25 / 93.25 KB
+    static constexpr int SMEM = 1024 + Q_BYTES + STAGES * (STAGE_BYTES + V_STAGE_BYTES) + 2 * P_BYTES + 256;  // 105.25 / 93.25 KB
 };
 
 template <int D>
@@ -120,8 +150,8 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
     // K and V travel through separate rings: a K stage is free again as soon as S(j) has been computed,
     // a V stage only after PV(j), two MMAs later; one shared ring would hold the next K load back
     const uint32_t sm_k = sm_q + Cfg::Q_BYTES, sm_v = sm_k + ST * Cfg::STAGE_BYTES;  // per stage: main | tail
-    const uint32_t sm_p = sm_v + ST * Cfg::STAGE_BYTES;
-    uint8_t* p_ptr = base_ptr + Cfg::Q_BYTES + 2 * ST * Cfg::STAGE_BYTES;
+    const uint32_t sm_p = sm_v + ST * Cfg::V_STAGE_BYTES;
+    uint8_t* p_ptr = base_ptr + Cfg::Q_BYTES + ST * (Cfg::STAGE_BYTES + Cfg::V_STAGE_BYTES);
     const uint32_t bars = sm_p + 2 * Cfg::P_BYTES;
     uint8_t* bars_ptr = p_ptr + 2 * Cfg::P_BYTES;
     const uint32_t b_qfull = bars, b_kfull = bars + 8, b_kempty = b_kfull + 8 * ST, b_vfull = b_kempty + 8 * ST;
@@ -130,15 +160,10 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
     const uint32_t b_pempty = b_pfull + 16;      // ends at bars + 8 + 32 * ST + 64 <= bars + 168
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_ptr + 176);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 180);
+    const uint32_t b_qempty = bars + 184;        // the last S product of an item has read Q
+    const uint32_t b_oempty = bars + 192;        // the softmax warps have read an item's O out of TMEM
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int head = blockIdx.y, batch = blockIdx.z;
-    // causal: the last query blocks see the most keys; they get the lowest block ids and start first
-    const int qblk = p.causal_pos >= 0 ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
-    const int q0 = qblk * ABQ;
-    int kv_end = p.kv_len;
-    if (p.causal_pos >= 0) kv_end = min(kv_end, p.causal_pos + min(q0 + ABQ, p.q_len));
-    const int nt = (kv_end + ABKV - 1) / ABKV;
 
     md_pdl_launch_dependents();
     if (threadIdx.x == 0) {
@@ -152,6 +177,8 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
             tma_prefetch_map(&tm.vt);
         }
         mbar_init(b_qfull, 1);
+        mbar_init(b_qempty, 1);
+        mbar_init(b_oempty, 4);
         for (int s = 0; s < ST; ++s) {
             mbar_init(b_kfull + 8 * s, 1);
             mbar_init(b_kempty + 8 * s, 1);
@@ -180,29 +207,38 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
     const uint32_t tmem_base = *tmem_slot;
     md_pdl_wait();
 
+    // Every role walks the same items in the same order.  Ring slots, the S / P buffer of a tile and the wait
+    // parities run on over the items: `g` counts the key tiles this CTA has handled before the current item.
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            int cq[4] = {0, 0, 0, 0}, ck[4] = {0, 0, 0, 0};
-            cq[p.q_dim_row] = q0; cq[p.q_dim_head] = head; cq[p.q_dim_batch] = batch;
-            ck[p.kv_dim_head] = head; ck[p.kv_dim_batch] = batch;
-            mbar_expect_tx(b_qfull, Cfg::Q_BYTES);
-            tma_load_4d(sm_q, &tm.q, b_qfull, 0, cq[1], cq[2], cq[3]);
-            if (TAIL) tma_load_4d(sm_qt, &tm.qt, b_qfull, 64, cq[1], cq[2], cq[3]);
-            for (int j = 0; j < nt; ++j) {
-                const int st = j % ST;
-                const uint32_t par = (uint32_t)((j / ST) & 1) ^ 1u;
-                ck[p.kv_dim_row] = j * ABKV;
-                mbar_wait(b_kempty + 8 * st, par, abort_flag, flags, 11);
-                const uint32_t kfull = b_kfull + 8 * st, kdst = sm_k + st * Cfg::STAGE_BYTES;
-                mbar_expect_tx(kfull, Cfg::STAGE_BYTES);
-                tma_load_4d(kdst, &tm.k, kfull, 0, ck[1], ck[2], ck[3]);
-                if (TAIL) tma_load_4d(kdst + Cfg::KV_MAIN, &tm.kt, kfull, 64, ck[1], ck[2], ck[3]);
-                mbar_wait(b_vempty + 8 * st, par, abort_flag, flags, 10);
-                const uint32_t vfull = b_vfull + 8 * st, vdst = sm_v + st * Cfg::STAGE_BYTES;
-                mbar_expect_tx(vfull, Cfg::STAGE_BYTES);
-                tma_load_4d(vdst, &tm.v, vfull, 0, ck[1], ck[2], ck[3]);
-                if (TAIL) tma_load_4d(vdst + Cfg::KV_MAIN, &tm.vt, vfull, 64, ck[1], ck[2], ck[3]);
+            uint32_t st = 0, par = 1;  // ring slot and the parity that says "slot free"
+            int it = 0;
+            for (int w = blockIdx.x; w < p.n_items; w += gridDim.x, ++it) {
+                int qblk, head, batch;
+                attn_item(p, w, qblk, head, batch);
+                const int q0 = qblk * ABQ, nt = attn_tiles(p, q0);
+                int cq[4] = {0, 0, 0, 0}, ck[4] = {0, 0, 0, 0};
+                cq[p.q_dim_row] = q0; cq[p.q_dim_head] = head; cq[p.q_dim_batch] = batch;
+                ck[p.kv_dim_head] = head; ck[p.kv_dim_batch] = batch;
+                if (it > 0) mbar_wait(b_qempty, (uint32_t)((it - 1) & 1), abort_flag, flags, 9);
+                mbar_expect_tx(b_qfull, Cfg::Q_BYTES);
+                tma_load_4d(sm_q, &tm.q, b_qfull, 0, cq[1], cq[2], cq[3]);
+                if (TAIL) tma_load_4d(sm_qt, &tm.qt, b_qfull, 64, cq[1], cq[2], cq[3]);
+                for (int j = 0; j < nt; ++j) {
+                    ck[p.kv_dim_row] = j * ABKV;
+                    mbar_wait(b_kempty + 8 * st, par, abort_flag, flags, 11);
+                    const uint32_t kfull = b_kfull + 8 * st, kdst = sm_k + st * Cfg::STAGE_BYTES;
+                    mbar_expect_tx(kfull, Cfg::STAGE_BYTES);
+                    tma_load_4d(kdst, &tm.k, kfull, 0, ck[1], ck[2], ck[3]);
+                    if (TAIL) tma_load_4d(kdst + Cfg::KV_MAIN, &tm.kt, kfull, 64, ck[1], ck[2], ck[3]);
+                    mbar_wait(b_vempty + 8 * st, par, abort_flag, flags, 10);
+                    const uint32_t vfull = b_vfull + 8 * st, vdst = sm_v + st * Cfg::V_STAGE_BYTES;
+                    mbar_expect_tx(vfull, Cfg::V_STAGE_BYTES);
+                    tma_load_4d(vdst, &tm.v, vfull, 0, ck[1], ck[2], ck[3]);
+                    if (TAIL) tma_load_4d(vdst + Cfg::KV_MAIN, &tm.vt, vfull, 64, ck[1], ck[2], ck[3]);
+                    if (++st == ST) { st = 0; par ^= 1u; }
+                }
             }
             if (*abort_flag) {  // let copies in flight land before the CTA's shared memory is released
                 const unsigned long long t0 = global_ns();
@@ -213,188 +249,207 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc_s = (1u << 4) | ((uint32_t)(ABKV >> 3) << 17) | ((uint32_t)(ABQ >> 4) << 24);
-            const uint32_t idesc_pv = (1u << 4) | (1u << 16) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(ABQ >> 4) << 24);
-            const uint32_t idesc_pvt = (1u << 4) | (1u << 16) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(ABQ >> 4) << 24);
-            // descriptors as 32-bit halves (tc_common.cuh): constant high words, low words advanced by adds; the
-            // ring slot (j % ST) and its wait parity are kept as running counters instead of divisions
+            const uint32_t idesc_pv =
+                (1u << 4) | (1u << 16) | ((uint32_t)(Cfg::DPAD >> 3) << 17) | ((uint32_t)(ABQ >> 4) << 24);
+            // descriptors as 32-bit halves (tc_common.cuh): constant high words, low words advanced by adds; ring
+            // slots and their wait parities are running counters
             const uint32_t hi128 = desc_hi(1024, 2), hi32 = desc_hi(256, 6);
             const uint32_t q_lo = desc_lo(sm_q, 16), qt_lo = desc_lo(sm_qt, 16);
             const uint32_t k_lo0 = desc_lo(sm_k, 16), kt_lo0 = desc_lo(sm_k + Cfg::KV_MAIN, 16);
             const uint32_t p_lo0 = desc_lo(sm_p, 16);
-            const uint32_t v_lo0 = desc_lo(sm_v, ABKV * 128), vt_lo0 = desc_lo(sm_v + Cfg::KV_MAIN, 512);
-            constexpr uint32_t STAGE16 = Cfg::STAGE_BYTES >> 4, P16 = Cfg::P_BYTES >> 4;
+            // V: MN-major, 64 dims contiguous per key; the next atom along the dims (d = 72) lies one main tile further
+            const uint32_t v_lo0 = desc_lo(sm_v, ABKV * 128);
+            constexpr uint32_t STAGE16 = Cfg::STAGE_BYTES >> 4, VSTAGE16 = Cfg::V_STAGE_BYTES >> 4, P16 = Cfg::P_BYTES >> 4;
+            uint32_t st = 0, par = 0;        // ring slot and parity of the next S product
             uint32_t pv_st = 0, pv_par = 0;  // ring slot and parity of the next PV product
+            uint32_t g = 0;                  // key tiles of earlier items
+            int it = 0;
             auto issue_pv = [&](int i) {
-                const uint32_t pb = (uint32_t)i & 1u;
+                const uint32_t gi = g + (uint32_t)i, pb = gi & 1u;
                 mbar_wait(b_vfull + 8 * pv_st, pv_par, abort_flag, flags, 13);
-                mbar_wait(b_pfull + 8 * pb, (uint32_t)((i >> 1) & 1), abort_flag, flags, 12);
+                mbar_wait(b_pfull + 8 * pb, (gi >> 1) & 1u, abort_flag, flags, 12);
+                // the first product of an item overwrites O: the previous item's output must have left TMEM
+                if (i == 0 && it > 0) mbar_wait(b_oempty, (uint32_t)((it - 1) & 1), abort_flag, flags, 17);
                 tc_fence_after();
-                const uint32_t p_lo = p_lo0 + pb * P16, v_lo = v_lo0 + pv_st * STAGE16, vt_lo = vt_lo0 + pv_st * STAGE16;
-                // V is the MN-major B operand: 64 dims contiguous per key, 16 keys = 2048 B per k-step; the tail
-                // holds 16 dims per key (32B swizzle), 16 keys = 512 B per k-step
-                if (i == 0) {
-                    tc_mma_f16_parts<false>(tmem_base + T_O, p_lo, hi128, v_lo, hi128, idesc_pv);
-                    if (TAIL) tc_mma_f16_parts<false>(tmem_base + T_O + 64, p_lo, hi128, vt_lo, hi32, idesc_pvt);
-                } else {
-                    tc_mma_f16_parts<true>(tmem_base + T_O, p_lo, hi128, v_lo, hi128, idesc_pv);
-                    if (TAIL) tc_mma_f16_parts<true>(tmem_base + T_O + 64, p_lo, hi128, vt_lo, hi32, idesc_pvt);
-                }
+                const uint32_t p_lo = p_lo0 + pb * P16, v_lo = v_lo0 + pv_st * VSTAGE16;
+                // 16 keys = 2048 B per k-step in every atom
+                if (i == 0) tc_mma_f16_parts<false>(tmem_base + T_O, p_lo, hi128, v_lo, hi128, idesc_pv);
+                else tc_mma_f16_parts<true>(tmem_base + T_O, p_lo, hi128, v_lo, hi128, idesc_pv);
 #pragma unroll
-                for (int ks = 1; ks < ABKV / 16; ++ks) {
+                for (int ks = 1; ks < ABKV / 16; ++ks)
                     tc_mma_f16_parts<true>(tmem_base + T_O, p_lo + ks * 2, hi128, v_lo + ks * 128, hi128, idesc_pv);
-                    if (TAIL)
-                        tc_mma_f16_parts<true>(tmem_base + T_O + 64, p_lo + ks * 2, hi128, vt_lo + ks * 32, hi32, idesc_pvt);
-                }
                 tc_commit(b_pempty + 8 * pb);
                 tc_commit(b_vempty + 8 * pv_st);
                 if (++pv_st == ST) { pv_st = 0; pv_par ^= 1u; }
             };
-            mbar_wait(b_qfull, 0, abort_flag, flags, 14);
-            uint32_t st = 0, par = 0;
-            for (int j = 0; j < nt; ++j) {
-                const uint32_t sb = (uint32_t)j & 1u;
-                mbar_wait(b_kfull + 8 * st, par, abort_flag, flags, 15);
-                mbar_wait(b_sempty + 8 * sb, (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, flags, 16);
-                tc_fence_after();
-                const uint32_t t_s = tmem_base + sb * 64u, k_lo = k_lo0 + st * STAGE16;
-                tc_mma_f16_parts<false>(t_s, q_lo, hi128, k_lo, hi128, idesc_s);
+            for (int w = blockIdx.x; w < p.n_items; w += gridDim.x, ++it) {
+                int qblk, head, batch;
+                attn_item(p, w, qblk, head, batch);
+                const int nt = attn_tiles(p, qblk * ABQ);
+                mbar_wait(b_qfull, (uint32_t)(it & 1), abort_flag, flags, 14);
+                for (int j = 0; j < nt; ++j) {
+                    const uint32_t gj = g + (uint32_t)j, sb = gj & 1u;
+                    mbar_wait(b_kfull + 8 * st, par, abort_flag, flags, 15);
+                    mbar_wait(b_sempty + 8 * sb, ((gj >> 1) & 1u) ^ 1u, abort_flag, flags, 16);
+                    tc_fence_after();
+                    const uint32_t t_s = tmem_base + sb * 64u, k_lo = k_lo0 + st * STAGE16;
+                    tc_mma_f16_parts<false>(t_s, q_lo, hi128, k_lo, hi128, idesc_s);
 #pragma unroll
-                for (int ks = 1; ks < 4; ++ks) tc_mma_f16_parts<true>(t_s, q_lo + ks * 2, hi128, k_lo + ks * 2, hi128, idesc_s);
-                if (TAIL) tc_mma_f16_parts<true>(t_s, qt_lo, hi32, kt_lo0 + st * STAGE16, hi32, idesc_s);
-                tc_commit(b_sfull + 8 * sb);
-                tc_commit(b_kempty + 8 * st);
-                if (++st == ST) { st = 0; par ^= 1u; }
-                if (j > 0) issue_pv(j - 1);
+                    for (int ks = 1; ks < 4; ++ks)
+                        tc_mma_f16_parts<true>(t_s, q_lo + ks * 2, hi128, k_lo + ks * 2, hi128, idesc_s);
+                    if (TAIL) tc_mma_f16_parts<true>(t_s, qt_lo, hi32, kt_lo0 + st * STAGE16, hi32, idesc_s);
+                    tc_commit(b_sfull + 8 * sb);
+                    tc_commit(b_kempty + 8 * st);
+                    if (j == nt - 1) tc_commit(b_qempty);   // Q may be overwritten by the next item's
+                    if (++st == ST) { st = 0; par ^= 1u; }
+                    if (j > 0) issue_pv(j - 1);
+                }
+                if (nt > 0) issue_pv(nt - 1);
+                else mbar_arrive(b_qempty);
+                g += (uint32_t)nt;
             }
-            if (nt > 0) issue_pv(nt - 1);
         }
     } else {
         // ------------------------------------------------------------------ softmax + output (warps 2..5)
-        const int quad = warp & 3, row = quad * 32 + lane, qi = q0 + row;
+        const int quad = warp & 3, row = quad * 32 + lane;
         const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
-        const bool row_ok = qi < p.q_len;
-        float m_run = -INFINITY, l_run = 0.f;  // exponent reference (log2 units) and row sum on that reference
+        uint32_t g = 0;
+        for (int w = blockIdx.x; w < p.n_items; w += gridDim.x) {
+            int qblk, head, batch;
+            attn_item(p, w, qblk, head, batch);
+            const int q0 = qblk * ABQ, nt = attn_tiles(p, q0), qi = q0 + row;
+            const bool row_ok = qi < p.q_len;
+            float m_run = -INFINITY, l_run = 0.f;  // exponent reference (log2 units) and row sum on that reference
 
-        for (int j = 0; j < nt; ++j) {
-            const int sb = j & 1, key0 = j * ABKV;
-            mbar_wait(b_sfull + 8 * sb, (uint32_t)((j >> 1) & 1), abort_flag, flags, 19);
-            tc_fence_after();
-            uint32_t s0[32], s1[32];
-            tc_ld_32x32(t_lane + (uint32_t)(sb * 64), s0);
-            tc_ld_32x32(t_lane + (uint32_t)(sb * 64 + 32), s1);
-            tc_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(b_sempty + 8 * sb);
+            for (int j = 0; j < nt; ++j) {
+                const uint32_t gj = g + (uint32_t)j;
+                const int sb = (int)(gj & 1u), key0 = j * ABKV;
+                mbar_wait(b_sfull + 8 * sb, (gj >> 1) & 1u, abort_flag, flags, 19);
+                tc_fence_after();
+                uint32_t s0[32], s1[32];
+                tc_ld_32x32(t_lane + (uint32_t)(sb * 64), s0);
+                tc_ld_32x32(t_lane + (uint32_t)(sb * 64 + 32), s1);
+                tc_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(b_sempty + 8 * sb);
 
-            // tiles wholly inside the valid, visible region (all but the last ones) skip the per-key tests
-            const bool interior = !p.mask && key0 + ABKV <= p.kv_len &&
-                                  (p.causal_pos < 0 || key0 + ABKV - 1 <= p.causal_pos + q0 + quad * 32);
-            if (!interior) {
+                // tiles wholly inside the valid, visible region (all but the last ones) skip the per-key tests
+                const bool interior = !p.mask && key0 + ABKV <= p.kv_len &&
+                                      (p.causal_pos < 0 || key0 + ABKV - 1 <= p.causal_pos + q0 + quad * 32);
+                if (!interior) {
 #pragma unroll
-                for (int e = 0; e < 64; ++e) {
-                    const int key = key0 + e;
-                    bool vis = row_ok && key < p.kv_len;
-                    if (p.causal_pos >= 0) vis = vis && key <= p.causal_pos + qi;
-                    if (vis && p.mask) vis = p.mask[(long long)qi * p.kv_len + key] != 0;
-                    if (!vis) {
-                        if (e < 32) s0[e] = 0xff800000u; else s1[e - 32] = 0xff800000u;  // -inf
+                    for (int e = 0; e < 64; ++e) {
+                        const int key = key0 + e;
+                        bool vis = row_ok && key < p.kv_len;
+                        if (p.causal_pos >= 0) vis = vis && key <= p.causal_pos + qi;
+                        if (vis && p.mask) vis = p.mask[(long long)qi * p.kv_len + key] != 0;
+                        if (!vis) {
+                            if (e < 32) s0[e] = 0xff800000u; else s1[e - 32] = 0xff800000u;  // -inf
+                        }
                     }
                 }
-            }
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-            for (int e = 0; e < 32; e += 2) {
-                mx0 = fmaxf(mx0, __uint_as_float(s0[e]));
-                mx1 = fmaxf(mx1, __uint_as_float(s0[e + 1]));
-                mx2 = fmaxf(mx2, __uint_as_float(s1[e]));
-                mx3 = fmaxf(mx3, __uint_as_float(s1[e + 1]));
-            }
-            const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;  // -inf stays -inf (scale > 0)
+                for (int e = 0; e < 32; e += 2) {
+                    mx0 = fmaxf(mx0, __uint_as_float(s0[e]));
+                    mx1 = fmaxf(mx1, __uint_as_float(s0[e + 1]));
+                    mx2 = fmaxf(mx2, __uint_as_float(s1[e]));
+                    mx3 = fmaxf(mx3, __uint_as_float(s1[e + 1]));
+                }
+                const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;  // -inf stays -inf (scale > 0)
 
-            if (j == 0) {
-                m_run = mt;
-            } else if (__any_sync(0xffffffffu, mt > m_run + RESCALE_THRESHOLD)) {
-                // move this warp's rows to their new maxima: O(row) *= 2^(old - new), once PV(j-1) has landed
-                const float m_new = fmaxf(m_run, mt);
-                const float corr = (m_new == -INFINITY) ? 1.f : ex2_fast(m_run - m_new);
-                l_run *= corr;
-                m_run = m_new;
-                mbar_wait(b_pempty + 8 * ((j - 1) & 1), (uint32_t)(((j - 1) >> 1) & 1), abort_flag, flags, 21);
+                if (j == 0) {
+                    m_run = mt;
+                } else if (__any_sync(0xffffffffu, mt > m_run + RESCALE_THRESHOLD)) {
+                    // move this warp's rows to their new maxima: O(row) *= 2^(old - new), once PV(j-1) has landed
+                    const float m_new = fmaxf(m_run, mt);
+                    const float corr = (m_new == -INFINITY) ? 1.f : ex2_fast(m_run - m_new);
+                    l_run *= corr;
+                    m_run = m_new;
+                    mbar_wait(b_pempty + 8 * ((gj - 1) & 1u), ((gj - 1) >> 1) & 1u, abort_flag, flags, 21);
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < Cfg::DPAD / 16; ++c) {
+                        uint32_t r[16];
+                        tc_ld_32x16(t_lane + T_O + c * 16, r);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * corr);
+                        tc_st_32x16(t_lane + T_O + c * 16, r);
+                    }
+                    tc_wait_st();
+                    tc_fence_before();
+                }
+                const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+
+                float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+                uint32_t pk[32];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const float a0 = ex2_fast(fmaf(__uint_as_float(s0[2 * e]), p.scale_log2, neg_m));
+                    const float a1 = ex2_fast(fmaf(__uint_as_float(s0[2 * e + 1]), p.scale_log2, neg_m));
+                    const float b0 = ex2_fast(fmaf(__uint_as_float(s1[2 * e]), p.scale_log2, neg_m));
+                    const float b1 = ex2_fast(fmaf(__uint_as_float(s1[2 * e + 1]), p.scale_log2, neg_m));
+                    rs0 += a0; rs1 += a1; rs2 += b0; rs3 += b1;
+                    const __half2 ha = __floats2half2_rn(a0, a1), hb = __floats2half2_rn(b0, b1);
+                    pk[e] = *reinterpret_cast<const uint32_t*>(&ha);
+                    pk[16 + e] = *reinterpret_cast<const uint32_t*>(&hb);
+                }
+                l_run += (rs0 + rs1) + (rs2 + rs3);
+
+                // P buffer sb is free once the PV product two tiles back has consumed it
+                mbar_wait(b_pempty + 8 * sb, ((gj >> 1) & 1u) ^ 1u, abort_flag, flags, 20);
+                uint8_t* prow = p_ptr + sb * Cfg::P_BYTES + row * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) * 16)) =
+                        make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+                fence_async_smem();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(b_pfull + 8 * sb);
+            }
+
+            // the item's output: out of TMEM into registers first, so that the next item's PV products can start
+            uint32_t o[Cfg::DPAD / 16][16];
+            if (nt > 0) {
+                const uint32_t gl = g + (uint32_t)nt - 1u;
+                mbar_wait(b_pempty + 8 * (gl & 1u), (gl >> 1) & 1u, abort_flag, flags, 18);
                 tc_fence_after();
 #pragma unroll
-                for (int c = 0; c < Cfg::DPAD / 16; ++c) {
-                    uint32_t r[16];
-                    tc_ld_32x16(t_lane + T_O + c * 16, r);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * corr);
-                    tc_st_32x16(t_lane + T_O + c * 16, r);
-                }
-                tc_wait_st();
-                tc_fence_before();
-            }
-            const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
-
-            float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
-            uint32_t pk[32];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) {
-                const float a0 = ex2_fast(fmaf(__uint_as_float(s0[2 * e]), p.scale_log2, neg_m));
-                const float a1 = ex2_fast(fmaf(__uint_as_float(s0[2 * e + 1]), p.scale_log2, neg_m));
-                const float b0 = ex2_fast(fmaf(__uint_as_float(s1[2 * e]), p.scale_log2, neg_m));
-                const float b1 = ex2_fast(fmaf(__uint_as_float(s1[2 * e + 1]), p.scale_log2, neg_m));
-                rs0 += a0; rs1 += a1; rs2 += b0; rs3 += b1;
-                const __half2 ha = __floats2half2_rn(a0, a1), hb = __floats2half2_rn(b0, b1);
-                pk[e] = *reinterpret_cast<const uint32_t*>(&ha);
-                pk[16 + e] = *reinterpret_cast<const uint32_t*>(&hb);
-            }
-            l_run += (rs0 + rs1) + (rs2 + rs3);
-
-            // P buffer sb is free once PV(j-2) has consumed it
-            mbar_wait(b_pempty + 8 * sb, (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, flags, 20);
-            uint8_t* prow = p_ptr + sb * Cfg::P_BYTES + row * 128;
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) * 16)) =
-                    make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-            fence_async_smem();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(b_pfull + 8 * sb);
-        }
-
-        if (nt > 0) {
-            mbar_wait(b_pempty + 8 * ((nt - 1) & 1), (uint32_t)(((nt - 1) >> 1) & 1), abort_flag, flags, 18);
-            tc_fence_after();
-        }
-        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-        __half* orow = p.out + batch * p.o_batch + head * p.o_head + (long long)qi * p.o_row;
-#pragma unroll
-        for (int c = 0; c < Cfg::DPAD / 16; ++c) {
-            uint32_t r[16];
-            if (nt > 0) {
-                tc_ld_32x16(t_lane + T_O + c * 16, r);
+                for (int c = 0; c < Cfg::DPAD / 16; ++c) tc_ld_32x16(t_lane + T_O + c * 16, o[c]);
                 tc_wait_ld();
+                tc_fence_before();
             } else {
 #pragma unroll
-                for (int e = 0; e < 16; ++e) r[e] = 0u;
+                for (int c = 0; c < Cfg::DPAD / 16; ++c)
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) o[c][e] = 0u;
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(b_oempty);
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            __half* orow = p.out + batch * p.o_batch + head * p.o_head + (long long)qi * p.o_row;
             if (row_ok) {
 #pragma unroll
-                for (int g = 0; g < 2; ++g) {
-                    if (c * 16 + g * 8 < D) {
-                        uint32_t w[4];
+                for (int c = 0; c < Cfg::DPAD / 16; ++c) {
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const __half2 h = __floats2half2_rn(__uint_as_float(r[g * 8 + 2 * e]) * inv,
-                                                                __uint_as_float(r[g * 8 + 2 * e + 1]) * inv);
-                            w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                    for (int h8 = 0; h8 < 2; ++h8) {
+                        if (c * 16 + h8 * 8 < D) {
+                            uint32_t wv[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const __half2 h = __floats2half2_rn(__uint_as_float(o[c][h8 * 8 + 2 * e]) * inv,
+                                                                    __uint_as_float(o[c][h8 * 8 + 2 * e + 1]) * inv);
+                                wv[e] = *reinterpret_cast<const uint32_t*>(&h);
+                            }
+                            *reinterpret_cast<uint4*>(orow + c * 16 + h8 * 8) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
                         }
-                        *reinterpret_cast<uint4*>(orow + c * 16 + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
             }
+            g += (uint32_t)nt;
         }
     }
 
@@ -490,7 +545,7 @@ int md_launch_sdpa_tc(md_ctx* ctx, const __half* q, const __half* k, const __hal
     if (d > 64) {
         MD_TRY(md_make_map_4d(ctx, &maps.qt, q, mq.dims, mq.strides_bytes, 16, boxq, 32));
         MD_TRY(md_make_map_4d(ctx, &maps.kt, k, mk.dims, mk.strides_bytes, 16, boxk, 32));
-        MD_TRY(md_make_map_4d(ctx, &maps.vt, v, mk.dims, mk.strides_bytes, 16, boxk, 32));
+        MD_TRY(md_make_map_4d(ctx, &maps.vt, v, mk.dims, mk.strides_bytes, 64, boxk, 128));   // dims 64..127: 72.. zero fill
     } else {
         maps.qt = maps.q; maps.kt = maps.k; maps.vt = maps.v;
     }
@@ -501,6 +556,13 @@ int md_launch_sdpa_tc(md_ctx* ctx, const __half* q, const __half* k, const __hal
     p.o_row = (long long)o_row; p.o_head = (long long)o_head; p.o_batch = (long long)o_batch;
     p.q_dim_row = mq.dim_of[0]; p.q_dim_head = mq.dim_of[1]; p.q_dim_batch = mq.dim_of[2];
     p.kv_dim_row = mk.dim_of[0]; p.kv_dim_head = mk.dim_of[1]; p.kv_dim_batch = mk.dim_of[2];
-    dim3 grid((unsigned)((q_len + ABQ - 1) / ABQ), (unsigned)n_heads, (unsigned)batch);
+    p.n_qblk = (int)((q_len + ABQ - 1) / ABQ); p.n_heads = (int)n_heads; p.n_batch = (int)batch;
+    const size_t n_items = (size_t)p.n_qblk * n_heads * batch;
+    if (n_items > (size_t)INT_MAX) return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 attention: too many query blocks");
+    p.n_items = (int)n_items;
+    // at most two CTAs per SM (what fits); option attn_ctas_per_sm = 0 gives every item its own CTA
+    size_t ctas = n_items;
+    if (ctx->attn_ctas_per_sm > 0) ctas = std::min(n_items, (size_t)ctx->attn_ctas_per_sm * (size_t)ctx->sm_count);
+    dim3 grid((unsigned)ctas);
     return d == 64 ? launch_attn_tc<64>(ctx, maps, p, grid) : launch_attn_tc<72>(ctx, maps, p, grid);
 }

@@ -330,6 +330,11 @@ int md_set_option(md_ctx* ctx, const char* key, long value) {
     if (!strcmp(key, "pdl")) { ctx->pdl = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "prefill_fork")) { ctx->prefill_fork = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "decode_fork")) { ctx->decode_fork = value ? 1 : 0; return MD_OK; }
+    if (!strcmp(key, "attn_ctas_per_sm")) {
+        if (value < 0 || value > 2) return md_fail(ctx, MD_ERR_INVALID_ARG, "attn_ctas_per_sm must be 0, 1 or 2");
+        ctx->attn_ctas_per_sm = (int)value;
+        return MD_OK;
+    }
     if (!strcmp(key, "decode_loop")) { ctx->decode_loop = (int)value; return MD_OK; }
     if (!strcmp(key, "decode_mlp_split")) {
         MD_NEED(ctx, value == 0 || value == 2 || value == 4, "decode_mlp_split must be 0, 2 or 4");

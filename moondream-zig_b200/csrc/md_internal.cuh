@@ -89,6 +89,8 @@ struct md_ctx {
     int prefill_fork = 1;       // md_set_option("prefill_fork"): prefill layers run the MLP beside the attention
     int decode_split_ln = 5;    // md_set_option("decode_split_ln"): from this many rows on a decode step runs the LayerNorm once
     int decode_fork = 1;        // md_set_option("decode_fork"): a decode layer runs as two concurrent kernel chains
+    int attn_ctas_per_sm = 2;   // md_set_option("attn_ctas_per_sm"): grid of the tcgen05 attention = this many CTAs per SM, each
+                                // walking several (query block, head, batch) items; 0 = one CTA per item
     int decode_loop = -1;       // md_set_option("decode_loop"): batched decode attention as one CTA per (head, request) when there
                                 // are at least this many pairs; -1 = 192, 0 = never
     int decode_mlp_split = 2;   // md_set_option("decode_mlp_split"): single-request decode runs the MLP as 2 or 4 chains (0 = one)

@@ -151,6 +151,29 @@ def test_fused_decode_at_long_context(ctx, oracle):
     assert_close_ref(out.numpy(), ref, "decode at 2047")
 
 
+@pytest.mark.parametrize("pos", [0, 1, 127, 128, 129, 255, 256, 257, 383, 384, 385, 1000, 2047])
+def test_fused_decode_with_one_cta_per_head_matches_reference(ctx, oracle, pos):
+    """Option decode_loop = 1: one CTA per head walks all keys in turns of 128 (two turns in flight), no merge across
+    CTAs.  Positions on both sides of every turn boundary, the empty cache and the last slot, against the oracle's
+    rope + cache append + singleMaskedSDPA; the appended k / v rows must land in the cache as well."""
+    rng = np.random.default_rng(1000 + pos)
+    kc_ref, vc_ref = f16_normal(rng, (32, 2048, 64)), f16_normal(rng, (32, 2048, 64))
+    kc_ref[:, pos:], vc_ref[:, pos:] = 0, 0
+    kc, vc = ctx.upload(kc_ref), ctx.upload(vc_ref)
+    row = f16_normal(rng, (1, 6144))
+    ref = ref_attention_block(oracle, row, kc_ref, vc_ref, pos)
+    out = ctx.alloc((1, 2048))
+    ctx.set_option("decode_loop", 1)
+    try:
+        ctx.sdpa_decode_fused(ctx.upload(row), kc, vc, out, 32, 64, 2048, pos, 32)
+        ctx.sync()
+    finally:
+        ctx.set_option("decode_loop", -1)
+    assert_close_ref(out.numpy(), ref, f"one CTA per head at {pos}")
+    assert_close_ref(kc.numpy()[:, pos], kc_ref[:, pos], "appended key", rel=2e-3)
+    np.testing.assert_array_equal(vc.numpy()[:, pos], vc_ref[:, pos])
+
+
 def test_fused_decode_rejects_full_cache(ctx, pkg):
     b = ctx.alloc((32, 2048, 64))
     with pytest.raises(pkg.MdError) as e:

@@ -87,6 +87,50 @@ def test_vit_layout(ctx, oracle, forced, crops):
         assert_close_ref(got[c * T:(c + 1) * T], ref, f"crop {c}")
 
 
+_WALK: dict = {}
+
+
+@pytest.mark.parametrize("per_sm", [0, 1, 2])
+def test_ctas_that_walk_several_items_give_the_same_result(ctx, oracle, per_sm):
+    """The tcgen05 kernel's grid is capped at attn_ctas_per_sm CTAs per SM; a CTA then walks several (query block,
+    head, batch) items, carrying its rings, S / P buffers and wait parities from one item to the next.  13 crops are
+    1248 items (4-9 per CTA); the causal case (320 items) has items of 2 to 20 key tiles in one CTA's walk.  per_sm = 0 gives
+    every item its own CTA.  All three against the oracle, and bit-equal to one another."""
+    ctx.set_option("attn_tc", 1)
+    ctx.set_option("attn_ctas_per_sm", per_sm)
+    try:
+        rng = np.random.default_rng(77)
+        crops, T, H, d = 13, 729, 16, 72
+        qkv = f16_normal(rng, (crops * T, 3 * H * d))
+        out = ctx.alloc((crops * T, H * d))
+        ctx.sdpa_vit_fused(ctx.upload(qkv), out, crops, T, H, d)
+        ctx.sync()
+        got = out.numpy()
+        for c in (0, 6, 12):
+            blk = qkv[c * T:(c + 1) * T]
+            q, k, v = [np.ascontiguousarray(blk[:, i * H * d:(i + 1) * H * d].reshape(T, H, d).transpose(1, 0, 2))
+                       for i in range(3)]
+            ref = np.ascontiguousarray(oracle.sdpa_maskless(q, k, v).transpose(1, 0, 2)).reshape(T, H * d)
+            assert_close_ref(got[c * T:(c + 1) * T], ref, f"crop {c}")
+        S = 1230
+        qkv2 = f16_normal(rng, (S, 6144))
+        kc, vc, o2 = ctx.alloc((32, 2048, 64)), ctx.alloc((32, 2048, 64)), ctx.alloc((S, 2048))
+        ctx.sdpa_prefill_fused(ctx.upload(qkv2), kc, vc, o2, S, 32, 64, 2048, 0, 32)
+        ctx.sync()
+        got2 = o2.numpy()
+    finally:
+        ctx.set_option("attn_ctas_per_sm", 2)
+        ctx.set_option("attn_tc", -1)
+    _WALK[per_sm] = (got, got2)
+    if per_sm == 0:   # the causal case against the oracle once; the other grids must equal this one bit for bit
+        from test_gpu_attention import ref_attention_block
+        kc_ref, vc_ref = np.zeros((32, 2048, 64), np.float16), np.zeros((32, 2048, 64), np.float16)
+        assert_close_ref(got2, ref_attention_block(oracle, qkv2, kc_ref, vc_ref, 0), "causal prefill of 1230 rows")
+    elif 0 in _WALK:
+        np.testing.assert_array_equal(got, _WALK[0][0])
+        np.testing.assert_array_equal(got2, _WALK[0][1])
+
+
 def test_forced_tcgen05_rejects_other_head_dims(ctx, pkg):
     ctx.set_option("attn_tc", 1)
     try:

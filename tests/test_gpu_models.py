@@ -280,33 +280,30 @@ def test_text_batched_decode_equals_single_requests(ctx, models_mod, cluster_mer
 def test_text_batched_decode_with_one_cta_per_head_and_request_equals_single_requests(ctx, models_mod):
     """Option decode_loop: the attention of a batched step as one CTA per (head, request) walking all keys (no merge
     across CTAs).  Prompt lengths sit on both sides of the 128-key turn and of the two-turn unroll; 12 steps carry
-    some requests across a boundary while decoding.  Tokens must equal the single-request runs, whose attention
-    splits the keys over CTAs."""
+    some requests across a boundary while decoding.  The single-request runs use the same kernel (same summation
+    order), so the tokens must be equal; the kernel itself is checked against the oracle in test_gpu_attention.py."""
     w = text_weights(4024, n_layers=2, hidden=512, vocab=2048)
     gpu = models_mod.TextModel(ctx, w)
     rng = np.random.default_rng(24)
     prompts = [w["wte"][rng.integers(0, 2048, n)] for n in (1, 120, 128, 129, 250, 256, 257, 600)]
-    singles, firsts = [], []
-    for p in prompts:
-        r = gpu.request()
-        _, _, tok = gpu.forward(r, p)
-        firsts.append(tok)
-        singles.append(gpu.generate(r, tok, 12))
-        r.close()
-    got = {}
-    for loop in (1, 0):
+    ctx.set_option("decode_loop", 1)   # from one (head, request) pair on
+    try:
+        singles, firsts = [], []
+        for p in prompts:
+            r = gpu.request()
+            _, _, tok = gpu.forward(r, p)
+            firsts.append(tok)
+            singles.append(gpu.generate(r, tok, 12))
+            r.close()
         reqs = [gpu.request() for _ in prompts]
         for r, p in zip(reqs, prompts):
             gpu.forward(r, p)
-        ctx.set_option("decode_loop", loop)   # 1: from one pair on; 0: never
-        try:
-            got[loop] = gpu.generate_batch(reqs, firsts, 12)
-        finally:
-            ctx.set_option("decode_loop", -1)
-        for r in reqs:
-            r.close()
-    np.testing.assert_array_equal(got[1], np.stack(singles))
-    np.testing.assert_array_equal(got[0], np.stack(singles))
+        batch = gpu.generate_batch(reqs, firsts, 12)
+    finally:
+        ctx.set_option("decode_loop", -1)
+    np.testing.assert_array_equal(batch, np.stack(singles))
+    for r in reqs:
+        r.close()
     gpu.close()
 
 
@@ -329,10 +326,12 @@ def test_text_batched_decode_with_one_layernorm_kernel_equals_the_fused_kernels(
     for r, p in zip(reqs, prompts):
         gpu.forward(r, p)
     ctx.set_option("decode_split_ln", split_ln)
+    ctx.set_option("decode_loop", 0)   # the attention of the single-request runs (same summation order: same tokens)
     try:
         batch = gpu.generate_batch(reqs, firsts, 8)
     finally:
         ctx.set_option("decode_split_ln", 5)
+        ctx.set_option("decode_loop", -1)
     np.testing.assert_array_equal(batch, np.stack(singles))
     for r in reqs:
         r.close()
