@@ -114,6 +114,11 @@ __device__ __forceinline__ void tc_st_32x16(uint32_t taddr, const uint32_t (&r)[
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
+__device__ __forceinline__ void tc_st_32x8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float ex2_fast(float x) {
     float y;
@@ -122,16 +127,15 @@ __device__ __forceinline__ float ex2_fast(float x) {
 }
 
 template <int D> struct AttnCfg {
-    static constexpr bool TAIL = D > 64;                     // a 16-dim, 32B-swizzled second tile
+    static constexpr bool TAIL = D > 64;                     // dims 64.. of d = 72
     static constexpr int DPAD = TAIL ? 80 : 64;              // MMA extent of the head dimension
-    static constexpr int STAGES = TAIL ? 2 : 3;              // depth of the K ring and of the V ring
+    static constexpr int STAGES = 3;                         // depth of the K ring and of the V ring
     static constexpr int Q_MAIN = ABQ * 128, Q_TAIL = TAIL ? ABQ * 32 : 0;
     static constexpr int KV_MAIN = ABKV * 128, KV_TAIL = TAIL ? ABKV * 32 : 0;
     static constexpr int Q_BYTES = Q_MAIN + Q_TAIL;
     static constexpr int STAGE_BYTES = KV_MAIN + KV_TAIL;    // one K tile: main | 32B-swizzled tail
     static constexpr int V_STAGE_BYTES = KV_MAIN + (TAIL ? KV_MAIN : 0);   // one V tile: main | second 128B atom
-    static constexpr int P_BYTES = ABQ * 128;                // 128 rows x 64 keys f16, two buffers
-    static constexpr int SMEM = 1024 + Q_BYTES + STAGES * (STAGE_BYTES + V_STAGE_BYTES) + 2 * P_BYTES + 256;  // 105.25 / 93.25 KB
+    static constexpr int SMEM = 1024 + Q_BYTES + STAGES * (STAGE_BYTES + V_STAGE_BYTES) + 256;  // 99.25 / 65.25 KB
 };
 
 template <int D>
@@ -140,8 +144,10 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
     using Cfg = AttnCfg<D>;
     constexpr int ST = Cfg::STAGES;
     constexpr bool TAIL = Cfg::TAIL;
-    constexpr uint32_t TMEM_COLS = 256;          // S0 @0, S1 @64, O @128 (64 or 80 columns)
-    constexpr uint32_t T_O = 128;
+    // Tensor memory, 256 columns: two S buffers of 64 (P, as packed f16, takes the first 32 columns of the buffer its
+    // S came from), O (64 or 80), Q as packed f16 (32 or 40)
+    constexpr uint32_t TMEM_COLS = 256, T_O = 128, T_Q = 208;
+    static_assert(T_O + Cfg::DPAD <= T_Q && T_Q + Cfg::DPAD / 2 <= TMEM_COLS, "tensor memory layout");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -150,18 +156,18 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
     // K and V travel through separate rings: a K stage is free again as soon as S(j) has been computed,
     // a V stage only after PV(j), two MMAs later; one shared ring would hold the next K load back
     const uint32_t sm_k = sm_q + Cfg::Q_BYTES, sm_v = sm_k + ST * Cfg::STAGE_BYTES;  // per stage: main | tail
-    const uint32_t sm_p = sm_v + ST * Cfg::V_STAGE_BYTES;
-    uint8_t* p_ptr = base_ptr + Cfg::Q_BYTES + ST * (Cfg::STAGE_BYTES + Cfg::V_STAGE_BYTES);
-    const uint32_t bars = sm_p + 2 * Cfg::P_BYTES;
-    uint8_t* bars_ptr = p_ptr + 2 * Cfg::P_BYTES;
+    const uint32_t bars = sm_v + ST * Cfg::V_STAGE_BYTES;
+    uint8_t* bars_ptr = base_ptr + Cfg::Q_BYTES + ST * (Cfg::STAGE_BYTES + Cfg::V_STAGE_BYTES);
     const uint32_t b_qfull = bars, b_kfull = bars + 8, b_kempty = b_kfull + 8 * ST, b_vfull = b_kempty + 8 * ST;
     const uint32_t b_vempty = b_vfull + 8 * ST;
-    const uint32_t b_sfull = b_vempty + 8 * ST, b_sempty = b_sfull + 16, b_pfull = b_sempty + 16;
-    const uint32_t b_pempty = b_pfull + 16;      // ends at bars + 8 + 32 * ST + 64 <= bars + 168
+    const uint32_t b_sfull = b_vempty + 8 * ST;  // S(j) is in tensor memory
+    const uint32_t b_pfull = b_sfull + 16;       // the softmax warps have written P(j) over it
+    const uint32_t b_pvdone = b_pfull + 16;      // PV(j) has completed: O is current, the S / P buffer is free
+    const uint32_t b_qcopied = b_pvdone + 16;    // the softmax warps have moved Q from shared to tensor memory
+    const uint32_t b_oempty = b_qcopied + 8;     // ... and have read an item's O out of tensor memory
+    // ends at bars + 8 + 32 * ST + 48 + 16 = bars + 168
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_ptr + 176);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 180);
-    const uint32_t b_qempty = bars + 184;        // the last S product of an item has read Q
-    const uint32_t b_oempty = bars + 192;        // the softmax warps have read an item's O out of TMEM
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -177,7 +183,7 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
             tma_prefetch_map(&tm.vt);
         }
         mbar_init(b_qfull, 1);
-        mbar_init(b_qempty, 1);
+        mbar_init(b_qcopied, 4);
         mbar_init(b_oempty, 4);
         for (int s = 0; s < ST; ++s) {
             mbar_init(b_kfull + 8 * s, 1);
@@ -187,9 +193,8 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(b_sfull + 8 * b, 1);
-            mbar_init(b_sempty + 8 * b, 4);
             mbar_init(b_pfull + 8 * b, 4);
-            mbar_init(b_pempty + 8 * b, 1);
+            mbar_init(b_pvdone + 8 * b, 1);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -221,7 +226,7 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
                 int cq[4] = {0, 0, 0, 0}, ck[4] = {0, 0, 0, 0};
                 cq[p.q_dim_row] = q0; cq[p.q_dim_head] = head; cq[p.q_dim_batch] = batch;
                 ck[p.kv_dim_head] = head; ck[p.kv_dim_batch] = batch;
-                if (it > 0) mbar_wait(b_qempty, (uint32_t)((it - 1) & 1), abort_flag, flags, 9);
+                if (it > 0) mbar_wait(b_qcopied, (uint32_t)((it - 1) & 1), abort_flag, flags, 9);
                 mbar_expect_tx(b_qfull, Cfg::Q_BYTES);
                 tma_load_4d(sm_q, &tm.q, b_qfull, 0, cq[1], cq[2], cq[3]);
                 if (TAIL) tma_load_4d(sm_qt, &tm.qt, b_qfull, 64, cq[1], cq[2], cq[3]);
@@ -248,18 +253,19 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
+            // both products take their A operand (Q, P: K-major, packed f16) from tensor memory, 8 columns per
+            // k-step of 16; only K and V are read from shared memory
             const uint32_t idesc_s = (1u << 4) | ((uint32_t)(ABKV >> 3) << 17) | ((uint32_t)(ABQ >> 4) << 24);
             const uint32_t idesc_pv =
                 (1u << 4) | (1u << 16) | ((uint32_t)(Cfg::DPAD >> 3) << 17) | ((uint32_t)(ABQ >> 4) << 24);
             // descriptors as 32-bit halves (tc_common.cuh): constant high words, low words advanced by adds; ring
             // slots and their wait parities are running counters
             const uint32_t hi128 = desc_hi(1024, 2), hi32 = desc_hi(256, 6);
-            const uint32_t q_lo = desc_lo(sm_q, 16), qt_lo = desc_lo(sm_qt, 16);
             const uint32_t k_lo0 = desc_lo(sm_k, 16), kt_lo0 = desc_lo(sm_k + Cfg::KV_MAIN, 16);
-            const uint32_t p_lo0 = desc_lo(sm_p, 16);
             // V: MN-major, 64 dims contiguous per key; the next atom along the dims (d = 72) lies one main tile further
             const uint32_t v_lo0 = desc_lo(sm_v, ABKV * 128);
-            constexpr uint32_t STAGE16 = Cfg::STAGE_BYTES >> 4, VSTAGE16 = Cfg::V_STAGE_BYTES >> 4, P16 = Cfg::P_BYTES >> 4;
+            constexpr uint32_t STAGE16 = Cfg::STAGE_BYTES >> 4, VSTAGE16 = Cfg::V_STAGE_BYTES >> 4;
+            const uint32_t t_q = tmem_base + T_Q;
             uint32_t st = 0, par = 0;        // ring slot and parity of the next S product
             uint32_t pv_st = 0, pv_par = 0;  // ring slot and parity of the next PV product
             uint32_t g = 0;                  // key tiles of earlier items
@@ -268,17 +274,17 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
                 const uint32_t gi = g + (uint32_t)i, pb = gi & 1u;
                 mbar_wait(b_vfull + 8 * pv_st, pv_par, abort_flag, flags, 13);
                 mbar_wait(b_pfull + 8 * pb, (gi >> 1) & 1u, abort_flag, flags, 12);
-                // the first product of an item overwrites O: the previous item's output must have left TMEM
+                // the first product of an item overwrites O: the previous item's output must have left tensor memory
                 if (i == 0 && it > 0) mbar_wait(b_oempty, (uint32_t)((it - 1) & 1), abort_flag, flags, 17);
                 tc_fence_after();
-                const uint32_t p_lo = p_lo0 + pb * P16, v_lo = v_lo0 + pv_st * VSTAGE16;
-                // 16 keys = 2048 B per k-step in every atom
-                if (i == 0) tc_mma_f16_parts<false>(tmem_base + T_O, p_lo, hi128, v_lo, hi128, idesc_pv);
-                else tc_mma_f16_parts<true>(tmem_base + T_O, p_lo, hi128, v_lo, hi128, idesc_pv);
+                const uint32_t t_p = tmem_base + pb * 64u, v_lo = v_lo0 + pv_st * VSTAGE16;
+                // 16 keys = 8 columns of P and 2048 B of V per k-step (in every atom)
+                if (i == 0) tc_mma_f16_ts<false>(tmem_base + T_O, t_p, v_lo, hi128, idesc_pv);
+                else tc_mma_f16_ts<true>(tmem_base + T_O, t_p, v_lo, hi128, idesc_pv);
 #pragma unroll
                 for (int ks = 1; ks < ABKV / 16; ++ks)
-                    tc_mma_f16_parts<true>(tmem_base + T_O, p_lo + ks * 2, hi128, v_lo + ks * 128, hi128, idesc_pv);
-                tc_commit(b_pempty + 8 * pb);
+                    tc_mma_f16_ts<true>(tmem_base + T_O, t_p + ks * 8, v_lo + ks * 128, hi128, idesc_pv);
+                tc_commit(b_pvdone + 8 * pb);
                 tc_commit(b_vempty + 8 * pv_st);
                 if (++pv_st == ST) { pv_st = 0; pv_par ^= 1u; }
             };
@@ -286,26 +292,24 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
                 int qblk, head, batch;
                 attn_item(p, w, qblk, head, batch);
                 const int nt = attn_tiles(p, qblk * ABQ);
-                mbar_wait(b_qfull, (uint32_t)(it & 1), abort_flag, flags, 14);
+                if (nt > 0) mbar_wait(b_qcopied, (uint32_t)(it & 1), abort_flag, flags, 14);
                 for (int j = 0; j < nt; ++j) {
                     const uint32_t gj = g + (uint32_t)j, sb = gj & 1u;
                     mbar_wait(b_kfull + 8 * st, par, abort_flag, flags, 15);
-                    mbar_wait(b_sempty + 8 * sb, ((gj >> 1) & 1u) ^ 1u, abort_flag, flags, 16);
+                    // the buffer still holds P of two tiles back until that PV product has completed
+                    mbar_wait(b_pvdone + 8 * sb, ((gj >> 1) & 1u) ^ 1u, abort_flag, flags, 16);
                     tc_fence_after();
                     const uint32_t t_s = tmem_base + sb * 64u, k_lo = k_lo0 + st * STAGE16;
-                    tc_mma_f16_parts<false>(t_s, q_lo, hi128, k_lo, hi128, idesc_s);
+                    tc_mma_f16_ts<false>(t_s, t_q, k_lo, hi128, idesc_s);
 #pragma unroll
-                    for (int ks = 1; ks < 4; ++ks)
-                        tc_mma_f16_parts<true>(t_s, q_lo + ks * 2, hi128, k_lo + ks * 2, hi128, idesc_s);
-                    if (TAIL) tc_mma_f16_parts<true>(t_s, qt_lo, hi32, kt_lo0 + st * STAGE16, hi32, idesc_s);
+                    for (int ks = 1; ks < 4; ++ks) tc_mma_f16_ts<true>(t_s, t_q + ks * 8, k_lo + ks * 2, hi128, idesc_s);
+                    if (TAIL) tc_mma_f16_ts<true>(t_s, t_q + 32, kt_lo0 + st * STAGE16, hi32, idesc_s);
                     tc_commit(b_sfull + 8 * sb);
                     tc_commit(b_kempty + 8 * st);
-                    if (j == nt - 1) tc_commit(b_qempty);   // Q may be overwritten by the next item's
                     if (++st == ST) { st = 0; par ^= 1u; }
                     if (j > 0) issue_pv(j - 1);
                 }
                 if (nt > 0) issue_pv(nt - 1);
-                else mbar_arrive(b_qempty);
                 g += (uint32_t)nt;
             }
         }
@@ -313,12 +317,48 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
         // ------------------------------------------------------------------ softmax + output (warps 2..5)
         const int quad = warp & 3, row = quad * 32 + lane;
         const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const uint8_t* q_row = base_ptr + row * 128;
+        const uint8_t* qt_row = base_ptr + Cfg::Q_MAIN + row * 32;
         uint32_t g = 0;
-        for (int w = blockIdx.x; w < p.n_items; w += gridDim.x) {
+        int it = 0;
+        for (int w = blockIdx.x; w < p.n_items; w += gridDim.x, ++it) {
             int qblk, head, batch;
             attn_item(p, w, qblk, head, batch);
             const int q0 = qblk * ABQ, nt = attn_tiles(p, q0), qi = q0 + row;
             const bool row_ok = qi < p.q_len;
+
+            // this row of Q: out of the swizzled tile (16-byte chunk c of a 128-byte row sits at c ^ (row & 7); of
+            // a 32-byte row at c ^ ((row >> 2) & 1)) into tensor memory, two dims per column.  Every S product of
+            // the previous item has completed (its last PV product was waited for), so the columns are free.
+            mbar_wait(b_qfull, (uint32_t)(it & 1), abort_flag, flags, 22);
+            {
+                uint32_t qa[16], qb[16];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(q_row + ((c ^ (row & 7)) << 4));
+                    qa[4 * c] = v.x; qa[4 * c + 1] = v.y; qa[4 * c + 2] = v.z; qa[4 * c + 3] = v.w;
+                }
+#pragma unroll
+                for (int c = 4; c < 8; ++c) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(q_row + ((c ^ (row & 7)) << 4));
+                    qb[4 * c - 16] = v.x; qb[4 * c - 15] = v.y; qb[4 * c - 14] = v.z; qb[4 * c - 13] = v.w;
+                }
+                tc_st_32x16(t_lane + T_Q, qa);
+                tc_st_32x16(t_lane + T_Q + 16, qb);
+                if (TAIL) {
+                    uint32_t qc[8];
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(qt_row + ((c ^ ((row >> 2) & 1)) << 4));
+                        qc[4 * c] = v.x; qc[4 * c + 1] = v.y; qc[4 * c + 2] = v.z; qc[4 * c + 3] = v.w;
+                    }
+                    tc_st_32x8(t_lane + T_Q + 32, qc);
+                }
+                tc_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(b_qcopied);
+            }
             float m_run = -INFINITY, l_run = 0.f;  // exponent reference (log2 units) and row sum on that reference
 
             for (int j = 0; j < nt; ++j) {
@@ -330,9 +370,6 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
                 tc_ld_32x32(t_lane + (uint32_t)(sb * 64), s0);
                 tc_ld_32x32(t_lane + (uint32_t)(sb * 64 + 32), s1);
                 tc_wait_ld();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(b_sempty + 8 * sb);
 
                 // tiles wholly inside the valid, visible region (all but the last ones) skip the per-key tests
                 const bool interior = !p.mask && key0 + ABKV <= p.kv_len &&
@@ -367,7 +404,7 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
                     const float corr = (m_new == -INFINITY) ? 1.f : ex2_fast(m_run - m_new);
                     l_run *= corr;
                     m_run = m_new;
-                    mbar_wait(b_pempty + 8 * ((gj - 1) & 1u), ((gj - 1) >> 1) & 1u, abort_flag, flags, 21);
+                    mbar_wait(b_pvdone + 8 * ((gj - 1) & 1u), ((gj - 1) >> 1) & 1u, abort_flag, flags, 21);
                     tc_fence_after();
 #pragma unroll
                     for (int c = 0; c < Cfg::DPAD / 16; ++c) {
@@ -378,13 +415,11 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
                         for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * corr);
                         tc_st_32x16(t_lane + T_O + c * 16, r);
                     }
-                    tc_wait_st();
-                    tc_fence_before();
                 }
                 const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
 
                 float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
-                uint32_t pk[32];
+                uint32_t pa[16], pb[16];   // P as packed f16: column c = keys 2c, 2c + 1
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
                     const float a0 = ex2_fast(fmaf(__uint_as_float(s0[2 * e]), p.scale_log2, neg_m));
@@ -393,29 +428,25 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
                     const float b1 = ex2_fast(fmaf(__uint_as_float(s1[2 * e + 1]), p.scale_log2, neg_m));
                     rs0 += a0; rs1 += a1; rs2 += b0; rs3 += b1;
                     const __half2 ha = __floats2half2_rn(a0, a1), hb = __floats2half2_rn(b0, b1);
-                    pk[e] = *reinterpret_cast<const uint32_t*>(&ha);
-                    pk[16 + e] = *reinterpret_cast<const uint32_t*>(&hb);
+                    pa[e] = *reinterpret_cast<const uint32_t*>(&ha);
+                    pb[e] = *reinterpret_cast<const uint32_t*>(&hb);
                 }
                 l_run += (rs0 + rs1) + (rs2 + rs3);
 
-                // P buffer sb is free once the PV product two tiles back has consumed it
-                mbar_wait(b_pempty + 8 * sb, ((gj >> 1) & 1u) ^ 1u, abort_flag, flags, 20);
-                uint8_t* prow = p_ptr + sb * Cfg::P_BYTES + row * 128;
-#pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) * 16)) =
-                        make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-                fence_async_smem();
+                // P over the first half of the S buffer it came from (this thread has its whole S row in registers)
+                tc_st_32x16(t_lane + (uint32_t)(sb * 64), pa);
+                tc_st_32x16(t_lane + (uint32_t)(sb * 64 + 16), pb);
+                tc_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(b_pfull + 8 * sb);
             }
 
-            // the item's output: out of TMEM into registers first, so that the next item's PV products can start
+            // the item's output: out of tensor memory into registers first, so that the next item's products can start
             uint32_t o[Cfg::DPAD / 16][16];
             if (nt > 0) {
                 const uint32_t gl = g + (uint32_t)nt - 1u;
-                mbar_wait(b_pempty + 8 * (gl & 1u), (gl >> 1) & 1u, abort_flag, flags, 18);
+                mbar_wait(b_pvdone + 8 * (gl & 1u), (gl >> 1) & 1u, abort_flag, flags, 18);
                 tc_fence_after();
 #pragma unroll
                 for (int c = 0; c < Cfg::DPAD / 16; ++c) tc_ld_32x16(t_lane + T_O + c * 16, o[c]);

@@ -115,6 +115,28 @@ __device__ __forceinline__ void tc_mma_f16_parts(uint32_t tmem_d, uint32_t a_lo,
             ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc)
             : "memory");
 }
+// The same product with the A operand in tensor memory (M = 128 rows = lanes, K-major, two 16-bit elements per
+// 32-bit column: a k-step of 16 elements is 8 columns) and B in shared memory.
+template <bool ACC>
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi,
+                                              uint32_t idesc) {
+    if (ACC)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+            "setp.eq.u32 p, 1, 1;\n\t"
+            "mov.b64 db, {%2, %3};\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+            ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+            "setp.ne.u32 p, 1, 1;\n\t"
+            "mov.b64 db, {%2, %3};\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+            ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc)
+            : "memory");
+}
 __device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
