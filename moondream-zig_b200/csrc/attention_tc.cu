@@ -4,25 +4,28 @@
 // attention.multiMaskedSDPA (attention.zig:416-541: decoder prefill, d = 64, causal) for the layouts
 // TMA can address; sdpa_mma_kernel (attention.cu) remains the path for everything else.
 //
-// A work item = 128 queries of one (batch, head).  The grid is at most two CTAs per SM (192 threads each); a CTA
-// takes items blockIdx.x, blockIdx.x + gridDim.x, ... and keeps its barriers, its TMEM and its rings across them,
-// so that from the second item on nothing of a CTA's start-up (launch, barrier set-up, TMEM allocation, descriptor
-// fetch, first loads) is paid again: the producer fetches the next item's Q as soon as the last S product of the
-// current item has read it, and its K / V tiles as ring stages come free, while the softmax warps still write the
-// current item's output.
-//   warp 0      TMA producer: per item Q, then K and V tiles of 64 keys through their own rings of stages.
-//   warp 1      one lane issues tcgen05.mma: S = Q K^T (128 x 64 x d into one of two S buffers in TMEM)
-//               and O += P V (128 x d x 64, accumulated in TMEM over all key tiles);
-//               tcgen05.commit signals completion.
-//   warps 2..5  one thread per query row: tcgen05.ld of its S row, mask / running max / exp2 in f32
-//               registers (no shuffles: a row lives in one thread), P written as f16 into one of two
-//               128B-swizzled shared-memory buffers (the A operand of the PV MMA).
-// O stays in TMEM.  The exponent reference of a row moves only when the row maximum has grown by more
-// than 2^8 since it was last set; only then do the softmax warps rescale that row of O in TMEM (rare
-// after the first tiles), so the usual tile costs one TMEM read of S and no read of O.  P therefore
-// holds values up to 2^8, well inside f16, and the row sum is kept in f32 on the same reference.
-// The issuer runs S(j+1) ahead of PV(j): the tensor pipe works on the next scores while the softmax
-// warps process tile j, and the second CTA of the SM fills the remaining gaps.
+// A work item = 128 queries of one (batch, head).  The grid is at most two CTAs per SM (224 threads each); a CTA
+// takes items blockIdx.x, blockIdx.x + gridDim.x, ... and keeps its barriers, its tensor memory and its rings across
+// them, so that from the second item on nothing of a CTA's start-up (launch, barrier set-up, TMEM allocation,
+// descriptor fetch, first loads) is paid again: the producer fetches the next item's Q as soon as the softmax warps
+// have moved the current one into tensor memory, and its K / V tiles as ring stages come free.
+//   warp 0      TMA producer: per item Q, then K and V tiles of 64 keys through their own rings of three stages.
+//   warp 1      one lane issues S = Q K^T (tcgen05.mma, 128 x 64 x d, into one of two S buffers in tensor memory);
+//   warp 6      one lane issues O += P V (128 x d x 64, accumulated in tensor memory over all key tiles).
+//               Both products read their A operand (Q, P) from tensor memory as packed f16 and only K and V from
+//               shared memory: with A in shared memory every k-step of 16 re-read 4 KB of Q or P for 2 KB of K or
+//               V, and those reads, the P stores and the TMA fills together kept the shared-memory port busy for
+//               the whole tile.  tcgen05.commit signals completion.
+//   warps 2..5  one thread per query row.  Per item: its row of Q from the swizzled shared-memory tile into tensor
+//               memory (tcgen05.st).  Per tile: tcgen05.ld of its S row, mask / running max / exp2 in f32 registers
+//               (no shuffles: a row lives in one thread), P as packed f16 written over the first half of the S
+//               buffer it came from (tcgen05.st).
+// O stays in tensor memory.  The exponent reference of a row moves only when the row maximum has grown by more
+// than 2^8 since it was last set; only then do the softmax warps rescale that row of O (rare after the first
+// tiles), so the usual tile costs one read of S and no read of O.  P therefore holds values up to 2^8, well inside
+// f16, and the row sum is kept in f32 on the same reference.
+// S(j+1) is issued while the softmax warps work on tile j (it needs PV(j-1), whose P it overwrites, to have
+// completed), and the second CTA of the SM fills the remaining gaps.
 //
 // Operands are addressed through 4-D tensor maps (d, row, head, batch) whose extents are exactly the
 // valid data, so everything outside (rows past kv_len, dims past d) is zero-filled by TMA: no stale
@@ -52,6 +55,7 @@ namespace {
 using namespace tc;
 
 constexpr int ABQ = 128, ABKV = 64;
+constexpr int ATTN_THREADS = 224;   // producer, S issuer, 4 softmax warps, PV issuer
 constexpr float LOG2E_F = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units a row maximum may grow before O is rescaled
 
@@ -59,11 +63,10 @@ struct AttnTcParams {
     int q_len, kv_len, causal_pos;
     float scale_log2;
     const uint8_t* mask;  // [q_len, kv_len] or null
-    __half* out;
-    long long o_row, o_head, o_batch;
     // 4-D tensor maps (dim 0 = head dimension d; dims 1..3 = row, head, batch in order of ascending stride):
     // which map dimension carries the row / head / batch index, for q and for k, v
     int q_dim_row, q_dim_head, q_dim_batch, kv_dim_row, kv_dim_head, kv_dim_batch;
+    int o_dim_row, o_dim_head, o_dim_batch;
     int n_qblk, n_heads, n_batch, n_items;   // items = n_qblk * n_heads * n_batch
 };
 
@@ -87,6 +90,7 @@ __device__ __forceinline__ int attn_tiles(const AttnTcParams& p, int q0) {
 struct AttnTcMaps {
     CUtensorMap q, k, v;     // dims 0-63, 128B swizzle
     CUtensorMap qt, kt, vt;  // dims 64-79 (d = 72 only), 32B swizzle
+    CUtensorMap o;           // the output, boxes of 32 rows x d, no swizzle
 };
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
@@ -97,6 +101,11 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map),
+                 "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
 __device__ __forceinline__ void tc_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -129,20 +138,22 @@ __device__ __forceinline__ float ex2_fast(float x) {
 template <int D> struct AttnCfg {
     static constexpr bool TAIL = D > 64;                     // dims 64.. of d = 72
     static constexpr int DPAD = TAIL ? 80 : 64;              // MMA extent of the head dimension
-    static constexpr int STAGES = 3;                         // depth of the K ring and of the V ring
+    static constexpr int STAGES = 3, V_STAGES = 2;           // depth of the K ring and of the V ring
     static constexpr int Q_MAIN = ABQ * 128, Q_TAIL = TAIL ? ABQ * 32 : 0;
     static constexpr int KV_MAIN = ABKV * 128, KV_TAIL = TAIL ? ABKV * 32 : 0;
     static constexpr int Q_BYTES = Q_MAIN + Q_TAIL;
     static constexpr int STAGE_BYTES = KV_MAIN + KV_TAIL;    // one K tile: main | 32B-swizzled tail
     static constexpr int V_STAGE_BYTES = KV_MAIN + (TAIL ? KV_MAIN : 0);   // one V tile: main | second 128B atom
-    static constexpr int SMEM = 1024 + Q_BYTES + STAGES * (STAGE_BYTES + V_STAGE_BYTES) + 256;  // 99.25 / 65.25 KB
+    static constexpr int OUT_ROW = D * 2;                    // one output row, packed
+    static constexpr int OUT_BYTES = ABQ * OUT_ROW;          // staging of an item's output for the TMA stores
+    static constexpr int SMEM = 1024 + Q_BYTES + STAGES * STAGE_BYTES + V_STAGES * V_STAGE_BYTES + OUT_BYTES + 256;  // 101.25 / 73.25 KB
 };
 
 template <int D>
-__global__ void __launch_bounds__(192, 2)
+__global__ void __launch_bounds__(ATTN_THREADS, 2)
 attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflags* flags) {
     using Cfg = AttnCfg<D>;
-    constexpr int ST = Cfg::STAGES;
+    constexpr int ST = Cfg::STAGES, STV = Cfg::V_STAGES;
     constexpr bool TAIL = Cfg::TAIL;
     // Tensor memory, 256 columns: two S buffers of 64 (P, as packed f16, takes the first 32 columns of the buffer its
     // S came from), O (64 or 80), Q as packed f16 (32 or 40)
@@ -156,16 +167,18 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
     // K and V travel through separate rings: a K stage is free again as soon as S(j) has been computed,
     // a V stage only after PV(j), two MMAs later; one shared ring would hold the next K load back
     const uint32_t sm_k = sm_q + Cfg::Q_BYTES, sm_v = sm_k + ST * Cfg::STAGE_BYTES;  // per stage: main | tail
-    const uint32_t bars = sm_v + ST * Cfg::V_STAGE_BYTES;
-    uint8_t* bars_ptr = base_ptr + Cfg::Q_BYTES + ST * (Cfg::STAGE_BYTES + Cfg::V_STAGE_BYTES);
+    const uint32_t sm_out = sm_v + STV * Cfg::V_STAGE_BYTES;
+    uint8_t* out_ptr = base_ptr + Cfg::Q_BYTES + ST * Cfg::STAGE_BYTES + STV * Cfg::V_STAGE_BYTES;
+    const uint32_t bars = sm_out + Cfg::OUT_BYTES;
+    uint8_t* bars_ptr = out_ptr + Cfg::OUT_BYTES;
     const uint32_t b_qfull = bars, b_kfull = bars + 8, b_kempty = b_kfull + 8 * ST, b_vfull = b_kempty + 8 * ST;
-    const uint32_t b_vempty = b_vfull + 8 * ST;
-    const uint32_t b_sfull = b_vempty + 8 * ST;  // S(j) is in tensor memory
+    const uint32_t b_vempty = b_vfull + 8 * STV;
+    const uint32_t b_sfull = b_vempty + 8 * STV;  // S(j) is in tensor memory
     const uint32_t b_pfull = b_sfull + 16;       // the softmax warps have written P(j) over it
     const uint32_t b_pvdone = b_pfull + 16;      // PV(j) has completed: O is current, the S / P buffer is free
     const uint32_t b_qcopied = b_pvdone + 16;    // the softmax warps have moved Q from shared to tensor memory
     const uint32_t b_oempty = b_qcopied + 8;     // ... and have read an item's O out of tensor memory
-    // ends at bars + 8 + 32 * ST + 48 + 16 = bars + 168
+    // ends at bars + 8 + 16 * (ST + STV) + 48 + 16 <= bars + 168
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_ptr + 176);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 180);
 
@@ -177,6 +190,7 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
         tma_prefetch_map(&tm.q);
         tma_prefetch_map(&tm.k);
         tma_prefetch_map(&tm.v);
+        tma_prefetch_map(&tm.o);
         if (TAIL) {
             tma_prefetch_map(&tm.qt);
             tma_prefetch_map(&tm.kt);
@@ -188,6 +202,8 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
         for (int s = 0; s < ST; ++s) {
             mbar_init(b_kfull + 8 * s, 1);
             mbar_init(b_kempty + 8 * s, 1);
+        }
+        for (int s = 0; s < STV; ++s) {
             mbar_init(b_vfull + 8 * s, 1);
             mbar_init(b_vempty + 8 * s, 1);
         }
@@ -217,32 +233,40 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            uint32_t st = 0, par = 1;  // ring slot and the parity that says "slot free"
+            uint32_t kst = 0, kpar = 1, vst = 0, vpar = 1;  // ring slots and the parities that say "slot free"
+            int ck[4] = {0, 0, 0, 0};
+            auto load_k = [&](int j) {
+                ck[p.kv_dim_row] = j * ABKV;
+                mbar_wait(b_kempty + 8 * kst, kpar, abort_flag, flags, 11);
+                const uint32_t kfull = b_kfull + 8 * kst, kdst = sm_k + kst * Cfg::STAGE_BYTES;
+                mbar_expect_tx(kfull, Cfg::STAGE_BYTES);
+                tma_load_4d(kdst, &tm.k, kfull, 0, ck[1], ck[2], ck[3]);
+                if (TAIL) tma_load_4d(kdst + Cfg::KV_MAIN, &tm.kt, kfull, 64, ck[1], ck[2], ck[3]);
+                if (++kst == ST) { kst = 0; kpar ^= 1u; }
+            };
             int it = 0;
             for (int w = blockIdx.x; w < p.n_items; w += gridDim.x, ++it) {
                 int qblk, head, batch;
                 attn_item(p, w, qblk, head, batch);
                 const int q0 = qblk * ABQ, nt = attn_tiles(p, q0);
-                int cq[4] = {0, 0, 0, 0}, ck[4] = {0, 0, 0, 0};
+                int cq[4] = {0, 0, 0, 0};
                 cq[p.q_dim_row] = q0; cq[p.q_dim_head] = head; cq[p.q_dim_batch] = batch;
                 ck[p.kv_dim_head] = head; ck[p.kv_dim_batch] = batch;
                 if (it > 0) mbar_wait(b_qcopied, (uint32_t)((it - 1) & 1), abort_flag, flags, 9);
                 mbar_expect_tx(b_qfull, Cfg::Q_BYTES);
                 tma_load_4d(sm_q, &tm.q, b_qfull, 0, cq[1], cq[2], cq[3]);
                 if (TAIL) tma_load_4d(sm_qt, &tm.qt, b_qfull, 64, cq[1], cq[2], cq[3]);
+                // K runs one tile ahead of V: a K stage comes free with S(j), a V stage only with PV(j)
+                if (nt > 0) load_k(0);
                 for (int j = 0; j < nt; ++j) {
+                    if (j + 1 < nt) load_k(j + 1);
                     ck[p.kv_dim_row] = j * ABKV;
-                    mbar_wait(b_kempty + 8 * st, par, abort_flag, flags, 11);
-                    const uint32_t kfull = b_kfull + 8 * st, kdst = sm_k + st * Cfg::STAGE_BYTES;
-                    mbar_expect_tx(kfull, Cfg::STAGE_BYTES);
-                    tma_load_4d(kdst, &tm.k, kfull, 0, ck[1], ck[2], ck[3]);
-                    if (TAIL) tma_load_4d(kdst + Cfg::KV_MAIN, &tm.kt, kfull, 64, ck[1], ck[2], ck[3]);
-                    mbar_wait(b_vempty + 8 * st, par, abort_flag, flags, 10);
-                    const uint32_t vfull = b_vfull + 8 * st, vdst = sm_v + st * Cfg::V_STAGE_BYTES;
+                    mbar_wait(b_vempty + 8 * vst, vpar, abort_flag, flags, 10);
+                    const uint32_t vfull = b_vfull + 8 * vst, vdst = sm_v + vst * Cfg::V_STAGE_BYTES;
                     mbar_expect_tx(vfull, Cfg::V_STAGE_BYTES);
                     tma_load_4d(vdst, &tm.v, vfull, 0, ck[1], ck[2], ck[3]);
                     if (TAIL) tma_load_4d(vdst + Cfg::KV_MAIN, &tm.vt, vfull, 64, ck[1], ck[2], ck[3]);
-                    if (++st == ST) { st = 0; par ^= 1u; }
+                    if (++vst == STV) { vst = 0; vpar ^= 1u; }
                 }
             }
             if (*abort_flag) {  // let copies in flight land before the CTA's shared memory is released
@@ -251,43 +275,22 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+        // ------------------------------------------------------------------ issuer of the S products
+        // Both products take their A operand (Q, P: K-major, packed f16) from tensor memory, 8 columns per k-step of
+        // 16; only K and V are read from shared memory.  Issuing a tile's nine MMAs and four commits from one thread
+        // took longer than the softmax of the tile, so the two products have a thread each; what orders them across
+        // the two threads are the barriers (S(j) waits for PV(j-2), whose P it overwrites; PV(j) waits for P(j)).
         if (lane == 0) {
-            // both products take their A operand (Q, P: K-major, packed f16) from tensor memory, 8 columns per
-            // k-step of 16; only K and V are read from shared memory
             const uint32_t idesc_s = (1u << 4) | ((uint32_t)(ABKV >> 3) << 17) | ((uint32_t)(ABQ >> 4) << 24);
-            const uint32_t idesc_pv =
-                (1u << 4) | (1u << 16) | ((uint32_t)(Cfg::DPAD >> 3) << 17) | ((uint32_t)(ABQ >> 4) << 24);
             // descriptors as 32-bit halves (tc_common.cuh): constant high words, low words advanced by adds; ring
             // slots and their wait parities are running counters
             const uint32_t hi128 = desc_hi(1024, 2), hi32 = desc_hi(256, 6);
             const uint32_t k_lo0 = desc_lo(sm_k, 16), kt_lo0 = desc_lo(sm_k + Cfg::KV_MAIN, 16);
-            // V: MN-major, 64 dims contiguous per key; the next atom along the dims (d = 72) lies one main tile further
-            const uint32_t v_lo0 = desc_lo(sm_v, ABKV * 128);
-            constexpr uint32_t STAGE16 = Cfg::STAGE_BYTES >> 4, VSTAGE16 = Cfg::V_STAGE_BYTES >> 4;
+            constexpr uint32_t STAGE16 = Cfg::STAGE_BYTES >> 4;
             const uint32_t t_q = tmem_base + T_Q;
             uint32_t st = 0, par = 0;        // ring slot and parity of the next S product
-            uint32_t pv_st = 0, pv_par = 0;  // ring slot and parity of the next PV product
             uint32_t g = 0;                  // key tiles of earlier items
             int it = 0;
-            auto issue_pv = [&](int i) {
-                const uint32_t gi = g + (uint32_t)i, pb = gi & 1u;
-                mbar_wait(b_vfull + 8 * pv_st, pv_par, abort_flag, flags, 13);
-                mbar_wait(b_pfull + 8 * pb, (gi >> 1) & 1u, abort_flag, flags, 12);
-                // the first product of an item overwrites O: the previous item's output must have left tensor memory
-                if (i == 0 && it > 0) mbar_wait(b_oempty, (uint32_t)((it - 1) & 1), abort_flag, flags, 17);
-                tc_fence_after();
-                const uint32_t t_p = tmem_base + pb * 64u, v_lo = v_lo0 + pv_st * VSTAGE16;
-                // 16 keys = 8 columns of P and 2048 B of V per k-step (in every atom)
-                if (i == 0) tc_mma_f16_ts<false>(tmem_base + T_O, t_p, v_lo, hi128, idesc_pv);
-                else tc_mma_f16_ts<true>(tmem_base + T_O, t_p, v_lo, hi128, idesc_pv);
-#pragma unroll
-                for (int ks = 1; ks < ABKV / 16; ++ks)
-                    tc_mma_f16_ts<true>(tmem_base + T_O, t_p + ks * 8, v_lo + ks * 128, hi128, idesc_pv);
-                tc_commit(b_pvdone + 8 * pb);
-                tc_commit(b_vempty + 8 * pv_st);
-                if (++pv_st == ST) { pv_st = 0; pv_par ^= 1u; }
-            };
             for (int w = blockIdx.x; w < p.n_items; w += gridDim.x, ++it) {
                 int qblk, head, batch;
                 attn_item(p, w, qblk, head, batch);
@@ -307,9 +310,44 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
                     tc_commit(b_sfull + 8 * sb);
                     tc_commit(b_kempty + 8 * st);
                     if (++st == ST) { st = 0; par ^= 1u; }
-                    if (j > 0) issue_pv(j - 1);
                 }
-                if (nt > 0) issue_pv(nt - 1);
+                g += (uint32_t)nt;
+            }
+        }
+    } else if (warp == 6) {
+        // ------------------------------------------------------------------ issuer of the PV products
+        if (lane == 0) {
+            const uint32_t idesc_pv =
+                (1u << 4) | (1u << 16) | ((uint32_t)(Cfg::DPAD >> 3) << 17) | ((uint32_t)(ABQ >> 4) << 24);
+            const uint32_t hi128 = desc_hi(1024, 2);
+            // V: MN-major, 64 dims contiguous per key; the next atom along the dims (d = 72) lies one main tile further
+            const uint32_t v_lo0 = desc_lo(sm_v, ABKV * 128);
+            constexpr uint32_t VSTAGE16 = Cfg::V_STAGE_BYTES >> 4;
+            uint32_t st = 0, par = 0;        // ring slot and parity of the next PV product
+            uint32_t g = 0;
+            int it = 0;
+            for (int w = blockIdx.x; w < p.n_items; w += gridDim.x, ++it) {
+                int qblk, head, batch;
+                attn_item(p, w, qblk, head, batch);
+                const int nt = attn_tiles(p, qblk * ABQ);
+                for (int j = 0; j < nt; ++j) {
+                    const uint32_t gj = g + (uint32_t)j, pb = gj & 1u;
+                    mbar_wait(b_vfull + 8 * st, par, abort_flag, flags, 13);
+                    mbar_wait(b_pfull + 8 * pb, (gj >> 1) & 1u, abort_flag, flags, 12);
+                    // the first product of an item overwrites O: the previous item's output must have left tensor memory
+                    if (j == 0 && it > 0) mbar_wait(b_oempty, (uint32_t)((it - 1) & 1), abort_flag, flags, 17);
+                    tc_fence_after();
+                    const uint32_t t_p = tmem_base + pb * 64u, v_lo = v_lo0 + st * VSTAGE16;
+                    // 16 keys = 8 columns of P and 2048 B of V per k-step (in every atom)
+                    if (j == 0) tc_mma_f16_ts<false>(tmem_base + T_O, t_p, v_lo, hi128, idesc_pv);
+                    else tc_mma_f16_ts<true>(tmem_base + T_O, t_p, v_lo, hi128, idesc_pv);
+#pragma unroll
+                    for (int ks = 1; ks < ABKV / 16; ++ks)
+                        tc_mma_f16_ts<true>(tmem_base + T_O, t_p + ks * 8, v_lo + ks * 128, hi128, idesc_pv);
+                    tc_commit(b_pvdone + 8 * pb);
+                    tc_commit(b_vempty + 8 * st);
+                    if (++st == STV) { st = 0; par ^= 1u; }
+                }
                 g += (uint32_t)nt;
             }
         }
@@ -319,46 +357,45 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
         const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
         const uint8_t* q_row = base_ptr + row * 128;
         const uint8_t* qt_row = base_ptr + Cfg::Q_MAIN + row * 32;
+        uint8_t* stage_row = out_ptr + row * Cfg::OUT_ROW;                       // this row in the output staging
+        const uint32_t stage_warp = sm_out + (uint32_t)(quad * 32 * Cfg::OUT_ROW);  // this warp's 32 rows of it
+        // This row of Q of the CTA's item number `item`: out of the swizzled tile (16-byte chunk c of a 128-byte row
+        // sits at c ^ (row & 7); of a 32-byte row at c ^ ((row >> 2) & 1)) into tensor memory, two dims per column.
+        // Called once every S product of the item before has completed (its last PV product was waited for).
+        auto copy_q = [&](int item) {
+            mbar_wait(b_qfull, (uint32_t)(item & 1), abort_flag, flags, 22);
+            uint32_t qa[16];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(q_row + (((4 * h + c) ^ (row & 7)) << 4));
+                    qa[4 * c] = v.x; qa[4 * c + 1] = v.y; qa[4 * c + 2] = v.z; qa[4 * c + 3] = v.w;
+                }
+                tc_st_32x16(t_lane + T_Q + 16 * h, qa);
+            }
+            if (TAIL) {
+                uint32_t qc[8];
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(qt_row + ((c ^ ((row >> 2) & 1)) << 4));
+                    qc[4 * c] = v.x; qc[4 * c + 1] = v.y; qc[4 * c + 2] = v.z; qc[4 * c + 3] = v.w;
+                }
+                tc_st_32x8(t_lane + T_Q + 32, qc);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(b_qcopied);
+        };
         uint32_t g = 0;
         int it = 0;
+        if ((int)blockIdx.x < p.n_items) copy_q(0);
         for (int w = blockIdx.x; w < p.n_items; w += gridDim.x, ++it) {
             int qblk, head, batch;
             attn_item(p, w, qblk, head, batch);
             const int q0 = qblk * ABQ, nt = attn_tiles(p, q0), qi = q0 + row;
             const bool row_ok = qi < p.q_len;
-
-            // this row of Q: out of the swizzled tile (16-byte chunk c of a 128-byte row sits at c ^ (row & 7); of
-            // a 32-byte row at c ^ ((row >> 2) & 1)) into tensor memory, two dims per column.  Every S product of
-            // the previous item has completed (its last PV product was waited for), so the columns are free.
-            mbar_wait(b_qfull, (uint32_t)(it & 1), abort_flag, flags, 22);
-            {
-                uint32_t qa[16], qb[16];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(q_row + ((c ^ (row & 7)) << 4));
-                    qa[4 * c] = v.x; qa[4 * c + 1] = v.y; qa[4 * c + 2] = v.z; qa[4 * c + 3] = v.w;
-                }
-#pragma unroll
-                for (int c = 4; c < 8; ++c) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(q_row + ((c ^ (row & 7)) << 4));
-                    qb[4 * c - 16] = v.x; qb[4 * c - 15] = v.y; qb[4 * c - 14] = v.z; qb[4 * c - 13] = v.w;
-                }
-                tc_st_32x16(t_lane + T_Q, qa);
-                tc_st_32x16(t_lane + T_Q + 16, qb);
-                if (TAIL) {
-                    uint32_t qc[8];
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        const uint4 v = *reinterpret_cast<const uint4*>(qt_row + ((c ^ ((row >> 2) & 1)) << 4));
-                        qc[4 * c] = v.x; qc[4 * c + 1] = v.y; qc[4 * c + 2] = v.z; qc[4 * c + 3] = v.w;
-                    }
-                    tc_st_32x8(t_lane + T_Q + 32, qc);
-                }
-                tc_wait_st();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(b_qcopied);
-            }
             float m_run = -INFINITY, l_run = 0.f;  // exponent reference (log2 units) and row sum on that reference
 
             for (int j = 0; j < nt; ++j) {
@@ -374,7 +411,17 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
                 // tiles wholly inside the valid, visible region (all but the last ones) skip the per-key tests
                 const bool interior = !p.mask && key0 + ABKV <= p.kv_len &&
                                       (p.causal_pos < 0 || key0 + ABKV - 1 <= p.causal_pos + q0 + quad * 32);
-                if (!interior) {
+                if (!interior && !p.mask) {
+                    // the visible keys of a row are a prefix of the tile: the first n_vis of its 64
+                    int n_vis = p.kv_len - key0;
+                    if (p.causal_pos >= 0) n_vis = min(n_vis, p.causal_pos + qi - key0 + 1);
+                    if (!row_ok) n_vis = 0;
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        if (e >= n_vis) s0[e] = 0xff800000u;  // -inf
+                        if (e + 32 >= n_vis) s1[e] = 0xff800000u;
+                    }
+                } else if (!interior) {
 #pragma unroll
                     for (int e = 0; e < 64; ++e) {
                         const int key = key0 + e;
@@ -442,7 +489,9 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
                 if (lane == 0) mbar_arrive(b_pfull + 8 * sb);
             }
 
-            // the item's output: out of tensor memory into registers first, so that the next item's products can start
+            // The item's output: out of tensor memory into registers first.  That frees O, and with it the next
+            // item can start: its Q goes into tensor memory now, so its first S product runs while this item's
+            // output is converted and stored.
             uint32_t o[Cfg::DPAD / 16][16];
             if (nt > 0) {
                 const uint32_t gl = g + (uint32_t)nt - 1u;
@@ -460,28 +509,40 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(b_oempty);
+            if (w + (int)gridDim.x < p.n_items) copy_q(it + 1);
+
+            // One row per thread would be 32 scattered 16-byte pieces per store instruction; instead the warp's 32
+            // rows are packed in shared memory and leave as one TMA store (rows past q_len are clipped by the map).
+            if (lane == 0) tma_store_wait_read<0>();   // the previous item's store has read the staging rows
+            __syncwarp();
             const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-            __half* orow = p.out + batch * p.o_batch + head * p.o_head + (long long)qi * p.o_row;
-            if (row_ok) {
 #pragma unroll
-                for (int c = 0; c < Cfg::DPAD / 16; ++c) {
+            for (int c = 0; c < Cfg::DPAD / 16; ++c) {
 #pragma unroll
-                    for (int h8 = 0; h8 < 2; ++h8) {
-                        if (c * 16 + h8 * 8 < D) {
-                            uint32_t wv[4];
+                for (int h8 = 0; h8 < 2; ++h8) {
+                    if (c * 16 + h8 * 8 < D) {
+                        uint32_t wv[4];
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const __half2 h = __floats2half2_rn(__uint_as_float(o[c][h8 * 8 + 2 * e]) * inv,
-                                                                    __uint_as_float(o[c][h8 * 8 + 2 * e + 1]) * inv);
-                                wv[e] = *reinterpret_cast<const uint32_t*>(&h);
-                            }
-                            *reinterpret_cast<uint4*>(orow + c * 16 + h8 * 8) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                        for (int e = 0; e < 4; ++e) {
+                            const __half2 h = __floats2half2_rn(__uint_as_float(o[c][h8 * 8 + 2 * e]) * inv,
+                                                                __uint_as_float(o[c][h8 * 8 + 2 * e + 1]) * inv);
+                            wv[e] = *reinterpret_cast<const uint32_t*>(&h);
                         }
+                        *reinterpret_cast<uint4*>(stage_row + (c * 16 + h8 * 8) * 2) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
                     }
                 }
             }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0 && q0 + quad * 32 < p.q_len) {
+                int co[4] = {0, 0, 0, 0};
+                co[p.o_dim_row] = q0 + quad * 32; co[p.o_dim_head] = head; co[p.o_dim_batch] = batch;
+                tma_store_4d(&tm.o, stage_warp, 0, co[1], co[2], co[3]);
+                tma_store_commit();
+            }
             g += (uint32_t)nt;
         }
+        if (lane == 0) tma_store_wait_all();
     }
 
     tc_fence_before();
@@ -533,7 +594,7 @@ int launch_attn_tc(md_ctx* ctx, const AttnTcMaps& maps, const AttnTcParams& p, d
         MD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<D>::SMEM));
         ctx->tc_configured |= cfg_bit;
     }
-    return md_launch_ex(ctx, kern, grid, dim3(192), AttnCfg<D>::SMEM, "attn_tc_kernel", maps, p, ctx->flags);
+    return md_launch_ex(ctx, kern, grid, dim3(ATTN_THREADS), AttnCfg<D>::SMEM, "attn_tc_kernel", maps, p, ctx->flags);
 }
 
 }  // namespace
@@ -580,13 +641,20 @@ int md_launch_sdpa_tc(md_ctx* ctx, const __half* q, const __half* k, const __hal
     } else {
         maps.qt = maps.q; maps.kt = maps.k; maps.vt = maps.v;
     }
+    MapPlan mo;
+    const size_t eo[3] = {q_len, n_heads, batch}, so[3] = {o_row, o_head, o_batch};
+    if (!plan_map(mo, d, eo, so))
+        return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 attention: output strides not addressable by a tensor map");
+    uint32_t boxo[3] = {1, 1, 1};
+    boxo[mo.dim_of[0] - 1] = 32;
+    MD_TRY(md_make_map_4d(ctx, &maps.o, out, mo.dims, mo.strides_bytes, (uint32_t)d, boxo, 0));
     AttnTcParams p;
     p.q_len = (int)q_len; p.kv_len = (int)kv_len; p.causal_pos = causal_pos;
     p.scale_log2 = (1.0f / sqrtf((float)d)) * LOG2E_F;
-    p.mask = mask; p.out = out;
-    p.o_row = (long long)o_row; p.o_head = (long long)o_head; p.o_batch = (long long)o_batch;
+    p.mask = mask;
     p.q_dim_row = mq.dim_of[0]; p.q_dim_head = mq.dim_of[1]; p.q_dim_batch = mq.dim_of[2];
     p.kv_dim_row = mk.dim_of[0]; p.kv_dim_head = mk.dim_of[1]; p.kv_dim_batch = mk.dim_of[2];
+    p.o_dim_row = mo.dim_of[0]; p.o_dim_head = mo.dim_of[1]; p.o_dim_batch = mo.dim_of[2];
     p.n_qblk = (int)((q_len + ABQ - 1) / ABQ); p.n_heads = (int)n_heads; p.n_batch = (int)batch;
     const size_t n_items = (size_t)p.n_qblk * n_heads * batch;
     if (n_items > (size_t)INT_MAX) return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 attention: too many query blocks");

@@ -531,7 +531,8 @@ int md_make_map_4d(md_ctx* ctx, CUtensorMap* map, const void* ptr, const uint64_
     const cuuint32_t elem[4] = {1, 1, 1, 1};
     CUresult r = reinterpret_cast<encode_tiled_fn>(ctx->encode_tiled)(
         map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(ptr), gd, gs, box, elem,
-        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+        CU_TENSOR_MAP_INTERLEAVE_NONE,
+        swizzle_bytes == 0 ? CU_TENSOR_MAP_SWIZZLE_NONE : swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_128B,
         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return md_fail(ctx, MD_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled (4-D) failed with CUresult %d", (int)r);
     return MD_OK;
