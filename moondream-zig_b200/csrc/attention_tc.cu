@@ -5,7 +5,7 @@
 // TMA can address; sdpa_mma_kernel (attention.cu) remains the path for everything else.
 //
 // A work item = 128 queries of one (batch, head).  The grid is at most two CTAs per SM (224 threads each); a CTA
-// takes items blockIdx.x, blockIdx.x + gridDim.x, ... and keeps its barriers, its tensor memory and its rings across
+// takes one item per round of gridDim.x items and keeps its barriers, its tensor memory and its rings across
 // them, so that from the second item on nothing of a CTA's start-up (launch, barrier set-up, TMEM allocation,
 // descriptor fetch, first loads) is paid again: the producer fetches the next item's Q as soon as the softmax warps
 // have moved the current one into tensor memory, and its K / V tiles as ring stages come free.
@@ -81,6 +81,13 @@ __device__ __forceinline__ void attn_item(const AttnTcParams& p, int w, int& qbl
     head = r % p.n_heads;
     batch = r / p.n_heads;
 }
+// The item a CTA takes in its round `it` (-1: none, and none later): rounds alternate direction over the CTAs, so the
+// CTA that got the longest causal item of one round gets the shortest of the next.
+__device__ __forceinline__ int attn_walk(const AttnTcParams& p, int it) {
+    const int c = (it & 1) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+    const long long w = (long long)it * gridDim.x + c;
+    return w < p.n_items ? (int)w : -1;
+}
 __device__ __forceinline__ int attn_tiles(const AttnTcParams& p, int q0) {
     int kv_end = p.kv_len;
     if (p.causal_pos >= 0) kv_end = min(kv_end, p.causal_pos + min(q0 + ABQ, p.q_len));
@@ -129,6 +136,11 @@ __device__ __forceinline__ void tc_st_32x8(uint32_t taddr, const uint32_t (&r)[8
                  : "memory");
 }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ float ex2_fast(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -245,7 +257,7 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
                 if (++kst == ST) { kst = 0; kpar ^= 1u; }
             };
             int it = 0;
-            for (int w = blockIdx.x; w < p.n_items; w += gridDim.x, ++it) {
+            for (int w; (w = attn_walk(p, it)) >= 0; ++it) {
                 int qblk, head, batch;
                 attn_item(p, w, qblk, head, batch);
                 const int q0 = qblk * ABQ, nt = attn_tiles(p, q0);
@@ -291,7 +303,7 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
             uint32_t st = 0, par = 0;        // ring slot and parity of the next S product
             uint32_t g = 0;                  // key tiles of earlier items
             int it = 0;
-            for (int w = blockIdx.x; w < p.n_items; w += gridDim.x, ++it) {
+            for (int w; (w = attn_walk(p, it)) >= 0; ++it) {
                 int qblk, head, batch;
                 attn_item(p, w, qblk, head, batch);
                 const int nt = attn_tiles(p, qblk * ABQ);
@@ -326,7 +338,7 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
             uint32_t st = 0, par = 0;        // ring slot and parity of the next PV product
             uint32_t g = 0;
             int it = 0;
-            for (int w = blockIdx.x; w < p.n_items; w += gridDim.x, ++it) {
+            for (int w; (w = attn_walk(p, it)) >= 0; ++it) {
                 int qblk, head, batch;
                 attn_item(p, w, qblk, head, batch);
                 const int nt = attn_tiles(p, qblk * ABQ);
@@ -390,8 +402,8 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
         };
         uint32_t g = 0;
         int it = 0;
-        if ((int)blockIdx.x < p.n_items) copy_q(0);
-        for (int w = blockIdx.x; w < p.n_items; w += gridDim.x, ++it) {
+        if (attn_walk(p, 0) >= 0) copy_q(0);
+        for (int w; (w = attn_walk(p, it)) >= 0; ++it) {
             int qblk, head, batch;
             attn_item(p, w, qblk, head, batch);
             const int q0 = qblk * ABQ, nt = attn_tiles(p, q0), qi = q0 + row;
@@ -433,15 +445,23 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
                         }
                     }
                 }
-                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+                // three-input max (two new values per instruction), eight independent chains of four
+                float mx[8];
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    mx0 = fmaxf(mx0, __uint_as_float(s0[e]));
-                    mx1 = fmaxf(mx1, __uint_as_float(s0[e + 1]));
-                    mx2 = fmaxf(mx2, __uint_as_float(s1[e]));
-                    mx3 = fmaxf(mx3, __uint_as_float(s1[e + 1]));
+                for (int c = 0; c < 4; ++c) {
+                    mx[c] = fmaxf(__uint_as_float(s0[8 * c]), __uint_as_float(s0[8 * c + 1]));
+                    mx[4 + c] = fmaxf(__uint_as_float(s1[8 * c]), __uint_as_float(s1[8 * c + 1]));
                 }
-                const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;  // -inf stays -inf (scale > 0)
+#pragma unroll
+                for (int e = 2; e < 8; e += 2) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        mx[c] = max3(mx[c], __uint_as_float(s0[8 * c + e]), __uint_as_float(s0[8 * c + e + 1]));
+                        mx[4 + c] = max3(mx[4 + c], __uint_as_float(s1[8 * c + e]), __uint_as_float(s1[8 * c + e + 1]));
+                    }
+                }
+                const float mt = fmaxf(max3(mx[0], mx[1], mx[2]), max3(max3(mx[3], mx[4], mx[5]), mx[6], mx[7])) *
+                                 p.scale_log2;  // -inf stays -inf (scale > 0)
 
                 if (j == 0) {
                     m_run = mt;
@@ -465,7 +485,9 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
                 }
                 const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
 
-                float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+                float rs[8];   // eight independent partial sums
+#pragma unroll
+                for (int c = 0; c < 8; ++c) rs[c] = 0.f;
                 uint32_t pa[16], pb[16];   // P as packed f16: column c = keys 2c, 2c + 1
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
@@ -473,12 +495,12 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
                     const float a1 = ex2_fast(fmaf(__uint_as_float(s0[2 * e + 1]), p.scale_log2, neg_m));
                     const float b0 = ex2_fast(fmaf(__uint_as_float(s1[2 * e]), p.scale_log2, neg_m));
                     const float b1 = ex2_fast(fmaf(__uint_as_float(s1[2 * e + 1]), p.scale_log2, neg_m));
-                    rs0 += a0; rs1 += a1; rs2 += b0; rs3 += b1;
+                    rs[(e & 1) * 4] += a0; rs[(e & 1) * 4 + 1] += a1; rs[(e & 1) * 4 + 2] += b0; rs[(e & 1) * 4 + 3] += b1;
                     const __half2 ha = __floats2half2_rn(a0, a1), hb = __floats2half2_rn(b0, b1);
                     pa[e] = *reinterpret_cast<const uint32_t*>(&ha);
                     pb[e] = *reinterpret_cast<const uint32_t*>(&hb);
                 }
-                l_run += (rs0 + rs1) + (rs2 + rs3);
+                l_run += ((rs[0] + rs[1]) + (rs[2] + rs[3])) + ((rs[4] + rs[5]) + (rs[6] + rs[7]));
 
                 // P over the first half of the S buffer it came from (this thread has its whole S row in registers)
                 tc_st_32x16(t_lane + (uint32_t)(sb * 64), pa);
@@ -509,7 +531,7 @@ attn_tc_kernel(const __grid_constant__ AttnTcMaps tm, AttnTcParams p, md_devflag
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(b_oempty);
-            if (w + (int)gridDim.x < p.n_items) copy_q(it + 1);
+            if (attn_walk(p, it + 1) >= 0) copy_q(it + 1);
 
             // One row per thread would be 32 scattered 16-byte pieces per store instruction; instead the warp's 32
             // rows are packed in shared memory and leave as one TMA store (rows past q_len are clipped by the map).
