@@ -67,12 +67,17 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     tn = r / rows;
 }
 
-// Bounded wait of the push warps for the epilogue's count of finished tiles (a shared-memory word).
+// Bounded wait of the push warps until EVERY epilogue warp has finished `target` tiles (one shared-memory word per
+// epilogue warp).  A single count over all warps is not enough: the accumulators are double-buffered, so some warps
+// may be a tile ahead of the others, and their extra counts would stand in for warps that have not stored yet.
 static __device__ __noinline__ bool wait_stored(volatile unsigned* stored, unsigned target, volatile int* abort_flag,
                                                 md_devflags* flags, unsigned site) {
     const unsigned long long t0 = global_ns();
     for (unsigned spin = 0;; ++spin) {
-        if (*stored >= target) {
+        unsigned least = stored[0];
+#pragma unroll
+        for (int e = 1; e < EPI_WARPS; ++e) least = min(least, stored[e]);
+        if (least >= target) {
             __threadfence_block();
             return true;
         }
@@ -120,7 +125,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const uint32_t bar_tfull = bars + 16 * STAGES, bar_tempty = bar_tfull + 16;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_ptr + 16 * STAGES + 32);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 16 * STAGES + 36);
-    // epilogue warps that have finished a tile (all of its TMA stores complete), counted over the CTA's tiles
+    // per epilogue warp: the number of this CTA's tiles it has finished (all of its TMA stores complete)
     volatile unsigned* stored = reinterpret_cast<volatile unsigned*>(bars_ptr + 16 * STAGES + 40);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -144,7 +149,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             mbar_init(bar_tempty + 8 * b, EPI_WARPS);
         }
         *abort_flag = 0;
-        *stored = 0u;
+        for (int e = 0; e < EPI_WARPS; ++e) stored[e] = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -305,11 +310,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             }
             if (PUSH && lane == 0) {
                 // Column-split GEMM: this warp's part of the tile is in this GPU's C once its TMA stores have
-                // completed; tell the push warps (every epilogue warp counts once per tile).  The wait costs
+                // completed; tell the push warps (every epilogue warp counts its own tiles).  The wait costs
                 // nothing: the warp would next wait for the following tile's accumulator anyway.
                 tma_store_wait_all();
                 __threadfence_block();
-                atomicAdd(const_cast<unsigned*>(stored), 1u);
+                stored[warp - 2] = (unsigned)(local + 1);
             }
         }
         if (lane == 0) tma_store_wait_all();
@@ -331,7 +336,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             int tm, tn;
             tile_coords(tile, tiles_m, tiles_n, tm, tn);
             const int m0 = tm * TILE_M, n0 = tn * BLOCK_N;
-            if (!wait_stored(stored, (unsigned)(EPI_WARPS * (local + 1)), abort_flag, flags, 5)) break;
+            if (!wait_stored(stored, (unsigned)(local + 1), abort_flag, flags, 5)) break;
             const int gc = n0 + cl;
             if (gc >= N) continue;  // columns past this rank's block belong to a neighbour
             const long long tile_off = (long long)m0 * push.ld + gc;
