@@ -192,6 +192,66 @@ argmax_kernel(const __half* __restrict__ x, size_t n, unsigned long long* __rest
     }
 }
 
+// The same for `gridDim.x` rows at once (row r at x + r * stride, n % 8 == 0, 16-byte aligned rows), one CTA per
+// row: 16-byte loads, all of a thread's loads requested before the first compare.  A thread walks its elements in
+// ascending order and a later element replaces the best only when strictly greater, as above.
+constexpr int ARGMAX_VEC_MAX = 8;   // vectors per thread: rows of up to 1024 x 8 x 8 = 65536 elements
+__global__ void __launch_bounds__(1024)
+argmax_rows_kernel(const __half* __restrict__ x, size_t n, size_t stride, unsigned long long* __restrict__ out) {
+    __shared__ float sv[32];
+    __shared__ unsigned long long si[32];
+    md_pdl_launch_dependents();
+    md_pdl_wait();
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)blockIdx.x * stride);
+    const size_t nvec = n >> 3;
+    uint4 v[ARGMAX_VEC_MAX];
+#pragma unroll
+    for (int k = 0; k < ARGMAX_VEC_MAX; ++k) {
+        const size_t c = threadIdx.x + (size_t)k * blockDim.x;
+        if (c < nvec) v[k] = __ldcg(xr + c);
+    }
+    float best = -INFINITY;
+    unsigned long long bi = ~0ull;
+#pragma unroll
+    for (int k = 0; k < ARGMAX_VEC_MAX; ++k) {
+        const size_t c = threadIdx.x + (size_t)k * blockDim.x;
+        if (c < nvec) {
+            const __half* h = reinterpret_cast<const __half*>(&v[k]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float f = __half2float(h[e]);
+                if (bi == ~0ull || f > best) { best = f; bi = c * 8 + e; }
+            }
+        }
+    }
+    auto better = [](float a, unsigned long long i, float bv, unsigned long long bidx) {
+        if (i == ~0ull) return false;
+        if (bidx == ~0ull) return true;
+        return a > bv || (a == bv && i < bidx);
+    };
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const unsigned long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, best, bi)) { best = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = blockDim.x >> 5;
+        best = lane < nw ? sv[lane] : -INFINITY;
+        bi = lane < nw ? si[lane] : ~0ull;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const unsigned long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ov, oi, best, bi)) { best = ov; bi = oi; }
+        }
+        if (lane == 0) out[blockIdx.x] = (bi == ~0ull) ? 0ull : bi;
+    }
+}
+
 // vision_model.zig:137-183 + reshape_handler.zig:5-129.  One thread per output element.
 __global__ void patchify_kernel(const uint8_t* __restrict__ img, __half* __restrict__ out, int crops, int height,
                                 int width, int patch, int out_stride) {
@@ -328,8 +388,22 @@ int md_launch_add(md_ctx* ctx, __half* a, const __half* b, size_t n) {
 }
 
 int md_launch_argmax(md_ctx* ctx, const __half* x, size_t n, unsigned long long* idx_dev) {
-    argmax_kernel<<<1, 1024, 0, ctx->stream>>>(x, n, idx_dev);
-    MD_LAUNCH_CHECK(ctx, "argmax_kernel");
+    return md_launch_argmax_rows(ctx, x, n, n, 1, idx_dev);
+}
+
+// The greedy sample of `rows` rows (row r at x + r * stride) into idx_dev[0 .. rows): one launch.
+int md_launch_argmax_rows(md_ctx* ctx, const __half* x, size_t n, size_t stride, size_t rows,
+                          unsigned long long* idx_dev) {
+    if (!rows) return MD_OK;
+    const bool vec = n > 0 && (n % 8) == 0 && (stride % 8) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                     n <= (size_t)1024 * 8 * ARGMAX_VEC_MAX && rows <= 65535;
+    if (vec)
+        return md_launch_ex(ctx, argmax_rows_kernel, dim3((unsigned)rows), dim3(1024), 0, "argmax_rows_kernel", x, n,
+                            stride, idx_dev);
+    for (size_t r = 0; r < rows; ++r) {
+        argmax_kernel<<<1, 1024, 0, ctx->stream>>>(x + r * stride, n, idx_dev + r);
+        MD_LAUNCH_CHECK(ctx, "argmax_kernel");
+    }
     return MD_OK;
 }
 

@@ -261,6 +261,7 @@ int md_launch_gelu(md_ctx* ctx, __half* x, size_t n);
 int md_launch_bias_add(md_ctx* ctx, __half* a, const __half* b, size_t rows, size_t cols);
 int md_launch_add(md_ctx* ctx, __half* a, const __half* b, size_t n);
 int md_launch_argmax(md_ctx* ctx, const __half* x, size_t n, unsigned long long* idx_dev);
+int md_launch_argmax_rows(md_ctx* ctx, const __half* x, size_t n, size_t stride, size_t rows, unsigned long long* idx_dev);
 int md_launch_patchify(md_ctx* ctx, const uint8_t* img, __half* out, size_t crops, size_t h, size_t w, size_t patch,
                        size_t out_stride);
 int md_launch_rope_table(md_ctx* ctx, float* table, size_t dim, size_t end, float theta);

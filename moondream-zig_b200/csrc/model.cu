@@ -389,7 +389,7 @@ int text_lm_head(md_text_model* m, const __half* hidden_rows, size_t rows, __hal
     md_epilogue e;
     e.bias = H(w.lm_b);
     MD_TRY(md_gemm_dispatch(ctx, ln_buf, H(w.lm_w), logits, rows, w.vocab, w.dim, 1, e));
-    for (size_t b = 0; b < rows; ++b) MD_TRY(md_launch_argmax(ctx, logits + b * w.vocab, w.vocab, sampled + b));
+    MD_TRY(md_launch_argmax_rows(ctx, logits, w.vocab, w.vocab, rows, sampled));
     return MD_OK;
 }
 

@@ -54,6 +54,26 @@ def test_argmax_first_maximum(ctx, oracle):
     assert ctx.argmax(np.array([-3.0], np.float16), 1) == 0
 
 
+@pytest.mark.parametrize("n", [8, 2048, 51200, 65536, 7, 51201, 65544])
+def test_argmax_vector_and_scalar_forms(ctx, oracle, n):
+    """Rows of a multiple of 8 elements (up to 65536) take 16-byte loads, everything else the scalar kernel: same
+    answer as the oracle for random rows, for ties inside one 16-byte vector, across threads and across a thread's
+    vectors (the first index wins), for a constant row, a row of -inf and the maximum in the last element."""
+    rng = np.random.default_rng(n)
+    x = f16_normal(rng, (n,))
+    assert ctx.argmax(x, n) == oracle.argmax(x)
+    for idx in ([n - 1], [0, n - 1], [n // 2, n // 2 + 1], [3, 5], [n - 3, n // 3]):
+        y = x.copy()
+        y[idx] = np.float16(11.0)
+        assert ctx.argmax(y, n) == min(idx) == oracle.argmax(y)
+    if n > 9000:
+        y = x.copy()
+        y[[1024 * 8 + 17, 17]] = np.float16(11.0)   # the same thread's second and first vector
+        assert ctx.argmax(y, n) == 17
+    assert ctx.argmax(np.full(n, 2.5, np.float16), n) == 0
+    assert ctx.argmax(np.full(n, -np.inf, np.float16), n) == 0
+
+
 @pytest.mark.parametrize("crops", [1, 2])
 def test_preprocess_patchify(ctx, oracle, crops):
     rng = np.random.default_rng(4)
