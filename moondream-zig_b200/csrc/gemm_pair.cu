@@ -30,6 +30,8 @@ constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int STAGES = 6;
 constexpr int EPI_WARPS = 8, EPI_BUF_BYTES = 32 * 128, EPI_BYTES = EPI_WARPS * EPI_BUF_BYTES;
 constexpr int NUM_THREADS = (2 + EPI_WARPS) * 32;
+constexpr int PUSH_WARPS = 8;                            // extra warps of the column-split form
+constexpr int NUM_THREADS_PUSH = NUM_THREADS + PUSH_WARPS * 32;
 constexpr int BAR_BYTES = 1024;
 constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;   // 231,424 of the 232,448 available
 constexpr uint32_t TMEM_COLS = 512;
@@ -85,11 +87,14 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
     tn = r / rows;
 }
 
-template <bool B_MN_MAJOR>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// PUSH = the column-split form: eight more warps per CTA copy every finished tile (this CTA's 128 rows of it) from
+// this GPU's C into the peers' C, as in the single-CTA kernel (its own instantiation, so that the plain kernel keeps
+// the register budget of 320 threads).
+template <bool B_MN_MAJOR, bool PUSH>
+__global__ void __launch_bounds__(PUSH ? NUM_THREADS_PUSH : NUM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_c, int M, int N, int K, int tiles_m, int num_tiles,
-                 md_epilogue ep, md_devflags* flags) {
+                 md_epilogue ep, md_push push, md_devflags* flags) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -104,6 +109,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const uint32_t bar_tfull = bars + 16 * STAGES, bar_tempty = bar_tfull + 16;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_ptr + 16 * STAGES + 32);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 16 * STAGES + 36);
+    // per epilogue warp: the number of this CTA's tiles it has finished (all of its TMA stores complete)
+    volatile unsigned* stored = reinterpret_cast<volatile unsigned*>(bars_ptr + 16 * STAGES + 40);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();   // 0 = leader (issues the MMAs), 1 = second CTA of the pair
@@ -125,6 +132,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             mbar_init(bar_tempty + 8 * b, 2 * EPI_WARPS);   // both CTAs' epilogue warps (used in the leader only)
         }
         *abort_flag = 0;
+        for (int e = 0; e < EPI_WARPS; ++e) stored[e] = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -215,7 +223,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 tc_commit_pair(peer_tfull + 8 * buf);
             }
         }
-    } else {
+    } else if (warp < 2 + EPI_WARPS) {
         // ------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
         const int quad = warp & 3;
         const int half = (warp - 2) >> 2;
@@ -268,8 +276,53 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     tma_store_commit();
                 }
             }
+            if (PUSH && lane == 0) {
+                // this warp's part of the tile is in this GPU's C once its TMA stores have completed: tell the
+                // push warps (every epilogue warp counts its own tiles)
+                tma_store_wait_all();
+                __threadfence_block();
+                stored[warp - 2] = (unsigned)(local + 1);
+            }
         }
         if (lane == 0) tma_store_wait_all();
+    } else if (PUSH) {
+        // ------------------------------------------------------------ push (warps 10..17, column-split GEMM)
+        // This CTA's 128 x 256 part of every tile of the pair, read back from this GPU's C and stored into every
+        // peer's C: a warp instruction covers one whole tile row (512 contiguous bytes), eight row groups are
+        // requested before their peer stores are issued.
+        constexpr int UNR = 8, ROW_STEP = PUSH_WARPS;
+        const int pw = warp - (2 + EPI_WARPS);
+        const int cl = lane * 8, ld = (int)push.ld;
+        int local = 0;
+        for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
+            int tm, tn;
+            pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const int m0 = tm * (2 * BLOCK_M) + (int)rank * BLOCK_M, n0 = tn * BLOCK_N;
+            if (!wait_stored(stored, EPI_WARPS, (unsigned)(local + 1), abort_flag, flags, 25)) break;
+            const int gc = n0 + cl;
+            if (gc >= N) continue;  // columns past this rank's block belong to a neighbour
+            const long long tile_off = (long long)m0 * push.ld + gc;
+            for (int r = pw; r < BLOCK_M; r += ROW_STEP * UNR) {
+                uint4 val[UNR];
+#pragma unroll
+                for (int u = 0; u < UNR; ++u) {
+                    const int rr = r + u * ROW_STEP;
+                    if (rr < BLOCK_M && m0 + rr < M) val[u] = __ldcg(reinterpret_cast<const uint4*>(push.self + tile_off + rr * ld));
+                }
+                for (int pi = 0; pi < push.n; ++pi) {
+                    // start with a different peer in every CTA so that the stores spread over the links
+                    int peer = pi + (int)blockIdx.x;
+                    peer -= (peer / push.n) * push.n;
+                    __half* dst = push.base[peer] + tile_off;
+#pragma unroll
+                    for (int u = 0; u < UNR; ++u) {
+                        const int rr = r + u * ROW_STEP;
+                        if (rr < BLOCK_M && m0 + rr < M) *reinterpret_cast<uint4*>(dst + rr * ld) = val[u];
+                    }
+                }
+            }
+        }
+        __threadfence_system();  // peer stores performed before the kernel ends
     }
 
     // nobody frees tensor memory or leaves while the pair's MMAs may still read its shared memory
@@ -288,28 +341,31 @@ int md_make_map_2d(md_ctx* ctx, CUtensorMap* map, const void* ptr, uint64_t inne
                    uint32_t box_outer, uint64_t ld);
 
 // C[M,N] = A . B (+ fused glue) on CTA pairs.  Same operand rules as the single-CTA kernel (K % 8 == 0, N % 8 == 0,
-// 16-byte aligned pointers); the caller decides when the shape is large enough to pay for the pairing.
+// 16-byte aligned pointers, C with row stride ldc); the caller decides when the shape is large enough to pay for the
+// pairing.  push.n > 0: the column-split form (every tile also stored into the peers' C).
 int md_launch_gemm_pair(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K, int b_layout,
-                        const md_epilogue& ep) {
-    const bool mn = (b_layout == 0);
+                        const md_epilogue& ep, size_t ldc, const md_push& push) {
+    const bool mn = (b_layout == 0), with_push = push.n > 0;
     CUtensorMap tm_a, tm_b, tm_c;
     MD_TRY(md_make_map_2d(ctx, &tm_a, a, K, M, BLOCK_K, BLOCK_M, 0));
     if (mn) MD_TRY(md_make_map_2d(ctx, &tm_b, b, N, K, 64, BLOCK_K, 0));
     else MD_TRY(md_make_map_2d(ctx, &tm_b, b, K, N, BLOCK_K, HALF_N, 0));
-    MD_TRY(md_make_map_2d(ctx, &tm_c, c, N, M, 64, 32, 0));
+    MD_TRY(md_make_map_2d(ctx, &tm_c, c, N, M, 64, 32, ldc));
     const int tiles_m = (int)((M + 2 * BLOCK_M - 1) / (2 * BLOCK_M)), tiles_n = (int)((N + BLOCK_N - 1) / BLOCK_N);
     const int num_tiles = tiles_m * tiles_n;
     const int max_pairs = ctx->sm_count / 2;
     const int pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
-    const uint32_t cfg_bit = 1u << (mn ? 30 : 29);
-    if (!(ctx->tc_configured & cfg_bit)) {
-        if (mn) MD_CUDA(ctx, cudaFuncSetAttribute(gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        else MD_CUDA(ctx, cudaFuncSetAttribute(gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        ctx->tc_configured |= cfg_bit;
+    void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, int, int, int, int, int, md_epilogue, md_push, md_devflags*) =
+        with_push ? (mn ? gemm_pair_kernel<true, true> : gemm_pair_kernel<false, true>)
+                  : (mn ? gemm_pair_kernel<true, false> : gemm_pair_kernel<false, false>);
+    const uint32_t cfg_bit = 1u << ((mn ? 1 : 0) + (with_push ? 2 : 0));
+    if (!(ctx->pair_configured & cfg_bit)) {
+        MD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        ctx->pair_configured |= cfg_bit;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * pairs));
-    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.blockDim = dim3(with_push ? NUM_THREADS_PUSH : NUM_THREADS);
     cfg.dynamicSmemBytes = SMEM_BYTES;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[2];
@@ -323,8 +379,7 @@ int md_launch_gemm_pair(md_ctx* ctx, const __half* a, const __half* b, __half* c
     cfg.numAttrs = ctx->pdl ? 2 : 1;
     ctx->last_tc_tile = 2256;   // md_get_option("last_tc_tile"): 2256 = a 256 x 256 tile on a CTA pair
     const int Mi = (int)M, Ni = (int)N, Ki = (int)K;
-    const cudaError_t e = mn ? cudaLaunchKernelEx(&cfg, gemm_pair_kernel<true>, tm_a, tm_b, tm_c, Mi, Ni, Ki, tiles_m, num_tiles, ep, ctx->flags)
-                             : cudaLaunchKernelEx(&cfg, gemm_pair_kernel<false>, tm_a, tm_b, tm_c, Mi, Ni, Ki, tiles_m, num_tiles, ep, ctx->flags);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, tm_c, Mi, Ni, Ki, tiles_m, num_tiles, ep, push, ctx->flags);
     if (e != cudaSuccess) return md_fail(ctx, MD_ERR_CUDA, "launch of gemm_pair_kernel failed: %s", cudaGetErrorString(e));
     ctx->launches++;
     return MD_OK;

@@ -67,30 +67,6 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     tn = r / rows;
 }
 
-// Bounded wait of the push warps until EVERY epilogue warp has finished `target` tiles (one shared-memory word per
-// epilogue warp).  A single count over all warps is not enough: the accumulators are double-buffered, so some warps
-// may be a tile ahead of the others, and their extra counts would stand in for warps that have not stored yet.
-static __device__ __noinline__ bool wait_stored(volatile unsigned* stored, unsigned target, volatile int* abort_flag,
-                                                md_devflags* flags, unsigned site) {
-    const unsigned long long t0 = global_ns();
-    for (unsigned spin = 0;; ++spin) {
-        unsigned least = stored[0];
-#pragma unroll
-        for (int e = 1; e < EPI_WARPS; ++e) least = min(least, stored[e]);
-        if (least >= target) {
-            __threadfence_block();
-            return true;
-        }
-        if (*abort_flag) return false;
-        if ((spin & 63u) == 63u && global_ns() - t0 > WAIT_BUDGET_NS) {
-            *abort_flag = 1;
-            md_flag_timeout(flags, site);
-            return false;
-        }
-        __nanosleep(64);
-    }
-}
-
 // PUSH = the column-split form with its eight extra warps (its own instantiation, so that the plain kernel keeps the
 // register budget of 320 threads)
 template <int BLOCK_N, bool B_MN_MAJOR, int MT, bool PUSH>
@@ -336,7 +312,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             int tm, tn;
             tile_coords(tile, tiles_m, tiles_n, tm, tn);
             const int m0 = tm * TILE_M, n0 = tn * BLOCK_N;
-            if (!wait_stored(stored, (unsigned)(local + 1), abort_flag, flags, 5)) break;
+            if (!wait_stored(stored, EPI_WARPS, (unsigned)(local + 1), abort_flag, flags, 5)) break;
             const int gc = n0 + cl;
             if (gc >= N) continue;  // columns past this rank's block belong to a neighbour
             const long long tile_off = (long long)m0 * push.ld + gc;
@@ -499,9 +475,9 @@ int md_launch_gemm_tc_ex(md_ctx* ctx, const __half* a, const __half* b, __half* 
     // a pair, the pair's 256 x 256 tile does the same work per SM with a third less traffic from L2 and measured
     // 1 to 12 % faster (761 x 8192 x 2048: 34.8 -> 31.2 us; 9477 x 1152 x 4304: 91.1 -> 84.7 us); with the other
     // choices it lost.  md_set_option("tc_pair"): 1 = always, 0 = never.
-    if (push.n == 0 && ldc == N && !ctx->tc_block_n &&
+    if (!ctx->tc_block_n &&
         (ctx->tc_pair == 1 || (ctx->tc_pair < 0 && bn == 256 && mt == 1 && M > 256)))
-        return md_launch_gemm_pair(ctx, a, b, c, M, N, K, b_layout, ep);
+        return md_launch_gemm_pair(ctx, a, b, c, M, N, K, b_layout, ep, ldc, push);
     if (ctx->tc_block_n) {  // forced: 512 = the 256 x 256 tile
         bn = ctx->tc_block_n == 512 ? 256 : ctx->tc_block_n;
         mt = ctx->tc_block_n == 512 ? 2 : 1;

@@ -63,6 +63,7 @@ struct md_ctx {
     unsigned int* counters = nullptr;
     // cuTensorMapEncodeTiled resolved through the runtime (no link against libcuda)
     void* encode_tiled = nullptr;
+    uint32_t pair_configured = 0;  // the same for the instantiations of gemm_pair_kernel
     uint32_t tc_configured = 0;  // tcgen05 kernels whose dynamic shared memory limit has been raised
     int skinny = 1;          // md_set_option("skinny"): 8 < M <= 64 takes the swapped-operand split-K kernel
     int skinny_splits = 0;   // md_set_option("skinny_splits"): 0 = automatic, else the number of K splits (tests)
@@ -228,7 +229,7 @@ int md_launch_gemm_skinny(md_ctx* ctx, const __half* a, const __half* b, __half*
 
 // gemm_pair.cu: 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2); same operand rules as md_launch_gemm_tc
 int md_launch_gemm_pair(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K, int b_layout,
-                        const md_epilogue& ep);
+                        const md_epilogue& ep, size_t ldc, const md_push& push);
 
 // gemm_tc.cu: a kernel whose bounded wait runs out on purpose (md_selftest_bounded_wait)
 int md_launch_selftest_wait(md_ctx* ctx, unsigned limit_ms);

@@ -57,6 +57,29 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return mbar_wait_slow(bar, parity, abort_flag, flags, site);
 }
 
+// Bounded wait of the push warps until EVERY epilogue warp has finished `target` tiles (one shared-memory word per
+// epilogue warp).  A single count over all warps is not enough: the accumulators are double-buffered, so some warps
+// may be a tile ahead of the others, and their extra counts would stand in for warps that have not stored yet.
+static __device__ __noinline__ bool wait_stored(volatile unsigned* stored, int n_warps, unsigned target,
+                                                volatile int* abort_flag, md_devflags* flags, unsigned site) {
+    const unsigned long long t0 = global_ns();
+    for (unsigned spin = 0;; ++spin) {
+        unsigned least = stored[0];
+        for (int e = 1; e < n_warps; ++e) least = min(least, stored[e]);
+        if (least >= target) {
+            __threadfence_block();
+            return true;
+        }
+        if (*abort_flag) return false;
+        if ((spin & 63u) == 63u && global_ns() - t0 > WAIT_BUDGET_NS) {
+            *abort_flag = 1;
+            md_flag_timeout(flags, site);
+            return false;
+        }
+        __nanosleep(64);
+    }
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

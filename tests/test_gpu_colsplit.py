@@ -37,15 +37,17 @@ def _push(ctx, a, b_slice, c_full, M, w, K, layout, N, off, peers):
                                               arr))
 
 
-# tile: forced tile of the tcgen05 GEMM (0 = the cost model's choice, 512 = 256 x 256)
-@pytest.mark.parametrize("tile", [0, 64, 128, 256, 512])
+# tile: forced tile of the tcgen05 GEMM (0 = the cost model's choice, 512 = 256 x 256, "pair" = 256 x 256 on a CTA pair)
+@pytest.mark.parametrize("tile", [0, 64, 128, 256, 512, "pair"])
 @pytest.mark.parametrize("shape", [(4096, 256, 4096, 1), (1000, 520, 2000, 0), (300, 256, 512, 1)])
 def test_colsplit_push_fills_the_peers_copies(ctx, oracle, tile, shape):
     """The push epilogue with peers, on one GPU: the two "ranks" are two calls and every rank's peer buffer is the
     other rank's C in the same device memory, so the dedicated push warps, the tile read-back and the column
     clipping at the block edge run exactly as they do across GPUs.  Several tiles per CTA in the first shape."""
     M, K, N, layout = shape
-    rng = np.random.default_rng(M + tile)
+    pair = tile == "pair"
+    tile = 0 if pair else tile
+    rng = np.random.default_rng(M + tile + pair)
     world, w = 2, N // 2
     a = f16_normal(rng, (M, K))
     b = f16_normal(rng, (K, N) if layout == 0 else (N, K), 0.05)
@@ -53,13 +55,17 @@ def test_colsplit_push_fills_the_peers_copies(ctx, oracle, tile, shape):
     da = ctx.upload(a)
     cs = [ctx.upload(np.full((M, N), 7.0, np.float16)) for _ in range(world)]
     ctx.set_option("tc_block_n", tile)
+    ctx.set_option("tc_pair", 1 if pair else 0 if tile else -1)
     try:
         for r in range(world):
             bs = np.ascontiguousarray(b[:, r * w:(r + 1) * w] if layout == 0 else b[r * w:(r + 1) * w])
             _push(ctx, da, ctx.upload(bs), cs[r], M, w, K, layout, N, r * w, [cs[1 - r]])
         ctx.sync()
+        if pair:
+            assert ctx.get_option("last_tc_tile") == 2256
     finally:
         ctx.set_option("tc_block_n", 0)
+        ctx.set_option("tc_pair", -1)
     got = [c.numpy() for c in cs]
     np.testing.assert_array_equal(got[0], got[1])       # both copies hold every block, bit for bit
     assert_close_ref(got[0], ref, f"pushed blocks, tile {tile}")
@@ -75,7 +81,7 @@ def test_colsplit_push_tile_choice_with_peers(ctx):
         db, c, peer = ctx.alloc((w, K)), ctx.alloc((M, 8192)), ctx.alloc((M, 8192))
         _push(ctx, da, db, c, M, w, K, 1, 8192, 0, [peer] * (world - 1))
         ctx.sync()
-        assert ctx.get_option("last_tc_tile") in allowed, (world, ctx.get_option("last_tc_tile"))
+        assert ctx.get_option("last_tc_tile") in allowed + (2256,), (world, ctx.get_option("last_tc_tile"))
         for buf in (db, c, peer):
             buf.free()
     da.free()
