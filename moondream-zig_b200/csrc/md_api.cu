@@ -47,10 +47,22 @@ static int stage_reserve(md_ctx* ctx, int slot, size_t bytes, void** out) {
     return MD_OK;
 }
 
+// Copies a small operand out of pinned, mapped host memory (the SMs read it over the bus).
+__global__ void stage_in_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n16) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n16) dst[i] = src[i];
+}
+
 int md_stage_in(md_ctx* ctx, int slot, const void* user, size_t bytes, md_arg* out) {
     out->user = user;
     out->bytes = bytes;
-    if (md_is_device_ptr(user)) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, user) != cudaSuccess) {
+        cudaGetLastError();
+        attr.type = cudaMemoryTypeUnregistered;
+        attr.devicePointer = nullptr;
+    }
+    if (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) {
         out->dev = const_cast<void*>(user);
         out->staged = false;
         return MD_OK;
@@ -59,7 +71,19 @@ int md_stage_in(md_ctx* ctx, int slot, const void* user, size_t bytes, md_arg* o
         return md_fail(ctx, MD_ERR_UNSUPPORTED, "host pointers cannot be used while a graph is being captured");
     MD_TRY(stage_reserve(ctx, slot, bytes ? bytes : 1, &out->dev));
     out->staged = true;
-    if (bytes) MD_CUDA(ctx, cudaMemcpyAsync(out->dev, user, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    if (!bytes) return MD_OK;
+    // A small operand in pinned, mapped memory (the activations of a GEMV) is fetched by a kernel instead of the copy
+    // engine: the call then queues two kernels on one engine, without the copy's start-up and the hand-over between
+    // the engines, which together cost more than the GEMV itself.
+    if (bytes <= ((size_t)64 << 10) && (bytes % 16) == 0 && attr.type == cudaMemoryTypeHost && attr.devicePointer &&
+        (reinterpret_cast<uintptr_t>(attr.devicePointer) % 16) == 0) {
+        const size_t n16 = bytes / 16;
+        stage_in_kernel<<<(unsigned)((n16 + 255) / 256), 256, 0, ctx->stream>>>(
+            reinterpret_cast<const uint4*>(attr.devicePointer), reinterpret_cast<uint4*>(out->dev), n16);
+        MD_LAUNCH_CHECK(ctx, "stage_in_kernel");
+        return MD_OK;
+    }
+    MD_CUDA(ctx, cudaMemcpyAsync(out->dev, user, bytes, cudaMemcpyHostToDevice, ctx->stream));
     return MD_OK;
 }
 

@@ -335,3 +335,28 @@ def test_linearity_at_full_size(ctx):
     ys = ctx.hgemm_nt(s, wd, 1, n, k, out=np.empty((1, n), np.float16)).astype(np.float32)
     assert np.abs(ys - (y1 + y2)).max() <= 1e-2 * np.abs(ys).max() + 2e-3
     wd.free()
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 2048, 6144), (8, 2048, 2048), (8, 8192, 2048), (64, 2048, 512), (3, 2040, 136)])
+def test_pinned_host_operands_equal_pageable_ones(ctx, oracle, m, k, n):
+    """A caller's buffers in pinned, mapped host memory take two short cuts: a small input (up to 64 KB, a multiple
+    of 16 bytes, 16-byte aligned) is fetched by a kernel instead of the copy engine, and a small result is written
+    by the GEMM's own stores.  Same bits as the pageable path (which copies both ways), at sizes on both sides of the
+    limits and from a pinned buffer at an odd offset (which falls back to the copy)."""
+    import ctypes as C
+    import torch
+    rng = np.random.default_rng(m + k + n)
+    a, bt = f16_normal(rng, (m, k)), f16_normal(rng, (n, k), 0.05)
+    want = ctx.hgemm_nt(a, bt, m, n, k)                      # numpy arrays: pageable host memory
+    assert_close_ref(want, oracle.hgemm_nt(a, bt), "pageable operands")
+    dbt = ctx.upload(bt)
+    pin = torch.empty(m * k + 8, dtype=torch.float16).pin_memory()
+    out = torch.zeros((m, n), dtype=torch.float16).pin_memory()
+    sz = C.c_size_t
+    for off in (0, 4):                                      # 0: 16-byte aligned; 4 halves = 8 bytes off
+        view = pin[off:off + m * k]
+        view.copy_(torch.from_numpy(a.reshape(-1)))
+        out.zero_()
+        ctx._check(ctx.lib.md_hgemm_nt(ctx.h, C.c_void_p(view.data_ptr()), C.c_void_p(dbt.ptr),
+                                       C.c_void_p(out.data_ptr()), sz(m), sz(n), sz(k)))
+        np.testing.assert_array_equal(out.numpy(), want, err_msg=f"pinned operands, offset {off}")
