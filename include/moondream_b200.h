@@ -116,6 +116,11 @@ int md_set_gemm_mode(md_ctx* ctx, int mode);
  *   "prefill_fork"  1 (default) = a prefill layer runs fc1 -> fc2 as a second kernel chain beside the attention
  *   "decode_fork"   1 (default) = the fused decode layer runs as two concurrent kernel chains (q/k/v projection ->
  *                   attention -> out-projection | fc1 -> fc2) joined by events, 0 = three kernels in a row
+ *   "tc_splitk"     0 (default): never; -1: the tcgen05 GEMM splits K over several CTAs per tile where its cost model
+ *                   expects a gain (fewer 128 x 256 tiles than SMs and a long K; f32 partial tiles added up in a fixed
+ *                   order by the CTA that finishes last); 2..8: always that many ranges where the shape allows.
+ *                   Faster for such a product alone (761 x 2048 x 8192: 42.6 -> 33.4 us), slower inside the forked
+ *                   prefill layer, where the other chain's kernels already fill the SMs it leaves idle
  *   "attn_ctas_per_sm" 2 (default), 1: the tcgen05 attention runs that many CTAs per SM, each walking several
  *                   (query block, head, batch) items with its barriers, rings and TMEM kept; 0: one CTA per item
  *   "decode_loop"   n: the attention of a batched decode step with at least n (head, request) pairs runs one CTA per

@@ -67,13 +67,19 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     tn = r / rows;
 }
 
+// Barrier of the eight epilogue warps (id 1; 0 is __syncthreads).
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory"); }
+
 // PUSH = the column-split form with its eight extra warps (its own instantiation, so that the plain kernel keeps the
 // register budget of 320 threads)
 template <int BLOCK_N, bool B_MN_MAJOR, int MT, bool PUSH>
 __global__ void __launch_bounds__(PUSH ? NUM_THREADS_PUSH : NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_c, int M, int N, int K, int tiles_m, int num_tiles,
-               md_epilogue ep, md_push push, md_devflags* flags) {
+               md_epilogue ep, md_push push, md_devflags* flags, int splits, float* part, unsigned* tickets) {
+    // splits > 1 (MT == 1, no peers): a work unit is one of `splits` ranges of k-blocks of a tile.  Every unit leaves
+    // its f32 accumulators in `part` ([unit][column][row]); the unit that arrives last at the tile's ticket adds the
+    // ranges up in their order and runs the epilogue.  For products with fewer tiles than SMs and a long K.
     constexpr int STAGES = num_stages(BLOCK_N, MT);
     constexpr int A_TILE_BYTES = MT * A_STAGE_BYTES;   // MT sub-tiles of 128 rows, one after the other
     constexpr int B_STAGE_BYTES = BLOCK_N * BLOCK_K * 2;
@@ -107,6 +113,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
     const int tiles_n = num_tiles / tiles_m;
+    const int num_units = num_tiles * splits, kb_per = (num_kb + splits - 1) / splits;
+    volatile int* last_flag = reinterpret_cast<volatile int*>(bars_ptr + 16 * STAGES + 40 + 4 * EPI_WARPS);
 
     // programmatic dependent launch: the successor may start its own set-up now; this kernel sets up its
     // barriers and tensor memory, then waits for its predecessor before any global access
@@ -146,11 +154,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
-            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+                const int tile = unit / splits, kb0 = (unit - tile * splits) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
                 int tm, tn;
                 tile_coords(tile, tiles_m, tiles_n, tm, tn);
                 const int m0 = tm * TILE_M, n0 = tn * BLOCK_N;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, flags, 1);
                     const uint32_t full = bar_full + 8 * stage;
                     mbar_expect_tx(full, STAGE_BYTES);
@@ -189,13 +198,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             int stage = 0;
             uint32_t phase = 0;
             int local = 0;
-            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+            for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, ++local) {
+                const int kb0 = (unit % splits) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
                 const int buf = local % NBUF;
                 const uint32_t acc_phase = (uint32_t)(local / NBUF) & 1u;
                 mbar_wait(bar_tempty + 8 * buf, acc_phase ^ 1u, abort_flag, flags, 2);
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BLOCK_N);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     mbar_wait(bar_full + 8 * stage, phase, abort_flag, flags, 3);
                     tc_fence_after();
                     const uint32_t a_lo = a_lo0 + (uint32_t)stage * (A_TILE_BYTES >> 4);
@@ -204,7 +214,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     for (int mt = 0; mt < MT; ++mt) {
                         // sub-tile mt: rows mt*128.. of the A tile, accumulator columns mt*256..
                         const uint32_t d = tmem_d + (uint32_t)(mt * 256), am = a_lo + (uint32_t)(mt * (A_STAGE_BYTES >> 4));
-                        if (kb == 0) tc_mma_f16_parts<false>(d, am, a_hi, b_lo, b_hi, idesc);
+                        if (kb == kb0) tc_mma_f16_parts<false>(d, am, a_hi, b_lo, b_hi, idesc);
                         else tc_mma_f16_parts<true>(d, am, a_hi, b_lo, b_hi, idesc);
                     }
 #pragma unroll
@@ -230,7 +240,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         uint8_t* my_epi_ptr = epi_ptr + (warp - 2) * EPI_BUF_BYTES;
         const bool any_glue = ep.bias || ep.residual || ep.residual2 || ep.gelu;
         int local = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+        for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, ++local) {
+            const int tile = unit / splits;
             int tm, tn;
             tile_coords(tile, tiles_m, tiles_n, tm, tn);
             const int m0 = tm * TILE_M, n0 = tn * BLOCK_N;
@@ -238,6 +249,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const uint32_t acc_phase = (uint32_t)(local / NBUF) & 1u;
             mbar_wait(bar_tfull + 8 * buf, acc_phase, abort_flag, flags, 4);
             tc_fence_after();
+            const bool from_part = splits > 1;
+            if (from_part) {
+                // this unit's accumulators to global memory, [column][row] so that a warp's 32 rows are neighbours
+                float* mine = part + (size_t)unit * (BLOCK_M * BLOCK_N) + quad * 32 + lane;
+                const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BLOCK_N);
+#pragma unroll 1
+                for (int c = half; c < CHUNKS_N; c += 2) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t r[32];
+                        tc_ld_32x32(t_acc + (uint32_t)(c * 64 + h * 32), r);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) mine[(size_t)(c * 64 + h * 32 + e) * BLOCK_M] = __uint_as_float(r[e]);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+                __threadfence();
+                epi_sync();
+                if (threadIdx.x == 64) {
+                    const unsigned t = atomicAdd(tickets + tile, 1u);
+                    const int last = t == (unsigned)(splits - 1);
+                    if (last) tickets[tile] = 0u;   // zero again for the next launch
+                    *last_flag = last;
+                }
+                epi_sync();
+                if (!*last_flag) continue;   // another unit of this tile finishes it
+                __threadfence();
+            }
+            const float* parts = part + (size_t)tile * splits * (BLOCK_M * BLOCK_N) + quad * 32 + lane;
 #pragma unroll 1
             for (int cc = half; cc < CHUNKS; cc += 2) {
                 // chunk cc = 64 columns c of sub-tile mt
@@ -251,8 +294,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     uint32_t r[32];
-                    tc_ld_32x32(t_row + (uint32_t)(c * 64 + h * 32), r);
-                    tc_wait_ld();
+                    if (from_part) {
+                        // the k ranges added up in their order, whichever unit got here last; a range's 32 loads are
+                        // independent of one another and all in flight before the first add
+                        const float* src = parts + (size_t)(c * 64 + h * 32) * BLOCK_M;
+                        float acc[32];
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) acc[e] = __ldcg(src + e * BLOCK_M);
+                        for (int sp = 1; sp < splits; ++sp) {
+                            src += BLOCK_M * BLOCK_N;
+                            float nxt[32];
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) nxt[e] = __ldcg(src + e * BLOCK_M);
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) acc[e] += nxt[e];
+                        }
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(acc[e]);
+                    } else {
+                        tc_ld_32x32(t_row + (uint32_t)(c * 64 + h * 32), r);
+                        tc_wait_ld();
+                    }
                     const int col0 = n0 + c * 64 + h * 32;
                     // Glue per group of 8 columns (N % 8 == 0, so a group is entirely inside or outside
                     // the matrix): bias, residual and residual2 arrive as single 16-byte loads.
@@ -265,7 +327,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         *reinterpret_cast<uint4*>(out_row + chunk * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                     }
                 }
-                if (cc + 2 >= CHUNKS) {
+                if (cc + 2 >= CHUNKS && !from_part) {
                     // all of this warp's TMEM reads of the tile are done: hand the buffer back
                     tc_fence_before();
                     __syncwarp();
@@ -278,7 +340,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     tma_store_commit();
                 }
             }
-            if (half >= CHUNKS) {
+            if (half >= CHUNKS && !from_part) {
                 // a warp without a chunk (tile narrower than its share) still releases the accumulator
                 tc_fence_before();
                 __syncwarp();
@@ -381,7 +443,7 @@ int make_map_2d(md_ctx* ctx, CUtensorMap* map, const void* ptr, uint64_t inner, 
 
 template <int BLOCK_N, bool B_MN_MAJOR, int MT, bool PUSH>
 int launch_as(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
-           const md_epilogue& ep, size_t ldc, const md_push& push) {
+           const md_epilogue& ep, size_t ldc, const md_push& push, int splits = 1) {
     CUtensorMap tm_a, tm_b, tm_c;
     MD_TRY(make_map_2d(ctx, &tm_a, a, K, M, BLOCK_K, BLOCK_M));
     if (B_MN_MAJOR) MD_TRY(make_map_2d(ctx, &tm_b, b, N, K, 64, BLOCK_K));
@@ -389,7 +451,18 @@ int launch_as(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M
     MD_TRY(make_map_2d(ctx, &tm_c, c, N, M, 64, 32, ldc));
     const int tiles_m = (int)((M + MT * BLOCK_M - 1) / (MT * BLOCK_M)), tiles_n = (int)((N + BLOCK_N - 1) / BLOCK_N);
     const int num_tiles = tiles_m * tiles_n;
-    const int grid = num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count;
+    float* part = nullptr;
+    unsigned* tickets = nullptr;
+    if constexpr (MT != 1 || PUSH) {
+        if (splits > 1)
+            return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 GEMM: K is split only for single 128-row tiles without peers");
+    } else if (splits > 1) {
+        if (num_tiles > (int)MD_SPLITK_TICKETS)
+            return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 GEMM: too many tiles for a split K");
+        MD_TRY(md_splitk_workspace(ctx, (size_t)num_tiles * splits * BLOCK_M * BLOCK_N * sizeof(float), &part, &tickets));
+    }
+    const int units = num_tiles * splits;
+    const int grid = units < ctx->sm_count ? units : ctx->sm_count;
     auto kern = gemm_tc_kernel<BLOCK_N, B_MN_MAJOR, MT, PUSH>;
     constexpr int smem = smem_bytes(BLOCK_N, MT);
     const uint32_t cfg_bit = (MT == 2 ? (1u << (B_MN_MAJOR ? 12 : 11))
@@ -399,16 +472,17 @@ int launch_as(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M
         MD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         ctx->tc_configured |= cfg_bit;
     }
-    ctx->last_tc_tile = MT == 2 ? 512 : BLOCK_N;
+    ctx->last_tc_tile = (MT == 2 ? 512 : BLOCK_N) + (splits > 1 ? 10000 * splits : 0);   // 30256 = 128 x 256 tiles, K in 3
     return md_launch_ex(ctx, kern, dim3((unsigned)grid), dim3(PUSH ? NUM_THREADS_PUSH : NUM_THREADS), smem,
-                        "gemm_tc_kernel", tm_a, tm_b, tm_c, (int)M, (int)N, (int)K, tiles_m, num_tiles, ep, push, ctx->flags);
+                        "gemm_tc_kernel", tm_a, tm_b, tm_c, (int)M, (int)N, (int)K, tiles_m, num_tiles, ep, push, ctx->flags,
+                        splits, part, tickets);
 }
 
 template <int BLOCK_N, bool B_MN_MAJOR, int MT = 1>
 int launch(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M, size_t N, size_t K,
-           const md_epilogue& ep, size_t ldc, const md_push& push) {
+           const md_epilogue& ep, size_t ldc, const md_push& push, int splits = 1) {
     if (push.n > 0) return launch_as<BLOCK_N, B_MN_MAJOR, MT, true>(ctx, a, b, c, M, N, K, ep, ldc, push);
-    return launch_as<BLOCK_N, B_MN_MAJOR, MT, false>(ctx, a, b, c, M, N, K, ep, ldc, push);
+    return launch_as<BLOCK_N, B_MN_MAJOR, MT, false>(ctx, a, b, c, M, N, K, ep, ldc, push, splits);
 }
 
 }  // namespace
@@ -470,6 +544,39 @@ int md_launch_gemm_tc_ex(md_ctx* ctx, const __half* a, const __half* b, __half* 
             }
             if (best < 0.0 || cost < best) { best = cost; bn = cand_n[i]; mt = cand_mt[i]; }
         }
+    }
+    // Split K (md_set_option("tc_splitk"), off by default: inside the forked prefill layer the other chain's kernels
+    // already use the SMs such a product leaves idle, and the whole prefill measured 3.13 ms without against 3.27 ms
+    // with it).  With fewer 128 x 256 tiles than SMs and a long K (the 2048-wide outputs of a 761-row prefill, the
+    // 1152-wide ones of a one-crop ViT layer) most of the machine would idle through a long main loop.  S CTAs per
+    // tile take a range of k-blocks each; the f32 partial tiles meet in global memory, which measured about 10 us
+    // per launch whatever the shape (7600 units of the cost above: the partials out, fence and ticket, S partial tiles
+    // back in through the one SM that finishes the tile).  So it pays for the 2048 x 8192 product of a 761-row
+    // prefill (42.6 -> 33.4 us in three ranges) and not for its 2048 x 2048 one (15.3 -> 20.6 us) or the one-crop
+    // ViT shapes.  At least 8 k-blocks per range.
+    int splits = 1;
+    if (M > 64 && push.n == 0 && !ctx->tc_block_n && ctx->tc_splitk != 0) {
+        const size_t t256 = ((M + BLOCK_M - 1) / BLOCK_M) * ((N + 255) / 256);
+        const int kblocks = (int)((K + BLOCK_K - 1) / BLOCK_K);
+        int s_max = t256 ? (int)((size_t)ctx->sm_count / t256) : 1;
+        if (s_max > 4) s_max = 4;
+        if (ctx->tc_splitk >= 2) s_max = ctx->tc_splitk;
+        while (s_max > 1 && (kblocks / s_max < 8 || (s_max - 1) * ((kblocks + s_max - 1) / s_max) >= kblocks)) --s_max;
+        if (s_max >= 2 && t256 <= MD_SPLITK_TICKETS) {
+            const double rows = BLOCK_M, per = (double)((kblocks + s_max - 1) / s_max);
+            const size_t waves = (t256 * s_max + ctx->sm_count - 1) / ctx->sm_count;
+            const double cost = (double)waves * ((rows + 256.0) * per + 7600.0);
+            // the unsplit choice above, recomputed (best is local to the loop): rows + columns per k-block and wave
+            const size_t rows_b = (size_t)mt * BLOCK_M;
+            const size_t t_b = ((M + rows_b - 1) / rows_b) * ((N + bn - 1) / bn);
+            const size_t waves_b = (t_b + ctx->sm_count - 1) / ctx->sm_count;
+            const double cost_b = (double)waves_b * (double)(rows_b + bn) * kblocks * (mt == 2 ? 1.3 : 1.0);
+            if (ctx->tc_splitk >= 2 || cost < cost_b) { splits = s_max; bn = 256; mt = 1; }
+        }
+    }
+    if (splits > 1) {
+        if (b_layout == 0) return launch<256, true>(ctx, a, b, c, M, N, K, ep, ldc, push, splits);
+        return launch<256, false>(ctx, a, b, c, M, N, K, ep, ldc, push, splits);
     }
     // CTA pairs (gemm_pair.cu): where the single-CTA choice is the 128 x 256 tile and there are rows for both CTAs of
     // a pair, the pair's 256 x 256 tile does the same work per SM with a third less traffic from L2 and measured

@@ -175,6 +175,38 @@ int md_scratch(md_ctx* ctx, size_t bytes, void** out) {
     return MD_OK;
 }
 
+// Partial tiles and tickets of a split-K GEMM for the stream the context is on.
+int md_splitk_workspace(md_ctx* ctx, size_t bytes, float** part, unsigned** tickets) {
+    md_ctx::SplitK* ws = nullptr;
+    for (auto& w : ctx->splitk)
+        if (w.stream == ctx->stream) ws = &w;
+    if (!ws || ws->cap < bytes) {
+        if (ctx->capturing)
+            return md_fail(ctx, MD_ERR_UNSUPPORTED,
+                           "split-K workspace would have to grow during graph capture; run the call once before capturing");
+        if (!ws) {
+            ctx->splitk.emplace_back();
+            ws = &ctx->splitk.back();
+            ws->stream = ctx->stream;
+            MD_CUDA(ctx, cudaMalloc((void**)&ws->tickets, MD_SPLITK_TICKETS * sizeof(unsigned)));
+            MD_CUDA(ctx, cudaMemset(ws->tickets, 0, MD_SPLITK_TICKETS * sizeof(unsigned)));
+        }
+        if (ws->part) {
+            MD_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            MD_CUDA(ctx, cudaFree(ws->part));
+            ws->part = nullptr;
+            ws->cap = 0;
+        }
+        const size_t cap = (bytes + bytes / 4 + 255) & ~(size_t)255;
+        MD_CUDA(ctx, cudaMalloc((void**)&ws->part, cap));
+        ws->cap = cap;
+        ctx->generation++;  // graphs that hold the old address are stale
+    }
+    *part = ws->part;
+    *tickets = ws->tickets;
+    return MD_OK;
+}
+
 int md_rope_cached(md_ctx* ctx, size_t rot_dim, float theta, size_t rows, const float** out) {
     if (!ctx->rope_tab || ctx->rope_dim != rot_dim || ctx->rope_theta != theta || ctx->rope_rows < rows) {
         if (ctx->capturing)
@@ -252,6 +284,10 @@ int md_destroy(md_ctx* ctx) {
     for (auto& s : ctx->stage)
         if (s.ptr) cudaFree(s.ptr);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    for (auto& w : ctx->splitk) {
+        if (w.part) cudaFree(w.part);
+        if (w.tickets) cudaFree(w.tickets);
+    }
     if (ctx->counters) cudaFree(ctx->counters);
     if (ctx->rope_tab) cudaFree(ctx->rope_tab);
     if (ctx->flags) cudaFree(ctx->flags);
@@ -354,6 +390,11 @@ int md_set_option(md_ctx* ctx, const char* key, long value) {
     if (!strcmp(key, "pdl")) { ctx->pdl = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "prefill_fork")) { ctx->prefill_fork = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "decode_fork")) { ctx->decode_fork = value ? 1 : 0; return MD_OK; }
+    if (!strcmp(key, "tc_splitk")) {
+        if (value < -1 || value == 1 || value > 8) return md_fail(ctx, MD_ERR_INVALID_ARG, "tc_splitk must be -1, 0 or 2..8");
+        ctx->tc_splitk = (int)value;
+        return MD_OK;
+    }
     if (!strcmp(key, "attn_ctas_per_sm")) {
         if (value < 0 || value > 2) return md_fail(ctx, MD_ERR_INVALID_ARG, "attn_ctas_per_sm must be 0, 1 or 2");
         ctx->attn_ctas_per_sm = (int)value;

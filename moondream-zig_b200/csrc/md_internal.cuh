@@ -41,6 +41,7 @@ struct md_graph {
 };
 
 constexpr size_t MD_COUNTER_WORDS = 256;
+constexpr size_t MD_SPLITK_TICKETS = 1024;   // tiles of a split-K GEMM (one arrival ticket each)
 
 struct md_ctx {
     int device = 0;
@@ -56,6 +57,11 @@ struct md_ctx {
     // staging buffers for host-pointer ("drop-in") calls, grown on demand
     struct Stage { void* ptr = nullptr; size_t cap = 0; };
     std::vector<Stage> stage;
+    // split-K GEMM: f32 partial tiles and arrival tickets, one set per stream that has used it (the two chains of a
+    // forked layer run such products at the same time); tickets are zero between launches
+    struct SplitK { cudaStream_t stream = nullptr; float* part = nullptr; size_t cap = 0; unsigned* tickets = nullptr; };
+    std::vector<SplitK> splitk;
+    int tc_splitk = 0;          // md_set_option("tc_splitk"): 0 never (default), -1 the cost model decides, n >= 2 always n ranges
     // scratch for kernels that need global memory beyond inputs and outputs
     void* scratch = nullptr;
     size_t scratch_cap = 0;
@@ -147,6 +153,7 @@ __device__ __forceinline__ void md_pdl_wait() { asm volatile("griddepcontrol.wai
 int md_rope_cached(md_ctx* ctx, size_t rot_dim, float theta, size_t rows, const float** out);
 // Ensure ctx->scratch holds at least `bytes`.
 int md_scratch(md_ctx* ctx, size_t bytes, void** out);
+int md_splitk_workspace(md_ctx* ctx, size_t bytes, float** part, unsigned** tickets);
 
 // Host-or-device argument resolution for drop-in calls.
 bool md_is_device_ptr(const void* p);

@@ -317,6 +317,51 @@ def test_gemm_on_cta_pairs(ctx, oracle, m, k, n, layout):
         b.free()
 
 
+@pytest.mark.parametrize("layout", [0, 1])
+@pytest.mark.parametrize("m,k,n,splits", [(761, 8192, 2048, 3), (729, 4304, 1152, 4), (300, 1024, 264, 2),
+                                          (129, 2048, 8, 4), (761, 8192, 2048, -1), (2304, 1024, 2048, 2)])
+def test_gemm_with_k_split_over_ctas(ctx, oracle, m, k, n, splits, layout):
+    """Option tc_splitk: S CTAs per 128 x 256 tile take a range of k-blocks each, leave f32 partial tiles in global
+    memory, and the CTA that arrives last at the tile's ticket adds them up in their order and runs the fused
+    epilogue.  Ragged M, N and K (a last range shorter than the others), more units than SMs (the last shape), the
+    cost model's own choice (-1: it must split the 761 x 2048 x 8192 product), twice in a row with the same bits
+    (tickets back at zero, fixed summation order); against the oracle, and close to the unsplit kernel."""
+    rng = np.random.default_rng(m + n + k + layout)
+    a = f16_normal(rng, (m, k))
+    w_kn = f16_normal(rng, (k, n), 0.05)
+    bias, res = f16_normal(rng, (n,), 0.5), f16_normal(rng, (m, n))
+    w = w_kn if layout == 0 else np.ascontiguousarray(w_kn.T)
+    ref = oracle.hgemm_nn(a, w_kn) if layout == 0 else oracle.hgemm_nt(a, w)
+    ref = oracle.add(oracle.gelu(oracle.bias_add(ref, bias)), res)
+    da, dw, db, dr = ctx.upload(a), ctx.upload(w), ctx.upload(bias), ctx.upload(res)
+    outs = {}
+    for mode in (splits, 0):
+        ctx.set_option("tc_splitk", mode)
+        try:
+            runs = []
+            for _ in range(2):
+                out = ctx.alloc((m, n))
+                ctx.hgemm_fused(da, dw, out, m, n, k, layout, bias=db, gelu=True, residual=dr)
+                ctx.sync()
+                runs.append(out.numpy())
+                out.free()
+            tile = ctx.get_option("last_tc_tile")
+            if mode == 0:
+                assert tile < 10000
+            elif mode > 0:
+                assert tile == 10000 * mode + 256, tile
+            else:
+                assert tile >= 20000 and tile % 10000 == 256, tile
+            np.testing.assert_array_equal(runs[0], runs[1])
+            outs[mode] = runs[0]
+        finally:
+            ctx.set_option("tc_splitk", 0)
+    assert_close_ref(outs[splits], ref, "split-K GEMM")
+    assert_close_ref(outs[splits], outs[0], "split against unsplit", rel=2e-3)
+    for b in (da, dw, db, dr):
+        b.free()
+
+
 def test_linearity_at_full_size(ctx):
     """Size-independent property at the lm_head size: (a1 + a2) W == a1 W + a2 W up to rounding,
     and a one-hot activation selects a weight column exactly."""
