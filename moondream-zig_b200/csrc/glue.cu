@@ -74,7 +74,10 @@ layernorm_kernel(const __half* __restrict__ x, const __half* __restrict__ w, con
 // The same LayerNorm for rows of up to 2048 columns with cols % 8 == 0 and 16-byte aligned rows: one warp per
 // row (no shared memory, no block barrier), every access a 16-byte vector, the row held in registers.
 constexpr int LN_ROWS_PER_CTA = 4;
-__global__ void __launch_bounds__(LN_ROWS_PER_CTA * 32)
+// The row stays in registers as the 16-byte vectors it was loaded as (4 registers per 8 columns, not 8 floats), so
+// that eight or more CTAs fit an SM and enough loads are in flight to reach the memory rate; the three passes (sum,
+// squared deviations, output) convert on the fly, in the same order as before.
+__global__ void __launch_bounds__(LN_ROWS_PER_CTA * 32, 8)
 layernorm_vec_kernel(const __half* __restrict__ x, const __half* __restrict__ w, const __half* __restrict__ b,
                      __half* __restrict__ y, int rows, int cols, float eps) {
     constexpr int MAXCH = 8;  // 8 chunks x 32 lanes x 8 halves = 2048 columns
@@ -84,19 +87,20 @@ layernorm_vec_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
     if (row >= rows) return;
     const int chunks = cols >> 3;
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * cols);
-    float v[MAXCH][8];
-    float sum = 0.f;
+    uint4 raw[MAXCH];
 #pragma unroll
     for (int i = 0; i < MAXCH; ++i) {
         const int c = lane + 32 * i;
-        if (c < chunks) {
-            const uint4 u = xr[c];
-            const __half2* h = reinterpret_cast<const __half2*>(&u);
+        if (c < chunks) raw[i] = xr[c];
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXCH; ++i) {
+        if (lane + 32 * i < chunks) {
+            const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float2 f = __half22float2(h[j]);
-                v[i][2 * j] = f.x;
-                v[i][2 * j + 1] = f.y;
                 sum += f.x + f.y;
             }
         }
@@ -106,10 +110,13 @@ layernorm_vec_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
 #pragma unroll
     for (int i = 0; i < MAXCH; ++i) {
         if (lane + 32 * i < chunks) {
+            const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float d = v[i][j] - mean;
-                sq += d * d;
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                const float d0 = f.x - mean, d1 = f.y - mean;
+                sq += d0 * d0;
+                sq += d1 * d1;
             }
         }
     }
@@ -121,13 +128,13 @@ layernorm_vec_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
         if (c < chunks) {
             const uint4 uw = reinterpret_cast<const uint4*>(w)[c], ub = reinterpret_cast<const uint4*>(b)[c];
             const __half2 *hw = reinterpret_cast<const __half2*>(&uw), *hb = reinterpret_cast<const __half2*>(&ub);
+            const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
             uint4 o;
             __half2* ho = reinterpret_cast<__half2*>(&o);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const float2 fw = __half22float2(hw[j]), fb = __half22float2(hb[j]);
-                ho[j] = __floats2half2_rn((v[i][2 * j] * rstd - mean_rstd) * fw.x + fb.x,
-                                          (v[i][2 * j + 1] * rstd - mean_rstd) * fw.y + fb.y);
+                const float2 f = __half22float2(h[j]), fw = __half22float2(hw[j]), fb = __half22float2(hb[j]);
+                ho[j] = __floats2half2_rn((f.x * rstd - mean_rstd) * fw.x + fb.x, (f.y * rstd - mean_rstd) * fw.y + fb.y);
             }
             yr[c] = o;
         }
