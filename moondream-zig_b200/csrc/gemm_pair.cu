@@ -16,6 +16,8 @@
 //   tfull[b]   per CTA: committed the same way when a tile's accumulators are complete
 //   tempty[b]  leader's only: 16 arrivals, the 8 epilogue warps of each CTA (the second CTA's remotely)
 // Every wait is bounded as in the single-CTA kernel; the two cluster barriers (set-up, tear-down) are unconditional.
+#include <cstring>
+
 #include "md_internal.cuh"
 #include "tc_common.cuh"
 
@@ -94,7 +96,7 @@ template <bool B_MN_MAJOR, bool PUSH>
 __global__ void __launch_bounds__(PUSH ? NUM_THREADS_PUSH : NUM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_c, int M, int N, int K, int tiles_m, int num_tiles,
-                 md_epilogue ep, md_push push, md_devflags* flags) {
+                 md_epilogue ep, md_push push, md_devflags* flags, const __grid_constant__ md_peer_maps pm) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -273,10 +275,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 __syncwarp();
                 if (lane == 0) {
                     tma_store_2d(&tm_c, my_epi, n0 + c * 64, mrow0);
+                    if (PUSH && push.tma) {
+                        // the same staged chunk into every peer's C, starting with a different peer in every CTA
+                        for (int pi = 0; pi < push.n; ++pi) {
+                            int peer = pi + (int)blockIdx.x;
+                            peer -= (peer / push.n) * push.n;
+                            tma_store_2d(&pm.m[peer], my_epi, n0 + c * 64, mrow0);
+                        }
+                    }
                     tma_store_commit();
                 }
             }
-            if (PUSH && lane == 0) {
+            if (PUSH && !push.tma && lane == 0) {
                 // this warp's part of the tile is in this GPU's C once its TMA stores have completed: tell the
                 // push warps (every epilogue warp counts its own tiles)
                 tma_store_wait_all();
@@ -294,7 +304,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int pw = warp - (2 + EPI_WARPS);
         const int cl = lane * 8, ld = (int)push.ld;
         int local = 0;
-        for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
+        for (int tile = pair; tile < num_tiles && !push.tma; tile += num_pairs, ++local) {
             int tm, tn;
             pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
             const int m0 = tm * (2 * BLOCK_M) + (int)rank * BLOCK_M, n0 = tn * BLOCK_N;
@@ -355,7 +365,12 @@ int md_launch_gemm_pair(md_ctx* ctx, const __half* a, const __half* b, __half* c
     const int num_tiles = tiles_m * tiles_n;
     const int max_pairs = ctx->sm_count / 2;
     const int pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
-    void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, int, int, int, int, int, md_epilogue, md_push, md_devflags*) =
+    md_peer_maps pm;
+    memset(&pm, 0, sizeof(pm));
+    if (with_push && push.tma)
+        for (int i = 0; i < push.n; ++i) MD_TRY(md_make_map_2d(ctx, &pm.m[i], push.base[i], N, M, 64, 32, ldc));
+    void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, int, int, int, int, int, md_epilogue, md_push, md_devflags*,
+                 md_peer_maps) =
         with_push ? (mn ? gemm_pair_kernel<true, true> : gemm_pair_kernel<false, true>)
                   : (mn ? gemm_pair_kernel<true, false> : gemm_pair_kernel<false, false>);
     const uint32_t cfg_bit = 1u << ((mn ? 1 : 0) + (with_push ? 2 : 0));
@@ -379,7 +394,7 @@ int md_launch_gemm_pair(md_ctx* ctx, const __half* a, const __half* b, __half* c
     cfg.numAttrs = ctx->pdl ? 2 : 1;
     ctx->last_tc_tile = 2256;   // md_get_option("last_tc_tile"): 2256 = a 256 x 256 tile on a CTA pair
     const int Mi = (int)M, Ni = (int)N, Ki = (int)K;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, tm_c, Mi, Ni, Ki, tiles_m, num_tiles, ep, push, ctx->flags);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, tm_c, Mi, Ni, Ki, tiles_m, num_tiles, ep, push, ctx->flags, pm);
     if (e != cudaSuccess) return md_fail(ctx, MD_ERR_CUDA, "launch of gemm_pair_kernel failed: %s", cudaGetErrorString(e));
     ctx->launches++;
     return MD_OK;

@@ -28,6 +28,8 @@
 // Every mbarrier wait is bounded (about a second); a wait that gives up records an error
 // in the context's device flag word, raises a CTA-wide abort flag that makes all later
 // waits return at once, and the kernel still runs to its end, frees its TMEM and exits.
+#include <cstring>
+
 #include "md_internal.cuh"
 #include "tc_common.cuh"
 
@@ -76,7 +78,8 @@ template <int BLOCK_N, bool B_MN_MAJOR, int MT, bool PUSH>
 __global__ void __launch_bounds__(PUSH ? NUM_THREADS_PUSH : NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_c, int M, int N, int K, int tiles_m, int num_tiles,
-               md_epilogue ep, md_push push, md_devflags* flags, int splits, float* part, unsigned* tickets) {
+               md_epilogue ep, md_push push, md_devflags* flags, int splits, float* part, unsigned* tickets,
+               const __grid_constant__ md_peer_maps pm) {
     // splits > 1 (MT == 1, no peers): a work unit is one of `splits` ranges of k-blocks of a tile.  Every unit leaves
     // its f32 accumulators in `part` ([unit][column][row]); the unit that arrives last at the tile's ticket adds the
     // ranges up in their order and runs the epilogue.  For products with fewer tiles than SMs and a long K.
@@ -337,6 +340,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 __syncwarp();
                 if (lane == 0) {
                     tma_store_2d(&tm_c, my_epi, n0 + c * 64, mrow0);
+                    if (PUSH && push.tma) {
+                        // the same staged chunk into every peer's C, starting with a different peer in every CTA;
+                        // the staging buffer is reused once all of these stores have read it
+                        for (int pi = 0; pi < push.n; ++pi) {
+                            int peer = pi + (int)blockIdx.x;
+                            peer -= (peer / push.n) * push.n;
+                            tma_store_2d(&pm.m[peer], my_epi, n0 + c * 64, mrow0);
+                        }
+                    }
                     tma_store_commit();
                 }
             }
@@ -346,7 +358,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
             }
-            if (PUSH && lane == 0) {
+            if (PUSH && !push.tma && lane == 0) {
                 // Column-split GEMM: this warp's part of the tile is in this GPU's C once its TMA stores have
                 // completed; tell the push warps (every epilogue warp counts its own tiles).  The wait costs
                 // nothing: the warp would next wait for the following tile's accumulator anyway.
@@ -370,7 +382,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const int sub = lane / LANES_PER_ROW, cl = (lane % LANES_PER_ROW) * 8;
         const int ld = (int)push.ld;
         int local = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+        for (int tile = blockIdx.x; tile < num_tiles && !push.tma; tile += gridDim.x, ++local) {
             int tm, tn;
             tile_coords(tile, tiles_m, tiles_n, tm, tn);
             const int m0 = tm * TILE_M, n0 = tn * BLOCK_N;
@@ -461,6 +473,10 @@ int launch_as(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M
             return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 GEMM: too many tiles for a split K");
         MD_TRY(md_splitk_workspace(ctx, (size_t)num_tiles * splits * BLOCK_M * BLOCK_N * sizeof(float), &part, &tickets));
     }
+    md_peer_maps pm;
+    memset(&pm, 0, sizeof(pm));
+    if (PUSH && push.tma)
+        for (int i = 0; i < push.n; ++i) MD_TRY(make_map_2d(ctx, &pm.m[i], push.base[i], N, M, 64, 32, ldc));
     const int units = num_tiles * splits;
     const int grid = units < ctx->sm_count ? units : ctx->sm_count;
     auto kern = gemm_tc_kernel<BLOCK_N, B_MN_MAJOR, MT, PUSH>;
@@ -475,7 +491,7 @@ int launch_as(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M
     ctx->last_tc_tile = (MT == 2 ? 512 : BLOCK_N) + (splits > 1 ? 10000 * splits : 0);   // 30256 = 128 x 256 tiles, K in 3
     return md_launch_ex(ctx, kern, dim3((unsigned)grid), dim3(PUSH ? NUM_THREADS_PUSH : NUM_THREADS), smem,
                         "gemm_tc_kernel", tm_a, tm_b, tm_c, (int)M, (int)N, (int)K, tiles_m, num_tiles, ep, push, ctx->flags,
-                        splits, part, tickets);
+                        splits, part, tickets, pm);
 }
 
 template <int BLOCK_N, bool B_MN_MAJOR, int MT = 1>

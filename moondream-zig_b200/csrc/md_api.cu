@@ -390,6 +390,7 @@ int md_set_option(md_ctx* ctx, const char* key, long value) {
     if (!strcmp(key, "pdl")) { ctx->pdl = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "prefill_fork")) { ctx->prefill_fork = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "decode_fork")) { ctx->decode_fork = value ? 1 : 0; return MD_OK; }
+    if (!strcmp(key, "push_tma")) { ctx->push_tma = value ? 1 : 0; return MD_OK; }
     if (!strcmp(key, "tc_splitk")) {
         if (value < -1 || value == 1 || value > 8) return md_fail(ctx, MD_ERR_INVALID_ARG, "tc_splitk must be -1, 0 or 2..8");
         ctx->tc_splitk = (int)value;
@@ -430,6 +431,7 @@ int md_get_option(md_ctx* ctx, const char* key, long* value_out) {
     if (!strcmp(key, "gemv_variant")) { *value_out = ctx->gemv_variant; return MD_OK; }
     if (!strcmp(key, "tc_block_n")) { *value_out = ctx->tc_block_n; return MD_OK; }
     if (!strcmp(key, "pdl")) { *value_out = ctx->pdl; return MD_OK; }
+    if (!strcmp(key, "push_tma")) { *value_out = ctx->push_tma; return MD_OK; }
     return md_fail(ctx, MD_ERR_INVALID_ARG, "md_get_option: unknown key '%s'", key);
 }
 
@@ -574,6 +576,7 @@ int md_hgemm_colsplit_push(md_ctx* ctx, const uint16_t* a, const uint16_t* b_sli
         push.base[i] = reinterpret_cast<__half*>(peer_c_full[i]) + col_offset;
     }
     push.self = reinterpret_cast<const __half*>(c_full) + col_offset;
+    push.tma = ctx->push_tma ? 1 : 0;
     md_epilogue ep;
     return md_launch_gemm_tc_ex(ctx, (const __half*)a, (const __half*)b_slice, (__half*)c_full + col_offset, M, N_local, K,
                                 b_layout, ep, N_total, push);

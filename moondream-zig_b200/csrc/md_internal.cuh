@@ -61,6 +61,8 @@ struct md_ctx {
     // forked layer run such products at the same time); tickets are zero between launches
     struct SplitK { cudaStream_t stream = nullptr; float* part = nullptr; size_t cap = 0; unsigned* tickets = nullptr; };
     std::vector<SplitK> splitk;
+    int push_tma = 0;           // md_set_option("push_tma"): column-split GEMM pushes by TMA stores from the epilogue's staging
+                                // buffers (1) or by the push warps' plain stores (0)
     int tc_splitk = 0;          // md_set_option("tc_splitk"): 0 never (default), -1 the cost model decides, n >= 2 always n ranges
     // scratch for kernels that need global memory beyond inputs and outputs
     void* scratch = nullptr;
@@ -197,6 +199,12 @@ struct md_push {
     long long ld = 0;          // row stride of the peers' C in elements
     __half* base[7] = {};      // peer pointers to element (0, 0) of this rank's column block
     const __half* self = nullptr;  // the same element of this rank's own C (the push warps read the tile back from it)
+    int tma = 0;               // 1: the epilogue warps send each staged chunk to the peers with TMA stores (no push warps)
+};
+
+// Tensor maps over the peers' copies of this rank's column block (column-split GEMM with TMA pushes).
+struct md_peer_maps {
+    CUtensorMap m[7];
 };
 
 // gemv.cu: C[M,N] = A[M,K] . Bt[N,K]^T for M <= 8, K % 8 == 0.

@@ -40,7 +40,8 @@ def _push(ctx, a, b_slice, c_full, M, w, K, layout, N, off, peers):
 # tile: forced tile of the tcgen05 GEMM (0 = the cost model's choice, 512 = 256 x 256, "pair" = 256 x 256 on a CTA pair)
 @pytest.mark.parametrize("tile", [0, 64, 128, 256, 512, "pair"])
 @pytest.mark.parametrize("shape", [(4096, 256, 4096, 1), (1000, 520, 2000, 0), (300, 256, 512, 1)])
-def test_colsplit_push_fills_the_peers_copies(ctx, oracle, tile, shape):
+@pytest.mark.parametrize("push_tma", [0, 1], ids=["push_warps", "tma_stores"])
+def test_colsplit_push_fills_the_peers_copies(ctx, oracle, tile, shape, push_tma):
     """The push epilogue with peers, on one GPU: the two "ranks" are two calls and every rank's peer buffer is the
     other rank's C in the same device memory, so the dedicated push warps, the tile read-back and the column
     clipping at the block edge run exactly as they do across GPUs.  Several tiles per CTA in the first shape."""
@@ -55,6 +56,7 @@ def test_colsplit_push_fills_the_peers_copies(ctx, oracle, tile, shape):
     da = ctx.upload(a)
     cs = [ctx.upload(np.full((M, N), 7.0, np.float16)) for _ in range(world)]
     ctx.set_option("tc_block_n", tile)
+    ctx.set_option("push_tma", push_tma)   # 1: the epilogue's staged chunks go to the peers as TMA stores
     ctx.set_option("tc_pair", 1 if pair else 0 if tile else -1)
     try:
         for r in range(world):
@@ -66,6 +68,7 @@ def test_colsplit_push_fills_the_peers_copies(ctx, oracle, tile, shape):
     finally:
         ctx.set_option("tc_block_n", 0)
         ctx.set_option("tc_pair", -1)
+        ctx.set_option("push_tma", 0)
     got = [c.numpy() for c in cs]
     np.testing.assert_array_equal(got[0], got[1])       # both copies hold every block, bit for bit
     assert_close_ref(got[0], ref, f"pushed blocks, tile {tile}")
