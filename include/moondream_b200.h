@@ -116,7 +116,7 @@ int md_set_gemm_mode(md_ctx* ctx, int mode);
  *   "prefill_fork"  1 (default) = a prefill layer runs fc1 -> fc2 as a second kernel chain beside the attention
  *   "decode_fork"   1 (default) = the fused decode layer runs as two concurrent kernel chains (q/k/v projection ->
  *                   attention -> out-projection | fc1 -> fc2) joined by events, 0 = three kernels in a row
- *   "push_tma"      how md_hgemm_colsplit_push / _fused send a finished tile to the peers: 1 = the epilogue warps issue
+ *   "push_tma"      how md_hgemm_colsplit_push / _fused send a finished tile to the peers: 1 (default) = the epilogue warps issue
  *                   one more TMA store per peer from the shared-memory chunk they have just staged for this GPU's C;
  *                   0 = eight extra warps read the tile back from this GPU's C and store it with plain 16-byte stores
  *   "tc_splitk"     0 (default): never; -1: the tcgen05 GEMM splits K over several CTAs per tile where its cost model

@@ -15,9 +15,11 @@
 //               64 KB per 1024 tensor cycles instead of 48 KB per 512.
 //   warps 2..9  epilogue: tcgen05.ld (32 lanes x 32 columns) -> fused glue -> f16 ->
 //               swizzled smem -> TMA store (clips the M and N tails).
-//   warps 10..17 (column-split GEMM only) push: once a tile's TMA stores have completed they read the tile
-//               back from this GPU's C (L2 hits) and store it into the other GPUs' copies of C with plain
-//               16-byte peer stores.  The epilogue warps never wait for NVLink: they hand the accumulator
+//               Column-split GEMM (push.tma): every staged chunk also leaves as one TMA store per peer into
+//               the other GPUs' copies of C; the warp goes on when the stores have read the chunk.
+//   warps 10..17 (column-split GEMM with push.tma = 0) push: once a tile's TMA stores have completed they read
+//               the tile back from this GPU's C (L2 hits) and store it into the other GPUs' copies of C with
+//               plain 16-byte peer stores.  The epilogue warps never wait for NVLink: they hand the accumulator
 //               back to the MMA issuer as before, and the push of tile i runs beside the main loop of the
 //               following tiles.
 // Tiles are walked in groups of 8 tile rows (all tile columns of a group before the next group), so that the

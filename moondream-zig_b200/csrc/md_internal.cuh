@@ -61,8 +61,8 @@ struct md_ctx {
     // forked layer run such products at the same time); tickets are zero between launches
     struct SplitK { cudaStream_t stream = nullptr; float* part = nullptr; size_t cap = 0; unsigned* tickets = nullptr; };
     std::vector<SplitK> splitk;
-    int push_tma = 0;           // md_set_option("push_tma"): column-split GEMM pushes by TMA stores from the epilogue's staging
-                                // buffers (1) or by the push warps' plain stores (0)
+    int push_tma = 1;           // md_set_option("push_tma"): column-split GEMM pushes by TMA stores from the epilogue's staging
+                                // buffers (1, default) or by the push warps' plain stores (0)
     int tc_splitk = 0;          // md_set_option("tc_splitk"): 0 never (default), -1 the cost model decides, n >= 2 always n ranges
     // scratch for kernels that need global memory beyond inputs and outputs
     void* scratch = nullptr;

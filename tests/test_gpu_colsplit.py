@@ -68,7 +68,7 @@ def test_colsplit_push_fills_the_peers_copies(ctx, oracle, tile, shape, push_tma
     finally:
         ctx.set_option("tc_block_n", 0)
         ctx.set_option("tc_pair", -1)
-        ctx.set_option("push_tma", 0)
+        ctx.set_option("push_tma", 1)
     got = [c.numpy() for c in cs]
     np.testing.assert_array_equal(got[0], got[1])       # both copies hold every block, bit for bit
     assert_close_ref(got[0], ref, f"pushed blocks, tile {tile}")
