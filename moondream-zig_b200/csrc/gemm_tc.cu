@@ -76,12 +76,15 @@ __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n
 
 // PUSH = the column-split form with its eight extra warps (its own instantiation, so that the plain kernel keeps the
 // register budget of 320 threads)
-template <int BLOCK_N, bool B_MN_MAJOR, int MT, bool PUSH>
+// SPLITK = the form that may split K over several CTAs per tile (its own instantiation: the others compile with one
+// range per tile and carry none of its code).
+template <int BLOCK_N, bool B_MN_MAJOR, int MT, bool PUSH, bool SPLITK>
 __global__ void __launch_bounds__(PUSH ? NUM_THREADS_PUSH : NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_c, int M, int N, int K, int tiles_m, int num_tiles,
-               md_epilogue ep, md_push push, md_devflags* flags, int splits, float* part, unsigned* tickets,
+               md_epilogue ep, md_push push, md_devflags* flags, int splits_arg, float* part, unsigned* tickets,
                const __grid_constant__ md_peer_maps pm) {
+    const int splits = SPLITK ? splits_arg : 1;
     // splits > 1 (MT == 1, no peers): a work unit is one of `splits` ranges of k-blocks of a tile.  Every unit leaves
     // its f32 accumulators in `part` ([unit][column][row]); the unit that arrives last at the tile's ticket adds the
     // ranges up in their order and runs the epilogue.  For products with fewer tiles than SMs and a long K.
@@ -254,7 +257,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const uint32_t acc_phase = (uint32_t)(local / NBUF) & 1u;
             mbar_wait(bar_tfull + 8 * buf, acc_phase, abort_flag, flags, 4);
             tc_fence_after();
-            const bool from_part = splits > 1;
+            const bool from_part = SPLITK && splits > 1;
             if (from_part) {
                 // this unit's accumulators to global memory, [column][row] so that a warp's 32 rows are neighbours
                 float* mine = part + (size_t)unit * (BLOCK_M * BLOCK_N) + quad * 32 + lane;
@@ -467,9 +470,10 @@ int launch_as(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M
     const int num_tiles = tiles_m * tiles_n;
     float* part = nullptr;
     unsigned* tickets = nullptr;
-    if constexpr (MT != 1 || PUSH) {
+    if constexpr (MT != 1 || PUSH || BLOCK_N != 256) {
         if (splits > 1)
-            return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 GEMM: K is split only for single 128-row tiles without peers");
+            return md_fail(ctx, MD_ERR_UNSUPPORTED,
+                           "tcgen05 GEMM: K is split only for single 128 x 256 tiles without peers");
     } else if (splits > 1) {
         if (num_tiles > (int)MD_SPLITK_TICKETS)
             return md_fail(ctx, MD_ERR_UNSUPPORTED, "tcgen05 GEMM: too many tiles for a split K");
@@ -481,11 +485,16 @@ int launch_as(md_ctx* ctx, const __half* a, const __half* b, __half* c, size_t M
         for (int i = 0; i < push.n; ++i) MD_TRY(make_map_2d(ctx, &pm.m[i], push.base[i], N, M, 64, 32, ldc));
     const int units = num_tiles * splits;
     const int grid = units < ctx->sm_count ? units : ctx->sm_count;
-    auto kern = gemm_tc_kernel<BLOCK_N, B_MN_MAJOR, MT, PUSH>;
+    // the split-K instantiation exists for single 128-row tiles of 256 columns without peers only
+    constexpr bool CAN_SPLIT = MT == 1 && !PUSH && BLOCK_N == 256;
+    auto kern = (CAN_SPLIT && splits > 1) ? gemm_tc_kernel<BLOCK_N, B_MN_MAJOR, MT, PUSH, CAN_SPLIT>
+                                          : gemm_tc_kernel<BLOCK_N, B_MN_MAJOR, MT, PUSH, false>;
     constexpr int smem = smem_bytes(BLOCK_N, MT);
-    const uint32_t cfg_bit = (MT == 2 ? (1u << (B_MN_MAJOR ? 12 : 11))
-                                      : 1u << ((BLOCK_N == 256 ? 0 : BLOCK_N == 128 ? 1 : 2) + (B_MN_MAJOR ? 3 : 0)))
-                             << (PUSH ? 16 : 0);
+    const uint32_t cfg_bit = (CAN_SPLIT && splits > 1)
+                                 ? 1u << (B_MN_MAJOR ? 7 : 6)
+                                 : (MT == 2 ? (1u << (B_MN_MAJOR ? 12 : 11))
+                                            : 1u << ((BLOCK_N == 256 ? 0 : BLOCK_N == 128 ? 1 : 2) + (B_MN_MAJOR ? 3 : 0)))
+                                       << (PUSH ? 16 : 0);
     if (!(ctx->tc_configured & cfg_bit)) {
         MD_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         ctx->tc_configured |= cfg_bit;

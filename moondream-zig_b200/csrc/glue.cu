@@ -74,11 +74,73 @@ layernorm_kernel(const __half* __restrict__ x, const __half* __restrict__ w, con
 // The same LayerNorm for rows of up to 2048 columns with cols % 8 == 0 and 16-byte aligned rows: one warp per
 // row (no shared memory, no block barrier), every access a 16-byte vector, the row held in registers.
 constexpr int LN_ROWS_PER_CTA = 4;
-// The row stays in registers as the 16-byte vectors it was loaded as (4 registers per 8 columns, not 8 floats), so
-// that eight or more CTAs fit an SM and enough loads are in flight to reach the memory rate; the three passes (sum,
-// squared deviations, output) convert on the fly, in the same order as before.
-__global__ void __launch_bounds__(LN_ROWS_PER_CTA * 32, 8)
+__global__ void __launch_bounds__(LN_ROWS_PER_CTA * 32)
 layernorm_vec_kernel(const __half* __restrict__ x, const __half* __restrict__ w, const __half* __restrict__ b,
+                     __half* __restrict__ y, int rows, int cols, float eps) {
+    constexpr int MAXCH = 8;  // 8 chunks x 32 lanes x 8 halves = 2048 columns
+    const int lane = threadIdx.x & 31, row = blockIdx.x * LN_ROWS_PER_CTA + (threadIdx.x >> 5);
+    md_pdl_launch_dependents();
+    md_pdl_wait();
+    if (row >= rows) return;
+    const int chunks = cols >> 3;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * cols);
+    float v[MAXCH][8];
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXCH; ++i) {
+        const int c = lane + 32 * i;
+        if (c < chunks) {
+            const uint4 u = xr[c];
+            const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                v[i][2 * j] = f.x;
+                v[i][2 * j + 1] = f.y;
+                sum += f.x + f.y;
+            }
+        }
+    }
+    const float mean = warp_sum(sum) / (float)cols;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXCH; ++i) {
+        if (lane + 32 * i < chunks) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float d = v[i][j] - mean;
+                sq += d * d;
+            }
+        }
+    }
+    const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)cols + eps), mean_rstd = mean * rstd;
+    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * cols);
+#pragma unroll
+    for (int i = 0; i < MAXCH; ++i) {
+        const int c = lane + 32 * i;
+        if (c < chunks) {
+            const uint4 uw = reinterpret_cast<const uint4*>(w)[c], ub = reinterpret_cast<const uint4*>(b)[c];
+            const __half2 *hw = reinterpret_cast<const __half2*>(&uw), *hb = reinterpret_cast<const __half2*>(&ub);
+            uint4 o;
+            __half2* ho = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 fw = __half22float2(hw[j]), fb = __half22float2(hb[j]);
+                ho[j] = __floats2half2_rn((v[i][2 * j] * rstd - mean_rstd) * fw.x + fb.x,
+                                          (v[i][2 * j + 1] * rstd - mean_rstd) * fw.y + fb.y);
+            }
+            yr[c] = o;
+        }
+    }
+}
+
+// The same for many rows (more than the kernel above keeps resident at once): the row stays in registers as the 16-byte
+// vectors it was loaded as (4 registers per 8 columns, not 8 floats), so that eight CTAs fit an SM and enough loads
+// are in flight to reach the memory rate (9477 x 1152: 14.7 -> 11.9 us); the three passes (sum, squared deviations,
+// output) convert on the fly, in the same order, so the results are the same bits.  With few rows the conversions
+// only lengthen each row's chain, and the kernel above is the faster one.
+__global__ void __launch_bounds__(LN_ROWS_PER_CTA * 32, 8)
+layernorm_vec_packed_kernel(const __half* __restrict__ x, const __half* __restrict__ w, const __half* __restrict__ b,
                      __half* __restrict__ y, int rows, int cols, float eps) {
     constexpr int MAXCH = 8;  // 8 chunks x 32 lanes x 8 halves = 2048 columns
     const int lane = threadIdx.x & 31, row = blockIdx.x * LN_ROWS_PER_CTA + (threadIdx.x >> 5);
@@ -361,9 +423,15 @@ int md_launch_layernorm(md_ctx* ctx, const __half* x, const __half* w, const __h
     const bool vec = cols <= 2048 && (cols % 8) == 0 &&
                      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(w) |
                        reinterpret_cast<uintptr_t>(b)) & 15) == 0;
-    if (vec)
-        return md_launch_ex(ctx, layernorm_vec_kernel, dim3((unsigned)((rows + LN_ROWS_PER_CTA - 1) / LN_ROWS_PER_CTA)),
-                            dim3(LN_ROWS_PER_CTA * 32), 0, "layernorm_vec_kernel", x, w, b, y, (int)rows, (int)cols, eps);
+    if (vec) {
+        const dim3 grid((unsigned)((rows + LN_ROWS_PER_CTA - 1) / LN_ROWS_PER_CTA)), block(LN_ROWS_PER_CTA * 32);
+        // rows beyond what five CTAs per SM hold at once: the form with the smaller register footprint
+        if (rows > (size_t)5 * LN_ROWS_PER_CTA * ctx->sm_count)
+            return md_launch_ex(ctx, layernorm_vec_packed_kernel, grid, block, 0, "layernorm_vec_packed_kernel", x, w, b, y,
+                                (int)rows, (int)cols, eps);
+        return md_launch_ex(ctx, layernorm_vec_kernel, grid, block, 0, "layernorm_vec_kernel", x, w, b, y, (int)rows,
+                            (int)cols, eps);
+    }
     if (cols <= 256 * 8)
         return md_launch_ex(ctx, layernorm_kernel<256, 8>, dim3((unsigned)rows), dim3(256), 0, "layernorm_kernel", x, w, b,
                             y, (int)cols, eps);
