@@ -572,6 +572,11 @@ int md_launch_gemm_tc_ex(md_ctx* ctx, const __half* a, const __half* b, __half* 
             if (best < 0.0 || cost < best) { best = cost; bn = cand_n[i]; mt = cand_mt[i]; }
         }
     }
+    // Column-split products with rows for both CTAs of a pair and at least one 256-wide tile take the pair kernel
+    // whatever the search above found: measured at 8 GPUs (8192 x 1024 x 8192 per rank, seven peers) 265 us on pairs
+    // against 289-292 us on 128 x 128, 128 x 256 or 256 x 256 single-CTA tiles; at 2 and 4 GPUs the search picks the
+    // 128 x 256 tile, and with it the pairs, by itself.
+    if (push.n > 0 && M > 256 && N >= 256 && !ctx->tc_block_n && ctx->tc_pair < 0) { bn = 256; mt = 1; }
     // Split K (md_set_option("tc_splitk"), off by default: inside the forked prefill layer the other chain's kernels
     // already use the SMs such a product leaves idle, and the whole prefill measured 3.13 ms without against 3.27 ms
     // with it).  With fewer 128 x 256 tiles than SMs and a long K (the 2048-wide outputs of a 761-row prefill, the
