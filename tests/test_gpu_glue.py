@@ -15,6 +15,22 @@ def test_layernorm(ctx, oracle, rows, cols):
     assert_close_ref(ctx.layernorm(x, w, b, rows, cols), oracle.layernorm(x, w, b), "layernorm", rel=2e-3)
 
 
+@pytest.mark.parametrize("rows,cols", [(3645, 1152), (9477, 1152), (4000, 2048), (3000, 72)])
+def test_layernorm_with_many_rows_takes_the_packed_form_and_gives_the_same_bits(ctx, oracle, rows, cols):
+    """From about 3000 rows on (more than the one-warp-per-row kernel keeps resident) the LayerNorm keeps its row as
+    the loaded 16-byte vectors and converts in every pass.  Same operations in the same order: the rows of a large
+    call must equal, bit for bit, the same rows normalised in a small call (which takes the other kernel), and the
+    whole result the oracle's."""
+    rng = np.random.default_rng(rows + cols)
+    x = f16_normal(rng, (rows, cols), 2.0)
+    w, b = f16_normal(rng, (cols,)), f16_normal(rng, (cols,), 0.1)
+    big = ctx.layernorm(x, w, b, rows, cols)
+    assert_close_ref(big, oracle.layernorm(x, w, b), "layernorm, many rows", rel=2e-3)
+    for lo in (0, rows - 500):
+        small = ctx.layernorm(np.ascontiguousarray(x[lo:lo + 500]), w, b, 500, cols)
+        np.testing.assert_array_equal(big[lo:lo + 500], small)
+
+
 def test_layernorm_and_broadcast_add_reference_cases(ctx):
     """The reference's own known-answer cases for the glue (ops_test.zig:1773-1824, 1849-1866, 2547-2640),
     through the C ABI."""
