@@ -37,6 +37,21 @@ def test_every_entry_point_cites_the_reference():
         assert zig in text, zig
 
 
+def test_every_option_key_is_documented_in_the_header():
+    """md_set_option / md_get_option compare the key against string literals; each of them must appear, quoted, in the
+    public header's option list."""
+    src = open(os.path.join(entry.PKG_DIR, "csrc", "md_api.cu")).read()
+    header = open(os.path.join(entry.ROOT, "include", "moondream_b200.h")).read()
+    keys = set()
+    for fn in ("int md_set_option(", "int md_get_option("):
+        body = src[src.index(fn):]
+        body = body[:body.index("\n}\n")]
+        keys |= set(re.findall(r'strcmp\(key, "(\w+)"\)', body))
+    assert len(keys) >= 20
+    undocumented = sorted(k for k in keys if f'"{k}"' not in header)
+    assert not undocumented, f"options missing from include/moondream_b200.h: {undocumented}"
+
+
 def test_no_cpu_fallback_without_gpu(pkg):
     import torch
     if torch.cuda.is_available():
