@@ -127,7 +127,7 @@ int md_set_gemm_mode(md_ctx* ctx, int mode);
  *   "attn_ctas_per_sm" 2 (default), 1: the tcgen05 attention runs that many CTAs per SM, each walking several
  *                   (query block, head, batch) items with its barriers, rings and TMEM kept; 0: one CTA per item
  *   "decode_loop"   n: the attention of a batched decode step with at least n (head, request) pairs runs one CTA per
- *                   pair that walks all of its keys (nothing to merge across CTAs); -1 (default) = 192, 0 = never
+ *                   pair that walks all of its keys (nothing to merge across CTAs); -1 (default) = 128 (four requests of 32 heads), 0 = never
  *   "decode_mlp_split" 2 (default) or 4 = with decode_fork and a single request, the MLP chain runs as that many
  *                   independent chains (a slice of fc1's rows, then that slice of fc2's K sum as f32 partial sums) which
  *                   the out-projection's epilogue adds with the reference's roundings; 0 = one MLP chain */

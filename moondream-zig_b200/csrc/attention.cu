@@ -922,7 +922,7 @@ int md_launch_sdpa(md_ctx* ctx, const __half* q, const __half* k, const __half* 
 static bool decode_loop_wanted(const md_ctx* ctx, const DecodeParams& p, size_t batch) {
     if (ctx->decode_loop == 0 || !p.fused || p.rot_dim > DEC_D) return false;
     if (ctx->decode_loop < 0 && batch < 2) return false;   // a single request keeps the key splits unless asked
-    return batch * (size_t)p.n_heads >= (size_t)(ctx->decode_loop > 0 ? ctx->decode_loop : 192);
+    return batch * (size_t)p.n_heads >= (size_t)(ctx->decode_loop > 0 ? ctx->decode_loop : 128);
 }
 
 static int decode_loop_launch(md_ctx* ctx, const DecodeParams& p, size_t batch) {

@@ -101,7 +101,7 @@ struct md_ctx {
     int attn_ctas_per_sm = 2;   // md_set_option("attn_ctas_per_sm"): grid of the tcgen05 attention = this many CTAs per SM, each
                                 // walking several (query block, head, batch) items; 0 = one CTA per item
     int decode_loop = -1;       // md_set_option("decode_loop"): batched decode attention as one CTA per (head, request) when there
-                                // are at least this many pairs; -1 = 192, 0 = never
+                                // are at least this many pairs; -1 = 128, 0 = never
     int decode_mlp_split = 2;   // md_set_option("decode_mlp_split"): single-request decode runs the MLP as 2 or 4 chains (0 = one)
     cudaStream_t side_stream = nullptr;  // second chain of the forked decode layer
     cudaStream_t mlp_stream[3] = {};     // further chains when the MLP is split (its first part runs on side_stream)
