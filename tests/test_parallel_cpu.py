@@ -51,6 +51,108 @@ def test_gather_tokens_single_process():
         p.gather_tokens({0: np.array([1])}, 2)
 
 
+class _Buf:
+    _next = 0x10000
+
+    def __init__(self, shape):
+        self.shape, self.ptr = shape, _Buf._next
+        _Buf._next += 0x100000
+
+
+class _Ctx:
+    def alloc(self, shape):
+        return _Buf(shape)
+
+
+class _Vision:
+    """Stands in for models.VisionModel: records what the request driver asks for."""
+    tokens, proj_out = 729, 2048
+
+    def __init__(self, max_crops):
+        self.max_crops, self.calls = max_crops, []
+
+    def encode(self, crops, out_ptr):
+        self.calls.append(("one", crops.shape[0], out_ptr))
+
+    def encode_images(self, images, out_ptrs):
+        self.calls.append(("together", images.shape[0], list(out_ptrs)))
+
+
+class _Req:
+    def reset(self):
+        pass
+
+
+class _Text:
+    """Stands in for models.TextModel: the "first token" of a request is its prompt length, the generated tokens
+    count up from it unless forced."""
+    dim = 2048
+
+    def __init__(self):
+        self.encoded, self.forwards, self.batches = [], [], []
+
+    def request(self):
+        return _Req()
+
+    def text_encoder(self, ids, out_ptr):
+        self.encoded.append((len(ids), out_ptr))
+
+    def forward(self, req, base, want_hidden, want_logits, rows):
+        self.forwards.append((base, rows))
+        return None, None, rows
+
+    def generate_batch(self, reqs, firsts, n_steps, forced=None):
+        self.batches.append((len(reqs), list(firsts), None if forced is None else forced.copy()))
+        if forced is not None:
+            return forced
+        return np.stack([np.arange(f + 1, f + 1 + n_steps, dtype=np.uint32) for f in firsts])
+
+
+def test_serve_requests_groups_and_addresses_without_a_gpu():
+    """The request driver's host logic with stand-in models: this rank's share, groups of max_streams, one embeds
+    buffer per slot laid out [token 0 | 729 image rows | rest of the prompt], the images of a group encoded together
+    only when each is one crop and the encoder has the capacity, forced tokens handed through per group."""
+    p = par()
+    rng = np.random.default_rng(0)
+    lens = [3, 5, 2, 7, 4, 6, 1]
+    requests = [p.Request(rng.integers(0, 256, (1, 378, 378, 3), dtype=np.uint8), np.arange(n)) for n in lens]
+    requests[5] = p.Request(rng.integers(0, 256, (2, 378, 378, 3), dtype=np.uint8), np.arange(lens[5]))  # two crops
+    ctx, vis, txt = _Ctx(), _Vision(max_crops=4), _Text()
+    out = p.serve_requests(ctx, vis, txt, requests, world=2, rank=1, n_steps=3, max_streams=2)
+    assert sorted(out) == [1, 3, 5]                       # request i -> rank i mod 2
+    for i in (1, 3, 5):
+        rows = lens[i] + 729
+        assert out[i].tolist() == [rows, rows + 1, rows + 2, rows + 3]     # first token, then three steps
+    # groups: (1, 3) together, (5) alone (a group of one, and two crops anyway)
+    assert [c[0] for c in vis.calls] == ["together", "one"]
+    kind, n_img, ptrs = vis.calls[0]
+    assert n_img == 2 and len(ptrs) == 2
+    bases = [f[0] for f in txt.forwards]
+    assert ptrs == [bases[0] + 2048 * 2, bases[1] + 2048 * 2]            # image rows start after the first token's row
+    # slot 0 again in the second group; its request is one row longer than the slot's buffer, which is replaced
+    assert vis.calls[1][2] == bases[2] + 2048 * 2 and bases[2] != bases[0]
+    assert [f[1] for f in txt.forwards] == [lens[1] + 729, lens[3] + 729, lens[5] + 729]
+    # token 0 at the base, the rest of the prompt after the image rows
+    assert txt.encoded[0] == (1, bases[0]) and txt.encoded[1] == (lens[1] - 1, bases[0] + 730 * 2048 * 2)
+    assert [b[0] for b in txt.batches] == [2, 1]
+    # a state dict carried over keeps the requests' caches and the embeds buffers (now large enough for every slot)
+    state = {}
+    t1, t2 = _Text(), _Text()
+    p.serve_requests(ctx, _Vision(4), t1, requests, world=2, rank=1, n_steps=3, max_streams=2, state=state)
+    p.serve_requests(ctx, _Vision(4), t2, requests, world=2, rank=1, n_steps=3, max_streams=2, state=state)
+    assert [f[0] for f in t2.forwards] == [t1.forwards[2][0], t1.forwards[1][0], t1.forwards[2][0]]
+    # capacity too small for the group: one encode per request
+    vis2 = _Vision(max_crops=1)
+    p.serve_requests(ctx, vis2, _Text(), requests, world=2, rank=1, n_steps=3, max_streams=2)
+    assert [c[0] for c in vis2.calls] == ["one", "one", "one"]
+    # forced tokens reach generate_batch per group, in slot order
+    forced = {i: np.array([9, 8, 7], np.uint32) + i for i in (1, 3, 5)}
+    txt3 = _Text()
+    out3 = p.serve_requests(ctx, _Vision(4), txt3, requests, world=2, rank=1, n_steps=3, max_streams=2, forced=forced)
+    assert txt3.batches[0][2].tolist() == [forced[1].tolist(), forced[3].tolist()]
+    assert out3[3].tolist() == [lens[3] + 729] + forced[3].tolist()
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
