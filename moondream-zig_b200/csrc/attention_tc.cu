@@ -8,8 +8,10 @@
 // takes one item per round of gridDim.x items and keeps its barriers, its tensor memory and its rings across
 // them, so that from the second item on nothing of a CTA's start-up (launch, barrier set-up, TMEM allocation,
 // descriptor fetch, first loads) is paid again: the producer fetches the next item's Q as soon as the softmax warps
-// have moved the current one into tensor memory, and its K / V tiles as ring stages come free.
-//   warp 0      TMA producer: per item Q, then K and V tiles of 64 keys through their own rings of three stages.
+// have moved the current one into tensor memory, and its K / V tiles as ring stages come free.  Rounds alternate
+// direction over the CTAs, so the CTA with the longest causal item of one round gets the shortest of the next.
+//   warp 0      TMA producer: per item Q, then K tiles of 64 keys through a ring of three stages and V tiles through
+//               a ring of two, K one tile ahead of V (a K stage is free with S(j), a V stage only with PV(j)).
 //   warp 1      one lane issues S = Q K^T (tcgen05.mma, 128 x 64 x d, into one of two S buffers in tensor memory);
 //   warp 6      one lane issues O += P V (128 x d x 64, accumulated in tensor memory over all key tiles).
 //               Both products read their A operand (Q, P) from tensor memory as packed f16 and only K and V from
@@ -26,6 +28,8 @@
 // f16, and the row sum is kept in f32 on the same reference.
 // S(j+1) is issued while the softmax warps work on tile j (it needs PV(j-1), whose P it overwrites, to have
 // completed), and the second CTA of the SM fills the remaining gaps.
+// End of an item: O into registers (which frees it for the next item), the next item's Q into tensor memory (so its
+// first S product runs meanwhile), then the rows are packed in shared memory and leave as one TMA store per 32 rows.
 //
 // Operands are addressed through 4-D tensor maps (d, row, head, batch) whose extents are exactly the
 // valid data, so everything outside (rows past kv_len, dims past d) is zero-filled by TMA: no stale
