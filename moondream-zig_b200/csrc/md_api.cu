@@ -131,6 +131,11 @@ static int reset_flags(md_ctx* ctx) {
         init.mirror = nullptr;
     }
     MD_CUDA(ctx, cudaMemcpy(ctx->flags, &init, sizeof(init), cudaMemcpyHostToDevice));
+    // a kernel that gave up may have left arrival counts behind (split-KV decode attention, split-K GEMM): the next
+    // launch must find them at zero
+    if (ctx->counters) MD_CUDA(ctx, cudaMemset(ctx->counters, 0, MD_COUNTER_WORDS * 4));
+    for (auto& w : ctx->splitk)
+        if (w.tickets) MD_CUDA(ctx, cudaMemset(w.tickets, 0, MD_SPLITK_TICKETS * sizeof(unsigned)));
     return MD_OK;
 }
 
